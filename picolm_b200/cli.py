@@ -1,0 +1,115 @@
+"""The command line, after the reference's (picolm/picolm.c:140-196, parsed at
+picolm/picolm.c:820-940): a positional model path, `-p` prompt (or standard
+input), `-n` max tokens, `-t` temperature, `-k` top-k, `--top-p`, `-s` seed, `-c`
+context.  There is no tokenizer here, so a prompt is token ids separated by
+commas or blanks; several prompts (one per line, or separated by ';' in `-p`)
+run as batches.  Generated ids go to standard output, one line per prompt; the
+reference's `Prefill:` / `Generation:` lines go to standard error
+(picolm/picolm.c:1629-1636).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import re
+import sys
+from typing import List
+
+
+def parse_prompts(text: str) -> List[List[int]]:
+    prompts = []
+    for chunk in re.split(r"[;\n]", text):
+        ids = [int(t) for t in re.split(r"[,\s]+", chunk.strip()) if t]
+        if ids:
+            prompts.append(ids)
+    return prompts
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(
+        prog="picolm_b200",
+        description="picolm_b200 - Llama inference on one B200 (token ids in, token ids out)")
+    ap.add_argument("model", nargs="?", help="model folder (config.json + model.safetensors)")
+    g = ap.add_argument_group("Generation options")
+    g.add_argument("-p", dest="prompt", help="input prompt as token ids, e.g. \"1,15,27\" (or pipe via stdin); "
+                                             "';' or newlines separate several prompts")
+    g.add_argument("-n", dest="max_tokens", type=int, default=256, help="max tokens to generate (default: 256)")
+    g.add_argument("-t", dest="temperature", type=float, default=0.8, help="temperature (default: 0.8, 0=greedy)")
+    g.add_argument("-k", dest="top_k", type=int, default=40, help="top-k sampling (default: 40, 0=off)")
+    g.add_argument("--top-p", dest="top_p", type=float, default=0.9, help="top-p / nucleus sampling (default: 0.9)")
+    g.add_argument("--min-p", dest="min_p", type=float, default=0.05,
+                   help="drop tokens below min-p times the top probability (default: 0.05)")
+    g.add_argument("-s", dest="seed", type=int, default=42, help="RNG seed (default: 42)")
+    g.add_argument("-c", dest="context", type=int, default=0, help="context length override")
+    g.add_argument("--stop-id", dest="stop_ids", type=int, action="append",
+                   help="stop at this token id (default: the model's eos_token_id); may be repeated")
+    e = ap.add_argument_group("Engine options")
+    e.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                   help="bfloat16 (serving kernels) or float32 (everything in true 32-bit)")
+    e.add_argument("--max-batch", type=int, default=8, help="most sequences generated together (default: 8)")
+    i = ap.add_argument_group("Info options")
+    i.add_argument("--list-tensors", action="store_true", help="list all tensors (name, shape, type) and exit")
+    r = ap.add_argument_group("Random weights")
+    r.add_argument("--random-weights", metavar="CONFIG_JSON",
+                   help="write a model folder with random weights for this config.json and exit")
+    r.add_argument("--out", help="folder to write with --random-weights")
+    return ap
+
+
+def main(argv=None) -> int:
+    ap = build_parser()
+    args = ap.parse_args(argv)
+
+    if args.random_weights:
+        if not args.out:
+            ap.error("--random-weights needs --out DIR")
+        from . import architectures  # noqa: F401
+        from .config.registry import read_config
+        from .weights import write_random_model
+        write_random_model(read_config(args.random_weights), args.seed, args.out)
+        print(f"wrote {args.out}", file=sys.stderr)
+        return 0
+
+    if not args.model:
+        ap.print_usage(sys.stderr)
+        return 1
+
+    if args.list_tensors:
+        from .weights import Checkpoint
+        ck = Checkpoint(args.model)
+        for name in sorted(ck.names()):
+            ent = ck.entries[name]
+            print(f"{name}\t{list(ent.shape)}\t{ent.dtype}")
+        return 0
+
+    text = args.prompt if args.prompt is not None else sys.stdin.read()
+    try:
+        prompts = parse_prompts(text)
+    except ValueError as e:
+        print(f"prompt must be token ids: {e}", file=sys.stderr)
+        return 1
+    if not prompts:
+        print("no prompt given (-p \"1,2,3\" or token ids on stdin)", file=sys.stderr)
+        return 1
+
+    from .api import generate, model_load
+    engine = model_load(args.model, dtype=args.dtype, context=args.context or None,
+                        max_batch=min(args.max_batch, len(prompts)))
+    outputs, stats = generate(engine, prompts, max_tokens=args.max_tokens, temperature=args.temperature,
+                              top_p=args.top_p, top_k=args.top_k, min_p=args.min_p, seed=args.seed,
+                              stop_ids=args.stop_ids, return_stats=True)
+    for out in outputs:
+        print(" ".join(str(t) for t in out))
+    sys.stdout.flush()
+    pf, gn = stats.prefill_seconds, stats.generation_seconds
+    print("---", file=sys.stderr)
+    print(f"Prefill: {stats.prefill_tokens} tokens in {pf:.2f}s ({stats.prefill_tokens / pf if pf > 0 else 0:.1f} tok/s)",
+          file=sys.stderr)
+    print(f"Generation: {stats.generated_tokens} tokens in {gn:.2f}s "
+          f"({stats.generated_tokens / gn if gn > 0 else 0:.1f} tok/s)", file=sys.stderr)
+    print(f"Total: {pf + gn:.2f}s", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

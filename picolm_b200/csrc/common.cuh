@@ -1,0 +1,65 @@
+// Shared device helpers of the picolm_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+// Tokens per cache page.  The cache, the step metadata and every kernel that
+// walks a block table agree on this one number.
+#define PLM_PAGE 64
+
+// Return codes of the extern "C" entry points: 0 = launched, > 0 = a cudaError_t,
+// < 0 = the arguments were refused before any launch.
+#define PLM_OK 0
+#define PLM_ERR_DTYPE (-1)
+#define PLM_ERR_SHAPE (-2)
+#define PLM_ERR_ALIGN (-3)
+#define PLM_ERR_UNSUPPORTED (-4)
+
+// dtype codes shared with the Python side
+#define PLM_F32 0
+#define PLM_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, at most 1024); every
+// thread gets the result.  `red` is shared scratch of at least 33 floats.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = (lane < NT / 32) ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+static inline int plm_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? PLM_OK : (int)e;
+}

@@ -1,0 +1,215 @@
+// Row-wise and element-wise kernels of the decoder: token embedding gather,
+// RMSNorm with the residual add folded in, SwiGLU, and rotary position
+// encoding fused with the write of K and V into the paged cache.
+//
+// Formulas follow the reference's scalar forms:
+//   RMSNorm   ss = sum x^2; r = 1/sqrtf(ss/size + eps); out = (x*r)*w   (picolm/tensor.c:2942-3064)
+//   SiLU      x / (1 + expf(-x)), multiplied by the up branch             (picolm/tensor.c:3306-3315,
+//                                                                          picolm/model_core.c:2192-2193)
+//   RoPE      (x0,x1) -> (x0*c - x1*s, x0*s + x1*c), q and k only         (picolm/tensor.c:3216-3304)
+//   embedding x = float(row of the table), no scale                       (picolm/model_core.c:1785-1786)
+// All statistics and the residual stream are fp32.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename Tw>
+__global__ void embed_kernel(const int* __restrict__ tok, const Tw* __restrict__ table, float* __restrict__ out,
+                             int d, int vocab) {
+    const int t = blockIdx.x;
+    int id = tok[t];
+    if (id < 0 || id >= vocab) id = 0;   // ids are checked on the host; never read outside the table
+    const Tw* row = table + (size_t)id * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<Tw>(row[i]);
+}
+
+extern "C" int plm_embed(const int* tok, const void* table, int table_dtype, float* out, int n_tokens, int d,
+                         int vocab, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (d <= 0 || vocab <= 0) return PLM_ERR_SHAPE;
+    const int nt = d >= 1024 ? 256 : 128;
+    if (table_dtype == PLM_F32)
+        embed_kernel<float><<<n_tokens, nt, 0, stream>>>(tok, (const float*)table, out, d, vocab);
+    else if (table_dtype == PLM_BF16)
+        embed_kernel<bf16><<<n_tokens, nt, 0, stream>>>(tok, (const bf16*)table, out, d, vocab);
+    else
+        return PLM_ERR_DTYPE;
+    return plm_launch_status();
+}
+
+// -------------------------------------------------------------------- RMSNorm
+// One block per output row.  Row r reads source row rows[r] (or r).  With a
+// delta the sum x + delta is normalised; it is written back to x unless rows are
+// gathered.  The reduction order depends on the row's width only, never on what
+// else is in the batch.
+template <typename Tw, typename To, int NT>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const Tw* __restrict__ w,
+                               To* __restrict__ out, const int* __restrict__ rows, int d, float eps, int write_back) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* xr = x + (size_t)src * d;
+    const float* dr = delta ? delta + (size_t)src * d : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += NT) {
+        float v = xr[i];
+        if (dr) {
+            v += dr[i];
+            if (write_back) xr[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum<NT>(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    To* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += NT) {
+        float v = xr[i];
+        if (dr && !write_back) v += dr[i];
+        o[i] = from_f32<To>(v * scale * to_f32<Tw>(w[i]));
+    }
+}
+
+template <typename Tw, typename To>
+static int rmsnorm_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows, int d,
+                          float eps, int write_back, cudaStream_t stream) {
+    rmsnorm_kernel<Tw, To, 256><<<n_rows, 256, 0, stream>>>(x, delta, (const Tw*)w, (To*)out, rows, d, eps, write_back);
+    return plm_launch_status();
+}
+
+extern "C" int plm_rmsnorm(float* x, const float* delta, const void* w, int w_dtype, void* out, int out_dtype,
+                           const int* rows, int n_rows, int d, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0) return PLM_ERR_SHAPE;
+    const int write_back = (delta != nullptr && rows == nullptr) ? 1 : 0;
+    if (w_dtype == PLM_F32 && out_dtype == PLM_F32)
+        return rmsnorm_launch<float, float>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_F32)
+        return rmsnorm_launch<bf16, float>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_F32 && out_dtype == PLM_BF16)
+        return rmsnorm_launch<float, bf16>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_BF16)
+        return rmsnorm_launch<bf16, bf16>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
+    return PLM_ERR_DTYPE;
+}
+
+// --------------------------------------------------------------------- SwiGLU
+// gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  out[T,F] = silu(gate) * up.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t t = i / F;
+        const int c = (int)(i - t * F);
+        const float g = to_f32<T>(gu[t * 2 * F + c]);
+        const float u = to_f32<T>(gu[t * 2 * F + F + c]);
+        out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int F, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (F <= 0) return PLM_ERR_SHAPE;
+    const size_t total = (size_t)n_rows * F;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == PLM_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, F, total);
+    else if (dtype == PLM_BF16)
+        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, total);
+    else
+        return PLM_ERR_DTYPE;
+    return plm_launch_status();
+}
+
+// ------------------------------------------------- RoPE + write into the cache
+// qkv is [T, (H + 2G) * hd]: H query heads, then G key heads, then G value heads.
+// Query heads are rotated into q_out [T, H, hd]; key heads are rotated and
+// written, value heads copied, into the paged cache
+//   cache[page][g][slot_in_page][hd],  page = block_table[seq][pos / PLM_PAGE].
+// cos/sin are [table_len, rot_dim/2] fp32 tables; null tables mean no rotation.
+// pairing 0: (x[i], x[i + rot_dim/2]); pairing 1: (x[2i], x[2i+1]).  Elements at
+// and beyond rot_dim pass through.  store = 0 skips the cache (a layer that reads
+// another layer's cache).
+template <typename Ta, typename Tc>
+__global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q_out, Tc* __restrict__ kc,
+                                  Tc* __restrict__ vc, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                  int max_pages, int H, int G, int hd, int rot_dim, int pairing, int store) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd / 2, rot_half = rot_dim / 2;
+    const int n_heads = H + 2 * G;
+    const Ta* row = qkv + (size_t)t * n_heads * hd;
+    size_t page_base = 0;
+    int in_page = 0;
+    bool have_page = false;
+    if (store) {
+        const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / PLM_PAGE];
+        have_page = page >= 0;
+        page_base = (size_t)(page < 0 ? 0 : page) * G;
+        in_page = pos % PLM_PAGE;
+    }
+    for (int item = threadIdx.x; item < n_heads * half; item += blockDim.x) {
+        const int head = item / half, j = item - head * half;
+        int ia, ib;
+        bool rotate = (j < rot_half) && cos_t != nullptr;
+        if (j < rot_half) {
+            if (pairing == 0) { ia = j; ib = j + rot_half; } else { ia = 2 * j; ib = 2 * j + 1; }
+        } else {
+            ia = rot_dim + 2 * (j - rot_half); ib = ia + 1;
+        }
+        float a = to_f32<Ta>(row[head * hd + ia]);
+        float b = to_f32<Ta>(row[head * hd + ib]);
+        if (head < H) {
+            if (rotate) {
+                const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
+                const float ra = a * c - b * s, rb = a * s + b * c;
+                a = ra; b = rb;
+            }
+            Ta* o = q_out + ((size_t)t * H + head) * hd;
+            o[ia] = from_f32<Ta>(a);
+            o[ib] = from_f32<Ta>(b);
+        } else if (head < H + G) {
+            if (!store || !have_page) continue;
+            if (rotate) {
+                const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
+                const float ra = a * c - b * s, rb = a * s + b * c;
+                a = ra; b = rb;
+            }
+            const int g = head - H;
+            Tc* o = kc + ((page_base + g) * PLM_PAGE + in_page) * hd;
+            o[ia] = from_f32<Tc>(a);
+            o[ib] = from_f32<Tc>(b);
+        } else {
+            if (!store || !have_page) continue;
+            const int g = head - H - G;
+            Tc* o = vc + ((page_base + g) * PLM_PAGE + in_page) * hd;
+            o[ia] = from_f32<Tc>(a);
+            o[ib] = from_f32<Tc>(b);
+        }
+    }
+}
+
+extern "C" int plm_rope_store(const void* qkv, void* q_out, void* kc, void* vc, int dtype, const float* cos_t,
+                              const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
+                              int max_pages, int n_tokens, int H, int G, int hd, int rot_dim, int pairing, int store,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || hd <= 0 || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return PLM_ERR_SHAPE;
+    if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
+    const int items = (H + 2 * G) * (hd / 2);
+    const int nt = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+    if (dtype == PLM_F32)
+        rope_store_kernel<float, float><<<n_tokens, nt, 0, stream>>>(
+            (const float*)qkv, (float*)q_out, (float*)kc, (float*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table,
+            max_pages, H, G, hd, rot_dim, pairing, store);
+    else if (dtype == PLM_BF16)
+        rope_store_kernel<bf16, bf16><<<n_tokens, nt, 0, stream>>>(
+            (const bf16*)qkv, (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table,
+            max_pages, H, G, hd, rot_dim, pairing, store);
+    else
+        return PLM_ERR_DTYPE;
+    return plm_launch_status();
+}

@@ -1,0 +1,101 @@
+"""The engine: a model, its cache, and the one step function that both
+generation and trace replay drive.
+
+`step` runs exactly the tokens it is given, as one batch, against what earlier
+steps left in the cache, and returns the logits at the wanted places.  A batch's
+sequences start together with their whole prompts (unequal lengths) in one step
+and then go on by one token each; sequences that have ended are simply no longer
+in the entries.  The reference's two entry points are the single-sequence cases
+of it: `model_forward(token, pos)` (picolm/model_core.c:1682) and
+`model_forward_prefill(tokens, n, start_pos)` (picolm/model_core.c:2671).
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the known architectures)
+from ..cache import CacheFull, SequenceCache
+from ..config.registry import read_config, spec_of
+from ..runtime import Runtime
+from ..weights.loader import load_weights
+from .model import Model
+from .step_batch import StepBatch, build_step_batch
+
+
+class Engine:
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 max_seq_tokens: Optional[int] = None):
+        """`max_tokens`: the most tokens that live sequences hold at any time, each
+        sequence's count rounded up to a multiple of the page size.  `max_seqs`:
+        the most sequences alive at once (default: one per page).
+        `max_seq_tokens`: the longest single sequence (default: the model's
+        position limit, or the whole cache if that is smaller)."""
+        if not model.loaded:
+            raise RuntimeError("the model has no weights yet")
+        self.model = model
+        self.runtime = model.runtime
+        spec = model.spec
+        longest = min(max_seq_tokens or spec.max_positions, spec.max_positions)
+        self.cache = SequenceCache(model.cache_specs(), max_tokens=max_tokens,
+                                   max_seqs=max_seqs or max(1, (max_tokens + 63) // 64),
+                                   kv_dtype=self.runtime.dtype, device=self.runtime.device,
+                                   max_seq_tokens=longest)
+        model.prepare(self.cache.max_seq_tokens)
+        self.vocab_size = spec.vocab_size
+
+    # ----------------------------------------------------------- construction
+    @staticmethod
+    def from_folder(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
+                    max_seq_tokens: Optional[int] = None, device="cuda:0") -> "Engine":
+        """Load `model_dir` (config.json + safetensors); the model class is chosen
+        by config.json's `architectures` through the registry."""
+        runtime = Runtime.create(dtype, device)
+        config = read_config(model_dir)
+        model = Model(spec_of(config), runtime)
+        load_weights(model, model_dir)
+        eng = Engine(model, max_tokens, max_seqs, max_seq_tokens)
+        eng.config = config
+        return eng
+
+    # -------------------------------------------------------------- sequences
+    def new_sequence(self) -> int:
+        """A cache slot for a sequence that starts now."""
+        return self.cache.allocate()
+
+    def end_sequence(self, slot: int) -> None:
+        """Give back the slot and everything it holds."""
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ------------------------------------------------------------------- step
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             wants: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Run one step.  `entries`: for each sequence its slot and its next
+        tokens.  `wants`: for each sequence the places among these tokens whose
+        logits are wanted (default: the last one).  Returns fp32 logits
+        [wanted places, vocab] on the device, in the order of the entries and of
+        `wants`, or None if nothing is wanted."""
+        if not entries:
+            return None
+        if wants is None:
+            wants = [[len(toks) - 1] for _, toks in entries]
+        if len(wants) != len(entries):
+            raise ValueError("wants must have one list per entry")
+        for slot, toks in entries:
+            if len(toks) == 0:
+                raise ValueError(f"slot {slot}: a sequence must bring at least one token")
+            lo, hi = min(toks), max(toks)
+            if lo < 0 or hi >= self.vocab_size:
+                raise ValueError(f"slot {slot}: token id {lo if lo < 0 else hi} is outside the vocabulary "
+                                 f"[0, {self.vocab_size})")
+        self.cache.reserve([(slot, len(toks)) for slot, toks in entries])
+        batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
+        logits = self.model.forward(batch, self.cache)
+        for slot, toks in entries:
+            self.cache.advance(slot, len(toks))
+        return logits

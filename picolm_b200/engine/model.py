@@ -1,0 +1,115 @@
+"""A model put together from a `ModelSpec`: embedding, blocks, final norm and
+head, and the schedule in which the blocks run.  Architecture-agnostic: what the
+parts are is decided by the spec, and what runs is decided by the schedule.
+
+One forward of a step follows the reference's order (picolm/model_core.c:1785-2220,
+picolm/model_core.c:2757-3225): embed, the layers, then final norm and LM head on
+the rows whose logits are wanted only (the reference's prefill does this for the
+last row, picolm/model_core.c:3219-3225).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache.sequence_cache import KVLayerCache, SequenceCache, StateLayerCache
+from ..cache.spec import CacheSpec
+from ..config.spec import ModelSpec
+from ..parts import ResidualStream, WeightSpec, build_part, part_class
+from ..parts.base import Part
+from ..runtime import Runtime
+
+
+def _join(*names: str) -> str:
+    return ".".join(n for n in names if n)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, runtime: Optional[Runtime]):
+        spec.validate()
+        self.spec = spec
+        self.runtime = runtime
+        self.embedding = build_part("embedding", spec.embedding, runtime)
+        self.blocks = [part_class("arrangement", layer.arrangement)(layer, runtime) for layer in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.head = build_part("head", spec.lm_head, runtime)
+        self.loaded = False
+
+    # ---------------------------------------------------------------- weights
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        """(absolute tensor-name prefix, part) of every part that owns weights."""
+        out: List[Tuple[str, Part]] = [(self.spec.embedding.prefix, self.embedding)]
+        for layer, block in zip(self.spec.layers, self.blocks):
+            for rel, part in block.parts():
+                out.append((_join(layer.prefix, rel), part))
+        out.append((self.spec.final_norm.prefix, self.final_norm))
+        out.append((self.spec.lm_head.prefix, self.head))
+        return out
+
+    def expected_tensors(self) -> Dict[str, WeightSpec]:
+        """Every tensor name the model reads, with its shape.  Two parts may name
+        the same tensor (tied embeddings); their shapes must agree."""
+        out: Dict[str, WeightSpec] = {}
+        for prefix, part in self.named_parts():
+            for rel, ws in part.weight_specs().items():
+                name = _join(prefix, rel)
+                if name in out and out[name].shape != ws.shape:
+                    raise ValueError(f"tensor {name!r} is wanted with shapes {out[name].shape} and {ws.shape}")
+                out.setdefault(name, ws)
+        return out
+
+    def load_tensors(self, get: Callable[[str], torch.Tensor]) -> None:
+        """Hand every part its tensors; `get(name)` returns the device tensor
+        (the same object for the same name, so tied weights stay one buffer)."""
+        for prefix, part in self.named_parts():
+            part.load({rel: get(_join(prefix, rel)) for rel in part.weight_specs()})
+        self.loaded = True
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights one decode step reads: every matrix of every scheduled
+        layer once, the norms, and the LM head (the embedding rows are negligible)."""
+        total = self.final_norm.weight_bytes() + self.head.weight_bytes()
+        for i in self.spec.schedule:
+            total += sum(part.weight_bytes() for _, part in self.blocks[i].parts())
+        return total
+
+    # ------------------------------------------------------------------ cache
+    def cache_specs(self) -> List[Optional[CacheSpec]]:
+        """What each layer owns in the cache (None: nothing, or another layer's)."""
+        out: List[Optional[CacheSpec]] = []
+        for layer, block in zip(self.spec.layers, self.blocks):
+            out.append(None if layer.cache_of is not None else block.mixer.cache_spec())
+        return out
+
+    def prepare(self, max_seq_tokens: int) -> None:
+        for block in self.blocks:
+            prep = getattr(block.mixer, "prepare", None)
+            if prep is not None:
+                prep(max_seq_tokens)
+
+    def layer_cache(self, layer: int, cache: SequenceCache, step):
+        owner = self.spec.layers[layer].cache_of
+        writable = owner is None
+        src = layer if owner is None else owner
+        if src in cache.layer_group:
+            gi = cache.layer_group[src]
+            g = cache.kv_groups[gi]
+            o = g.ordinal(src)
+            return KVLayerCache(g.k[o], g.v[o], step.block_tables[gi], g.spec.window, writable)
+        if src in cache.state:
+            return StateLayerCache(cache.state[src], writable)
+        return None
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, step, cache: SequenceCache) -> Optional[torch.Tensor]:
+        """Run the step's tokens through the scheduled layers; returns fp32 logits
+        [wanted rows, vocab] (None if no row is wanted)."""
+        stream = ResidualStream(self.embedding.forward(step))
+        for i in self.spec.schedule:
+            self.blocks[i].forward(stream, step, self.layer_cache(i, cache, step))
+        if step.n_want == 0:
+            # the last delta need not be added: nothing reads the stream after it
+            return None
+        h = self.final_norm.forward(stream, rows=step.want_rows)
+        return self.head.forward(h)

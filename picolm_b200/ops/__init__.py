@@ -1,0 +1,262 @@
+"""Python faces of the CUDA kernels.  Every function checks what it is given
+(device, dtype, shape, contiguity), launches on the current CUDA stream and
+raises `KernelError` if the kernel library refuses or fails.  There is no CPU
+path: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_library
+
+PAGE_TOKENS = 64            # tokens per cache page; PLM_PAGE in csrc/common.cuh
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+_SIGNATURES = {
+    "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
+    "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
+    "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
+}
+_fn_cache = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", -4: "unsupported option",
+          -5: "the device wait ran out (see the status word)"}
+
+
+def _fn(library: str, name: str, extra_flags=()):
+    key = (library, name, tuple(extra_flags))
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = load_library(library, extra_flags)
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = ctypes.c_int
+        _fn_cache[key] = f
+    return f
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused ({_CODES.get(code, code)})")
+    raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        return torch.cuda.cudart().cudaGetErrorString(code)  # type: ignore[attr-defined]
+    except Exception:
+        return "see cudaError_t"
+
+
+def _dev(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; picolm_b200 kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DT:
+        raise KernelError(f"{name} has dtype {t.dtype}; float32 and bfloat16 are supported")
+    return _DT[t.dtype]
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _dev(t, name)
+    if t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+
+
+# ---------------------------------------------------------------- elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = float(table[tokens[t], :]) as the fp32 residual stream."""
+    _i32(tokens, "tokens")
+    _dev(table, "table")
+    n, (vocab, d) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, d), dtype=torch.float32, device=table.device)
+    _check(_fn("elementwise", "plm_embed")(_p(tokens), _p(table), _dt(table, "table"), _p(out), n, d, vocab, _stream()),
+           "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of the fp32 stream `x` [T, d].  With `delta` the sum x + delta is
+    normalised and, unless `rows` gathers, written back to x.  `rows` (int32)
+    picks the source rows; the output then has len(rows) rows."""
+    _dev(x, "x")
+    _dev(weight, "weight")
+    if x.dtype != torch.float32:
+        raise KernelError("the residual stream must be float32")
+    T, d = x.shape
+    if weight.shape != (d,):
+        raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
+    if delta is not None:
+        _dev(delta, "delta")
+        if delta.dtype != torch.float32 or delta.shape != x.shape:
+            raise KernelError("delta must be float32 and shaped like x")
+    n_rows = T
+    if rows is not None:
+        _i32(rows, "rows")
+        n_rows = rows.numel()
+    if out is None:
+        out = torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "plm_rmsnorm")(
+        _p(x), _p(delta), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
+        float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gate_up [T, 2F] (gate columns first) -> silu(gate) * up, [T, F]."""
+    _dev(gate_up, "gate_up")
+    T, F2 = gate_up.shape
+    if F2 % 2:
+        raise KernelError("gate_up must have an even number of columns")
+    if out is None:
+        out = torch.empty((T, F2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_fn("elementwise", "plm_swiglu")(_p(gate_up), _p(out), _dt(gate_up, "gate_up"), T, F2 // 2, _stream()),
+           "swiglu")
+    return out
+
+
+def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+               v_cache: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+               tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+               num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, pairing: str,
+               store: bool = True) -> None:
+    """Rotate the query and key heads of `qkv` [T, (H+2G)*hd] by their tokens'
+    positions; write queries to `q_out` [T, H, hd] and keys/values into the paged
+    cache [pages, G, PAGE_TOKENS, hd]."""
+    _dev(qkv, "qkv")
+    _dev(q_out, "q_out")
+    _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
+    T = qkv.shape[0]
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    if qkv.shape[1] != (H + 2 * G) * hd or q_out.shape != (T, H, hd) or q_out.dtype != qkv.dtype:
+        raise KernelError("rope_store: qkv / q_out shapes do not match the head counts")
+    if store:
+        for c, n in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+            _dev(c, n)
+            if c.dtype != qkv.dtype or c.shape[1:] != (G, PAGE_TOKENS, hd):
+                raise KernelError(f"rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd}] of {qkv.dtype}")
+    if cos is not None:
+        _dev(cos, "cos"), _dev(sin, "sin")
+        if cos.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rope_store: cos/sin tables must be float32 [positions, rotary_dim/2]")
+    if pairing not in ("half", "adjacent"):
+        raise KernelError(f"rope_store: unknown pairing {pairing!r}")
+    _check(_fn("elementwise", "plm_rope_store")(
+        _p(qkv), _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None, _dt(qkv, "qkv"),
+        _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1], T, H, G, hd,
+        rotary_dim, 0 if pairing == "half" else 1, 1 if store else 0, _stream()), "rope_store")
+
+
+# ----------------------------------------------------------------------- GEMM
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, fp32 accumulation."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: a is [{M}, {K}] but w is [{N}, {K2}]")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _check(_fn("gemm_simt", "plm_gemm_simt")(
+        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, K, K, N, _stream()), "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
+                   tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
+                   window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of q [T, H, hd] over the paged cache; returns [T, H*hd]."""
+    _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
+    _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
+    T, H, hd = q.shape
+    G = num_kv_heads
+    if k_cache.dtype != q.dtype or k_cache.shape[1:] != (G, PAGE_TOKENS, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"attention: the cache must be [pages, {G}, {PAGE_TOKENS}, {hd}] of {q.dtype}")
+    if hd > 256:
+        raise KernelError(f"attention: head_dim {hd} exceeds 256, the largest this kernel takes")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    _check(_fn("attention_simt", "plm_attention_rows")(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _dt(q, "q"), _p(tok_pos), _p(tok_seq), _p(block_table),
+        block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _stream()), "attention_rows")
+    return out
+
+
+# ------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First index of each row's maximum, int32 [rows]."""
+    _dev(logits, "logits")
+    if logits.dtype != torch.float32:
+        raise KernelError("logits must be float32")
+    n, V = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "plm_argmax")(_p(logits), V, n, V, _p(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           min_p: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row by the reference's chain (top-k, top-p, min-p, p^(1/T));
+    `rng_state` (int64 [rows], xorshift64 states) is advanced in place."""
+    _dev(logits, "logits"), _dev(rng_state, "rng_state")
+    if logits.dtype != torch.float32 or rng_state.dtype != torch.int64:
+        raise KernelError("sample: logits must be float32 and rng_state int64")
+    n, V = logits.shape
+    if rng_state.numel() != n:
+        raise KernelError("sample: one rng state per row is needed")
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "plm_sample")(
+        _p(logits), V, n, V, float(temperature), int(top_k), float(top_p), float(min_p), _p(rng_state), _p(out),
+        _stream()), "sample")
+    return out
+
+
+# ---------------------------------------------------------------- dispatchers
+def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
+    types and shape, never by the model."""
+    return gemm_simt(a, w, out_dtype)
+
+
+def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> torch.Tensor:
+    """Causal attention of the step's queries over their sequences' cached keys
+    and values (`kv` is a `KVLayerCache`)."""
+    return attention_rows(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
+                          window=kv.window)

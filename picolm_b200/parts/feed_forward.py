@@ -1,0 +1,48 @@
+"""Feed-forwards.  Interface of the family: `forward(h, step)` takes the normed
+activations [T, d] and returns the residual delta [T, d] in fp32.
+
+The gated MLP as the reference computes it: `g = Wg x`, `u = Wu x`,
+`h = g / (1 + expf(-g)) * u`, `delta = Wd h`, no bias
+(picolm/model_core.c:2182-2204, picolm/tensor.c:3306-3315).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, WeightSpec, register_part
+from .mixer import _stack_rows
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(Part):
+    """params: hidden_size, intermediate_size, activation ("silu"),
+    gate_name/up_name/down_name (relative tensor names)."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        if self.params["activation"] != "silu":
+            raise ValueError(f"activation {self.params['activation']!r} has no kernel (silu only)")
+
+    def weight_specs(self):
+        p = self.params
+        d, F = p["hidden_size"], p["intermediate_size"]
+        return {
+            p["gate_name"]: WeightSpec((F, d)),
+            p["up_name"]: WeightSpec((F, d)),
+            p["down_name"]: WeightSpec((d, F)),
+        }
+
+    def load(self, tensors):
+        p = self.params
+        # one projection for both branches: rows [gate | up]
+        self.w_gate_up = _stack_rows([tensors[p["gate_name"]], tensors[p["up_name"]]])
+        self.w_down = tensors[p["down_name"]]
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, h, step):
+        gate_up = ops.linear(h, self.w_gate_up, self.runtime.dtype)
+        act = ops.swiglu(gate_up)
+        return ops.linear(act, self.w_down, torch.float32)

@@ -1,0 +1,102 @@
+"""Configuration and registry (no device)."""
+import json
+
+import pytest
+
+from picolm_b200.config import (ConfigError, LlamaConfig, config_from_dict, read_config, registered_architectures,
+                                spec_of)
+from util import TINY
+
+
+def test_reads_every_key_of_both_tiny_configs():
+    a = config_from_dict(TINY["A"]["config"])
+    b = config_from_dict(TINY["B"]["config"])
+    assert (a.num_hidden_layers, a.hidden_size, a.num_attention_heads, a.num_key_value_heads, a.head_dim) == (2, 64, 4, 2, 16)
+    assert (a.intermediate_size, a.vocab_size, a.rope_theta, a.rms_norm_eps) == (172, 256, 10000.0, 1e-5)
+    assert a.rope_scaling is None and not a.tie_word_embeddings and a.eos_token_id == (2,)
+    assert (b.num_hidden_layers, b.hidden_size, b.num_attention_heads, b.num_key_value_heads, b.head_dim) == (3, 96, 3, 1, 32)
+    assert b.rope_scaling.factor == 4.0 and b.rope_scaling.original_max_position_embeddings == 64
+    assert b.tie_word_embeddings and b.eos_token_id == (3, 4) and b.max_position_embeddings == 256
+
+
+def test_defaults_of_absent_keys_follow_the_reference():
+    raw = {"architectures": ["LlamaForCausalLM"], "vocab_size": 10, "hidden_size": 24, "intermediate_size": 8,
+           "num_hidden_layers": 1, "num_attention_heads": 3}
+    c = config_from_dict(raw)
+    assert c.head_dim == 8 and c.num_key_value_heads == 3
+    assert c.rms_norm_eps == 1e-6 and c.rope_theta == 10000.0
+    assert c.bos_token_id == 1 and c.eos_token_id == (2,)
+
+
+def test_round_trip_through_json(tmp_path):
+    c = config_from_dict(TINY["B"]["config"])
+    (tmp_path / "config.json").write_text(json.dumps(c.to_dict()))
+    assert read_config(str(tmp_path)) == c
+
+
+def test_text_config_is_unwrapped():
+    inner = dict(TINY["A"]["config"])
+    archs = inner.pop("architectures")
+    c = config_from_dict({"architectures": archs, "text_config": inner})
+    assert c.hidden_size == 64
+
+
+@pytest.mark.parametrize("patch,word", [
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"attention_bias": True}, "attention_bias"),
+    ({"mlp_bias": True}, "mlp_bias"),
+    ({"num_key_value_heads": 3}, "num_key_value_heads"),
+    ({"head_dim": 15}, "head_dim"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "rope_scaling"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 2.0}}, "low_freq_factor"),
+    ({"vocab_size": 0}, "vocab_size"),
+])
+def test_unsupported_values_name_their_key(patch, word):
+    raw = dict(TINY["A"]["config"])
+    raw.update(patch)
+    with pytest.raises(ConfigError) as e:
+        config_from_dict(raw)
+    assert word in str(e.value)
+
+
+def test_missing_key_is_named():
+    raw = dict(TINY["A"]["config"])
+    del raw["intermediate_size"]
+    with pytest.raises(ConfigError, match="intermediate_size"):
+        config_from_dict(raw)
+
+
+def test_unknown_architecture_lists_the_known_ones():
+    raw = dict(TINY["A"]["config"])
+    raw["architectures"] = ["MambaForCausalLM"]
+    with pytest.raises(KeyError) as e:
+        config_from_dict(raw)
+    assert "LlamaForCausalLM" in str(e.value)
+    assert "LlamaForCausalLM" in registered_architectures()
+
+
+def test_spec_is_data_layer_by_layer():
+    c = config_from_dict(TINY["B"]["config"])
+    s = spec_of(c)
+    assert len(s.layers) == 3 and s.schedule == (0, 1, 2)
+    assert s.layers[1].mixer.kind == "attention" and s.layers[1].feed_forward.kind == "gated_mlp"
+    assert s.layers[2].mixer.params["num_kv_heads"] == 1
+    assert s.layers[0].mixer.params["position"].params["scaling"]["factor"] == 4.0
+    assert s.lm_head.params["name"] == "model.embed_tokens.weight"          # tied
+    assert s.stop_token_ids == (3, 4)
+    a = spec_of(config_from_dict(TINY["A"]["config"]))
+    assert a.lm_head.params["name"] == "lm_head.weight"
+
+
+def test_schedule_and_cache_sharing_are_validated():
+    import dataclasses
+    s = spec_of(config_from_dict(TINY["B"]["config"]))
+    with pytest.raises(ValueError, match="schedule"):
+        dataclasses.replace(s, schedule=(0, 5)).validate()
+    layers = list(s.layers)
+    layers[0] = dataclasses.replace(layers[0], cache_of=2)                   # reads a cache not yet written
+    with pytest.raises(ValueError, match="before"):
+        dataclasses.replace(s, layers=tuple(layers)).validate()
+    layers = list(s.layers)
+    layers[2] = dataclasses.replace(layers[2], cache_of=0)
+    dataclasses.replace(s, layers=tuple(layers), schedule=(0, 1, 2, 1)).validate()

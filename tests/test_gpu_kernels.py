@@ -1,0 +1,270 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same
+operation, at sizes other than the tiny models'.  Inputs are built so that a
+fault shows: one far key among hundreds carries the attention, a window's edge
+decides the result, pages are scattered over the cache."""
+import math
+
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+PAGE = 64
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+def test_embed(wdtype):
+    from picolm_b200 import ops
+    table = torch.randn(301, 72).to(DT[wdtype])
+    toks = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = ops.embed(toks.to(DEV), table.to(DEV))
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), P.embed(toks.tolist(), table.float()))
+
+
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("odtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,eps", [(200, 1e-5), (2048, 1e-6), (7, 0.1)])
+def test_rmsnorm(wdtype, odtype, d, eps):
+    from picolm_b200 import ops
+    torch.manual_seed(d)
+    x = torch.randn(9, d) * 3
+    x[2] *= 1e-3                                            # a row where eps matters
+    w = (1 + 0.1 * torch.randn(d)).to(DT[wdtype])
+    delta = torch.randn(9, d)
+    ref = P.rmsnorm(x + delta, w.float(), eps)
+    xd = x.to(DEV).clone()
+    out = ops.rmsnorm(xd, w.to(DEV), eps, DT[odtype], delta=delta.to(DEV))
+    assert torch.allclose(out.float().cpu(), ref.to(DT[odtype]).float(), **tol(odtype))
+    assert torch.equal(xd.cpu(), x + delta)                 # the sum is written back
+    # gathered rows, no delta, stream untouched
+    rows = torch.tensor([8, 0, 2], dtype=torch.int32)
+    xd = x.to(DEV).clone()
+    out = ops.rmsnorm(xd, w.to(DEV), eps, DT[odtype], rows=rows.to(DEV))
+    assert torch.allclose(out.float().cpu(), P.rmsnorm(x, w.float(), eps)[rows.long()].to(DT[odtype]).float(), **tol(odtype))
+    assert torch.equal(xd.cpu(), x)
+    # gathered rows with a delta: the stream stays as it was
+    out = ops.rmsnorm(xd, w.to(DEV), eps, DT[odtype], delta=delta.to(DEV), rows=rows.to(DEV))
+    assert torch.allclose(out.float().cpu(), ref[rows.long()].to(DT[odtype]).float(), **tol(odtype))
+    assert torch.equal(xd.cpu(), x)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    from picolm_b200 import ops
+    torch.manual_seed(1)
+    gu = (torch.randn(13, 2 * 172) * 4).to(DT[dtype])
+    ref = P.swiglu(gu[:, :172].float(), gu[:, 172:].float())
+    out = ops.swiglu(gu.to(DEV))
+    assert torch.allclose(out.float().cpu(), ref.to(DT[dtype]).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("types", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                   ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "float32")])
+@pytest.mark.parametrize("M,N,K", [(1, 53, 91), (37, 130, 172), (129, 64, 16), (70, 257, 300)])
+def test_gemm_simt(types, M, N, K):
+    from picolm_b200 import ops
+    torch.manual_seed(M * N + K)
+    a = torch.randn(M, K).to(DT[types[0]])
+    w = torch.randn(N, K).to(DT[types[1]])
+    ref = P.linear(a.double(), w.double())
+    out = ops.gemm_simt(a.to(DEV), w.to(DEV), DT[types[2]])
+    assert out.dtype == DT[types[2]]
+    t = dict(atol=1e-4, rtol=1e-5) if types[2] == "float32" else dict(atol=0.1, rtol=1e-2)
+    assert torch.allclose(out.double().cpu(), ref, **t)
+
+
+def _paged(k, v, lens, n_pages, dtype, seed):
+    """Scatter per-sequence K/V [len, G, hd] over a paged cache with shuffled page numbers."""
+    G, hd = k[0].shape[1:]
+    g = torch.Generator().manual_seed(seed)
+    free = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+    kc = torch.full((n_pages, G, PAGE, hd), float("nan")).to(dtype)
+    vc = torch.full((n_pages, G, PAGE, hd), float("nan")).to(dtype)
+    max_pages = max((n + PAGE - 1) // PAGE for n in lens) + 1
+    table = torch.zeros((len(lens), max_pages), dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for blk in range((n + PAGE - 1) // PAGE):
+            page = free.pop()
+            table[b, blk] = page
+            m = min(PAGE, n - blk * PAGE)
+            kc[page, :, :m] = k[b][blk * PAGE:blk * PAGE + m].transpose(0, 1).to(dtype)
+            vc[page, :, :m] = v[b][blk * PAGE:blk * PAGE + m].transpose(0, 1).to(dtype)
+    return kc, vc, table
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,hd", [(6, 2, 48), (5, 5, 16), (8, 1, 128), (4, 2, 80)])
+def test_attention_rows_finds_a_far_key(dtype, H, G, hd):
+    """Sequences of unequal lengths; in each, one chosen far key matches the last
+    queries strongly, so the output is essentially that key's value: a kernel
+    that skips, misplaces or double-counts keys gives a visibly different row."""
+    from picolm_b200 import ops
+    torch.manual_seed(H * 100 + hd)
+    lens = [300, 1, 65, 130]
+    new = [3, 1, 65, 2]                                      # queries: the last `new` positions of each sequence
+    ks, vs, qs, pos, seq = [], [], [], [], []
+    for b, n in enumerate(lens):
+        k, v = torch.randn(n, G, hd) * 0.3, torch.randn(n, G, hd)
+        q = torch.randn(new[b], H, hd) * 0.3
+        far = n // 7
+        for h in range(H):
+            q[-1, h] = k[far, h // (H // G)] * (40.0 / (k[far, h // (H // G)].norm() ** 2)) * math.sqrt(hd)
+        ks.append(k), vs.append(v), qs.append(q)
+        pos += list(range(n - new[b], n))
+        seq += [b] * new[b]
+    dt = DT[dtype]
+    ks = [k.to(dt).float() for k in ks]
+    vs = [v.to(dt).float() for v in vs]
+    qs = [q.to(dt).float() for q in qs]
+    kc, vc, table = _paged(ks, vs, lens, 16, dt, 5)
+    scale = 1.0 / math.sqrt(hd)
+    ref = []
+    for b, n in enumerate(lens):
+        full_q = torch.zeros(n, H, hd)
+        full_q[n - new[b]:] = qs[b]
+        ref.append(P.attention(full_q, ks[b], vs[b], scale)[n - new[b]:].reshape(new[b], H * hd))
+    ref = torch.cat(ref)
+    out = ops.attention_rows(torch.cat(qs).to(dt).to(DEV), kc.to(DEV), vc.to(DEV),
+                             torch.tensor(pos, dtype=torch.int32, device=DEV),
+                             torch.tensor(seq, dtype=torch.int32, device=DEV), table.to(DEV), G, scale)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)))
+    # the last query of sequence 0 sees (almost) only the far key's value
+    far_v = vs[0][lens[0] // 7]
+    row = out.float().cpu()[new[0] - 1].reshape(H, hd)
+    for h in range(H):
+        assert torch.allclose(row[h], far_v[h // (H // G)], atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_rows_window_edge(dtype):
+    """With a window of W the key at distance W-1 counts and the key at distance
+    W does not: both are made dominant in turn."""
+    from picolm_b200 import ops
+    H = G = 2
+    hd, n, W = 32, 200, 70
+    dt = DT[dtype]
+    torch.manual_seed(9)
+    for dist, inside in ((W - 1, True), (W, False)):
+        k = (torch.randn(n, G, hd) * 0.1).to(dt).float()
+        v = torch.randn(n, G, hd).to(dt).float()
+        q = torch.zeros(1, H, hd)
+        for h in range(H):
+            kk = k[n - 1 - dist, h]
+            q[0, h] = kk * (50.0 / kk.norm() ** 2) * math.sqrt(hd)
+        q = q.to(dt).float()
+        kc, vc, table = _paged([k], [v], [n], 8, dt, 2)
+        out = ops.attention_rows(q.to(dt).to(DEV), kc.to(DEV), vc.to(DEV),
+                                 torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                 torch.tensor([0], dtype=torch.int32, device=DEV), table.to(DEV), G,
+                                 1.0 / math.sqrt(hd), window=W).float().cpu().reshape(H, hd)
+        full_q = torch.zeros(n, H, hd)
+        full_q[-1] = q[0]
+        ref = P.attention(full_q, k, v, 1.0 / math.sqrt(hd), window=W)[-1]
+        assert torch.allclose(out, ref, atol=3e-2 if dtype == "bfloat16" else 2e-5)
+        hit = torch.allclose(out, v[n - 1 - dist], atol=5e-2)
+        assert hit == inside
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("pairing", ["half", "adjacent"])
+@pytest.mark.parametrize("H,G,hd,rot", [(3, 1, 32, 32), (4, 2, 48, 16), (2, 2, 16, 16)])
+def test_rope_store(dtype, pairing, H, G, hd, rot):
+    """Rotation against the plain formula, and every K/V row lands at its own
+    (page, kv head, place in page); nothing else in the cache changes."""
+    from picolm_b200 import ops
+    dt = DT[dtype]
+    torch.manual_seed(hd + rot)
+    pos = [0, 1, 63, 64, 129, 7]
+    seq = [0, 0, 0, 0, 0, 1]
+    table = torch.tensor([[5, 2, 9], [3, 0, 0]], dtype=torch.int32)
+    T = len(pos)
+    qkv = torch.randn(T, (H + 2 * G) * hd).to(dt)
+    cos, sin = P.rope_table(200, rot, 10000.0, None)
+    cos, sin = cos.float(), sin.float()
+    kc = torch.full((10, G, PAGE, hd), 7.0).to(dt)
+    vc = torch.full((10, G, PAGE, hd), 7.0).to(dt)
+    q_out = torch.empty(T, H, hd, dtype=dt, device=DEV)
+    kcd, vcd = kc.to(DEV), vc.to(DEV)
+    ops.rope_store(qkv.to(DEV), q_out, kcd, vcd, cos.to(DEV), sin.to(DEV),
+                   torch.tensor(pos, dtype=torch.int32, device=DEV), torch.tensor(seq, dtype=torch.int32, device=DEV),
+                   table.to(DEV), H, G, hd, rot, pairing)
+    x = qkv.float().reshape(T, H + 2 * G, hd)
+
+    def rotate(part):                                       # [T, heads, hd] by each token's own position
+        out = part.clone()
+        for t, p in enumerate(pos):
+            out[t:t + 1, :, :rot] = P.rope(part[t:t + 1, :, :rot], cos[p:p + 1], sin[p:p + 1], pairing)
+        return out
+
+    t_ = tol(dtype)
+    assert torch.allclose(q_out.float().cpu(), rotate(x[:, :H]).to(dt).float(), **t_)
+    k_ref, v_ref = rotate(x[:, H:H + G]).to(dt).float(), x[:, H + G:]
+    expect_k, expect_v = kc.float().clone(), vc.float().clone()
+    for t, (p, b) in enumerate(zip(pos, seq)):
+        page = table[b, p // PAGE].item()
+        expect_k[page, :, p % PAGE] = k_ref[t]
+        expect_v[page, :, p % PAGE] = v_ref[t]
+    assert torch.allclose(kcd.float().cpu(), expect_k, **t_)
+    assert torch.equal(vcd.float().cpu(), expect_v)
+
+
+def test_argmax_first_index_on_ties():
+    from picolm_b200 import ops
+    x = torch.randn(5, 1000)
+    x[0, 700] = x[0, 30] = 9.0
+    x[1, 999] = 20.0
+    x[2] = 0.0
+    x[3, 0] = 50.0
+    out = ops.argmax(x.to(DEV)).cpu().tolist()
+    assert out == [P.argmax(r) for r in x]
+    assert out[0] == 30 and out[2] == 0
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p,min_p", [
+    (0.8, 40, 0.9, 0.05), (1.0, 0, 1.0, 0.0), (0.5, 5, 1.0, 0.0), (1.3, 0, 0.7, 0.0), (0.9, 0, 1.0, 0.2),
+    (2.0, 3, 0.5, 0.5)])
+def test_sample_against_the_reference_chain(temperature, top_k, top_p, min_p):
+    """Same kept set and weights as the reference's chain; the draw walks in
+    index order.  Several rows, each with its own xorshift64 stream, several
+    draws in a row (the state advances in place)."""
+    from picolm_b200 import ops
+    from picolm_b200.sampling import stream_seed
+    torch.manual_seed(3)
+    V = 777
+    logits = torch.randn(6, V) * 3
+    states = [stream_seed(42, i) for i in range(6)]
+    rng = torch.tensor(states, dtype=torch.int64, device=DEV)
+    ld = logits.to(DEV)
+    for _ in range(4):
+        got = ops.sample(ld, rng, temperature, top_k, top_p, min_p).cpu().tolist()
+        for r in range(6):
+            states[r], want = P.sample_index_order(logits[r], temperature, top_k, top_p, min_p, states[r])
+            kept, _ = P.sampling_weights(logits[r], temperature, top_k, top_p, min_p)
+            assert got[r] in kept
+            assert got[r] == want, f"row {r}: kernel drew {got[r]}, the plain chain {want}"
+    back = [s if s >= 0 else s + (1 << 64) for s in rng.cpu().tolist()]
+    assert back == states
+
+
+def test_sample_distribution():
+    """Over many draws the kernel's frequencies follow softmax(logits / T) on a small vocabulary."""
+    from picolm_b200 import ops
+    V, n = 12, 4000
+    logits = torch.linspace(-2, 2, V)[None, :].repeat(n, 1).contiguous()
+    rng = torch.arange(1, n + 1, dtype=torch.int64, device=DEV) * 7919
+    for _ in range(3):                                       # let the streams decorrelate from their seeds
+        got = ops.sample(logits.to(DEV), rng, 0.7, 0, 1.0, 0.0)
+    freq = torch.bincount(got.cpu().long(), minlength=V).double() / n
+    p = torch.softmax(logits[0].double() / 0.7, dim=0)
+    chi2 = (n * (freq - p) ** 2 / p).sum().item()
+    assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
