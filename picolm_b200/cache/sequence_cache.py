@@ -38,7 +38,7 @@ def pages_for(n_tokens: int) -> int:
 @dataclass
 class KVGroup:
     spec: CacheSpec
-    layers: List[int]                           # model layer indices, in ordinal order
+    layers: List[int]                           # runs of the schedule that own a layer of this storage, in order
     pool: IndexPool
     pages: Dict[int, List[int]] = field(default_factory=dict)     # slot -> page of each 64-position block (0: none)
     k: Optional[torch.Tensor] = None
@@ -69,7 +69,9 @@ class SequenceCache:
     def __init__(self, layer_specs: Sequence[Optional[CacheSpec]], max_tokens: int, max_seqs: int,
                  kv_dtype: torch.dtype = torch.bfloat16, device="cpu", max_seq_tokens: Optional[int] = None,
                  allocate_storage: bool = True):
-        """`layer_specs[i]` is what layer i's mixer asked for (None: nothing).
+        """`layer_specs[i]` is what the mixer of the i-th run of the model's
+        schedule asked for (None: nothing).  The indices used throughout this class
+        are those run indices.
         `max_tokens` is the most tokens live sequences hold together, each
         sequence's count rounded up to a page; `max_seqs` the most live
         sequences; `max_seq_tokens` the longest single sequence."""

@@ -72,6 +72,9 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.runtime.device)
+
     # ------------------------------------------------------------------- step
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              wants: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:

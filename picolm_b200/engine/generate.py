@@ -87,13 +87,14 @@ def finish_reason(token: int, n_generated: int, max_new: int, stop_ids, length_a
 def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_ids: Optional[Sequence[int]] = None,
              max_batch: Optional[int] = None,
-             on_token: Optional[Callable[[int, int], None]] = None) -> Tuple[List[List[int]], GenerationStats]:
+             on_token: Optional[Callable[[int, int], None]] = None,
+             sampler_factory=None) -> Tuple[List[List[int]], GenerationStats]:
     """Generate up to `max_tokens` new tokens for every prompt (lists of token
     ids).  Returns the new tokens of each prompt, in the prompts' order, and
     timing counters.  `stop_ids` defaults to the model's own end-of-sequence ids;
-    `on_token(request index, token)` is called for every new token."""
-    import torch
-
+    `on_token(request index, token)` is called for every new token.
+    `sampler_factory(params, request indices, device)` replaces the device
+    sampler (tests of the loop's decisions use it)."""
     sampling = sampling or SamplingParams()
     stop = frozenset(engine.model.spec.stop_token_ids if stop_ids is None else stop_ids)
     cache = engine.cache
@@ -118,10 +119,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
         stats.batches += 1
         slots = [engine.new_sequence() for _ in batch]
         try:
-            sampler = Sampler(sampling, [r.index for r in batch], engine.runtime.device)
+            sampler = (sampler_factory or Sampler)(sampling, [r.index for r in batch], engine.runtime.device)
             live = list(range(len(batch)))
             # the prompts, whole, in one step
-            torch.cuda.synchronize()
+            engine.synchronize()
             t0 = time.perf_counter()
             logits = engine.step([(slots[i], batch[i].prompt) for i in live])
             tokens = sampler.sample(logits).tolist()

@@ -75,12 +75,29 @@ class Model:
         return total
 
     # ------------------------------------------------------------------ cache
+    # The cache is kept per *run* of a layer (per entry of the schedule), not per
+    # layer: a layer that the schedule names twice shares its weights between
+    # the two runs, but each run sees other inputs and so has keys, values or
+    # state of its own.  A layer with `cache_of = j` owns nothing: each of its
+    # runs reads what the latest earlier run of layer j wrote.
     def cache_specs(self) -> List[Optional[CacheSpec]]:
-        """What each layer owns in the cache (None: nothing, or another layer's)."""
+        """What each run of the schedule owns in the cache (None: nothing, or
+        another layer's)."""
         out: List[Optional[CacheSpec]] = []
-        for layer, block in zip(self.spec.layers, self.blocks):
-            out.append(None if layer.cache_of is not None else block.mixer.cache_spec())
+        for i in self.spec.schedule:
+            layer = self.spec.layers[i]
+            out.append(None if layer.cache_of is not None else self.blocks[i].mixer.cache_spec())
         return out
+
+    def _cache_source(self, run: int) -> Tuple[int, bool]:
+        """(run whose cache this run uses, whether it may write it)."""
+        layer = self.spec.layers[self.spec.schedule[run]]
+        if layer.cache_of is None:
+            return run, True
+        for r in range(run - 1, -1, -1):
+            if self.spec.schedule[r] == layer.cache_of:
+                return r, False
+        raise ValueError(f"run {run}: layer {layer.cache_of}, whose cache it reads, has not run before it")
 
     def prepare(self, max_seq_tokens: int) -> None:
         for block in self.blocks:
@@ -88,10 +105,8 @@ class Model:
             if prep is not None:
                 prep(max_seq_tokens)
 
-    def layer_cache(self, layer: int, cache: SequenceCache, step):
-        owner = self.spec.layers[layer].cache_of
-        writable = owner is None
-        src = layer if owner is None else owner
+    def layer_cache(self, run: int, cache: SequenceCache, step):
+        src, writable = self._cache_source(run)
         if src in cache.layer_group:
             gi = cache.layer_group[src]
             g = cache.kv_groups[gi]
@@ -106,8 +121,8 @@ class Model:
         """Run the step's tokens through the scheduled layers; returns fp32 logits
         [wanted rows, vocab] (None if no row is wanted)."""
         stream = ResidualStream(self.embedding.forward(step))
-        for i in self.spec.schedule:
-            self.blocks[i].forward(stream, step, self.layer_cache(i, cache, step))
+        for run, i in enumerate(self.spec.schedule):
+            self.blocks[i].forward(stream, step, self.layer_cache(run, cache, step))
         if step.n_want == 0:
             # the last delta need not be added: nothing reads the stream after it
             return None

@@ -148,11 +148,13 @@ def swiglu(gate, up):
 
 
 # ----------------------------------------------------------------- the model
-def forward(cfg, w, tokens, pairing="half", window=None, return_hidden=False, act_dtype=None):
+def forward(cfg, w, tokens, pairing="half", window=None, return_hidden=False, act_dtype=None, kv_dtype=None):
     """Logits [T, vocab] of one whole sequence.  Layer order: picolm/model_core.c:1797-2220.
     `act_dtype=torch.bfloat16` rounds the activations where a bfloat16 run keeps them
     in 16 bits (norm outputs, projections, rotated q/k, v, attention output, the
-    activated branch); the residual stream and its deltas stay float32."""
+    activated branch); the residual stream and its deltas stay float32.
+    `kv_dtype=torch.float16` rounds only the cached keys and values, as the reference
+    does (picolm/model_core.c:1943-1955, :2003-2015)."""
     def rnd(t):
         return t if act_dtype is None else t.to(act_dtype).to(t.dtype)
 
@@ -172,6 +174,8 @@ def forward(cfg, w, tokens, pairing="half", window=None, return_hidden=False, ac
         k = rnd(linear(h, w[p + "self_attn.k_proj.weight"])).reshape(T, G, hd)
         v = rnd(linear(h, w[p + "self_attn.v_proj.weight"])).reshape(T, G, hd)
         q, k = rnd(rope(q, cos, sin, pairing)), rnd(rope(k, cos, sin, pairing))
+        if kv_dtype is not None:
+            k, v = k.to(kv_dtype).to(x.dtype), v.to(kv_dtype).to(x.dtype)
         a = rnd(attention(q, k, v, 1.0 / math.sqrt(hd), window)).reshape(T, H * hd)
         x = x + linear(a, w[p + "self_attn.o_proj.weight"])
         h = rnd(rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps))

@@ -1,0 +1,126 @@
+"""The generation loop's decisions, with a fake engine and sampler (no device):
+which requests form a batch, when a sequence ends, what is fed, that slots come
+back."""
+from types import SimpleNamespace
+
+import pytest
+
+from picolm_b200.cache import CacheSpec, SequenceCache
+from picolm_b200.engine.generate import Request, finish_reason, generate, plan_batch, tokens_reserved
+from picolm_b200.sampling import SamplingParams, stream_seed
+
+
+def test_tokens_reserved_counts_what_is_fed():
+    assert tokens_reserved(5, 8, 1000) == 64            # 5 + 7 fed
+    assert tokens_reserved(60, 5, 1000) == 64           # 60 + 4 = 64
+    assert tokens_reserved(60, 6, 1000) == 128
+    assert tokens_reserved(60, 500, 100) == 128         # capped by the longest sequence
+
+
+def test_plan_batch_takes_requests_in_order_while_they_fit():
+    reqs = [Request(i, [1] * n, 8) for i, n in enumerate([5, 70, 5, 5])]
+    assert [r.index for r in plan_batch(reqs, 64 * 4, 8, 8, 4096)] == [0, 1, 2]
+    assert [r.index for r in plan_batch(reqs, 64 * 4, 2, 8, 4096)] == [0, 1]
+    assert [r.index for r in plan_batch(reqs, 64 * 4, 8, 1, 4096)] == [0]
+    assert [r.index for r in plan_batch(reqs, 64, 8, 8, 4096)] == [0]
+    with pytest.raises(RuntimeError, match="does not fit"):
+        plan_batch(reqs[1:], 64, 8, 8, 4096)
+
+
+def test_finish_reason():
+    assert finish_reason(7, 1, 5, {7}, 10, 100) == "stop"
+    assert finish_reason(3, 5, 5, {7}, 10, 100) == "length"
+    assert finish_reason(3, 2, 5, {7}, 101, 100) == "context"
+    assert finish_reason(3, 2, 5, {7}, 100, 100) is None
+
+
+def test_stream_seed_follows_the_reference():
+    assert stream_seed(42, 0) == 42 and stream_seed(42, 3) == 45
+    assert stream_seed(0, 0) == 42                       # picolm/sampler.c:43: seed 0 reads as 42
+
+
+class FakeEngine:
+    """Counts what the loop feeds; the 'model' continues every sequence with
+    last token + 1 (the fake sampler reads that from the fake logits)."""
+
+    def __init__(self, max_tokens=64 * 6, max_seqs=3, max_seq_tokens=100):
+        self.cache = SequenceCache([CacheSpec.kv(1, 16)], max_tokens, max_seqs, device="cpu",
+                                   max_seq_tokens=max_seq_tokens, allocate_storage=False)
+        self.model = SimpleNamespace(spec=SimpleNamespace(stop_token_ids=(50,)))
+        self.runtime = SimpleNamespace(device="cpu")
+        self.steps = []
+
+    def new_sequence(self):
+        return self.cache.allocate()
+
+    def end_sequence(self, slot):
+        self.cache.release(slot)
+
+    def length(self, slot):
+        return self.cache.length(slot)
+
+    def synchronize(self):
+        pass
+
+    def step(self, entries, wants=None):
+        self.cache.reserve([(s, len(t)) for s, t in entries])
+        for s, t in entries:
+            self.cache.advance(s, len(t))
+        self.steps.append([(s, list(t)) for s, t in entries])
+        return [t[-1] + 1 for _, t in entries]           # "logits": the next token itself
+
+
+class FakeSampler:
+    made = []
+
+    def __init__(self, params, request_indices, device):
+        self.rows = list(request_indices)
+        FakeSampler.made.append(list(request_indices))
+
+    def keep(self, rows):
+        self.rows = [self.rows[r] for r in rows]
+
+    def sample(self, logits):
+        assert len(logits) == len(self.rows)
+        return SimpleNamespace(tolist=lambda: list(logits))
+
+
+def test_loop_batches_stops_and_gives_slots_back():
+    FakeSampler.made.clear()
+    eng = FakeEngine()
+    prompts = [[10, 11, 12], [47], [20] * 40, [30, 31], [48, 49]]
+    outs, stats = generate(eng, prompts, max_tokens=4, sampling=SamplingParams(temperature=0.0),
+                           sampler_factory=FakeSampler)
+    # the fake model counts up from the last prompt token; 50 is the stop token
+    assert outs == [[13, 14, 15, 16], [48, 49, 50], [21, 22, 23, 24], [32, 33, 34, 35], [50]]
+    assert FakeSampler.made == [[0, 1, 2], [3, 4]]       # 3 slots: two batches, requests in order
+    first = eng.steps[0]
+    assert [len(t) for _, t in first] == [3, 1, 40]      # unequal prompts in one step
+    # decode steps feed one token each; the stop token and the last token are never fed
+    fed = [t for step in eng.steps[1:] for _, toks in step for t in toks]
+    assert 50 not in fed and 16 not in fed and 24 not in fed
+    # request 1 ends after 3 tokens: the batch goes on without it
+    assert [len(step) for step in eng.steps[:4]] == [3, 3, 3, 2]
+    assert stats.batches == 2 and stats.generated_tokens == 4 + 3 + 4 + 4 + 1
+    assert stats.prefill_tokens == 3 + 1 + 40 + 2 + 2
+    eng.cache.check()
+    assert eng.cache.slots.used == 0 and eng.cache.kv_groups[0].pool.used == 0
+
+
+def test_loop_stops_at_the_context_limit():
+    eng = FakeEngine(max_seq_tokens=8)
+    outs, _ = generate(eng, [[1, 2, 3, 4, 5, 6]], max_tokens=10, sampling=SamplingParams(temperature=0.0),
+                       sampler_factory=FakeSampler)
+    # 6 prompt tokens + 2 fed = 8 positions; the third new token cannot be fed any more
+    assert outs == [[7, 8, 9]]
+    assert max(eng.cache.lengths.values(), default=0) == 0
+    with pytest.raises(ValueError, match="holds sequences"):
+        generate(eng, [[1] * 9], max_tokens=1, sampler_factory=FakeSampler)
+
+
+def test_zero_new_tokens_and_empty_prompt():
+    eng = FakeEngine()
+    outs, stats = generate(eng, [[1, 2]], max_tokens=0, sampler_factory=FakeSampler)
+    assert outs == [[]] and stats.steps == 0
+    with pytest.raises(ValueError, match="empty"):
+        generate(eng, [[]], max_tokens=1, sampler_factory=FakeSampler)

@@ -1,0 +1,82 @@
+"""Greedy and sampled generation through the Python entry point and the command line."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from plain import llama_plain as P
+from util import TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
+def test_greedy_generation_matches_the_plain_implementation(model_dirs, name):
+    """float32: token for token.  Unequal prompts, more requests than fit one
+    batch (so slots are used again), a stop token that ends one request early."""
+    from picolm_b200.api import generate, model_load
+    cfg, w = P.load_model(model_dirs[name])
+    vocab = TINY[name[0]]["config"]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 50 + i) for i, n in enumerate([5, 11, 17, 1, 40, 3, 64])]
+    free_run = [P.greedy(cfg, w, p, 10) for p in prompts]
+    stop = free_run[2][4]                                       # request 2 meets this token at its 5th step
+    want = [P.greedy(cfg, w, p, 10, stop=(stop,)) for p in prompts]
+    assert len(want[2]) <= 5
+    eng = model_load(model_dirs[name], dtype="float32", max_batch=3)
+    got, stats = generate(eng, prompts, max_tokens=10, temperature=0.0, stop_ids=[stop], return_stats=True)
+    assert got == want
+    assert stats.batches == 3 and eng.cache.slots.used == 0
+    eng.cache.check()
+    # alone or in a batch: the same tokens
+    assert generate(eng, [prompts[1]], max_tokens=10, temperature=0.0, stop_ids=[stop]) == [want[1]]
+
+
+def test_bfloat16_greedy_follows_the_plain_bfloat16_twin(model_dirs):
+    from picolm_b200.api import generate, model_load
+    name = "A_sharp"
+    cfg, w = P.load_model(model_dirs[name])
+    prompts = [random_tokens(n, 256, 70 + i) for i, n in enumerate([9, 30])]
+    eng = model_load(model_dirs[name], dtype="bfloat16", max_batch=2)
+    got = generate(eng, prompts, max_tokens=12, temperature=0.0, stop_ids=[])
+    # every generated token is the argmax of the twin's logits for the sequence so far,
+    # or so close to it that 16-bit rounding decides
+    for p, out in zip(prompts, got):
+        assert len(out) == 12
+        seq = list(p)
+        for tok in out:
+            logits = P.forward(cfg, w, seq, act_dtype=torch.bfloat16)[-1]
+            assert logits[tok] >= logits.max() - 0.05 * logits.std()
+            seq.append(tok)
+
+
+def test_sampling_is_seeded_per_request(model_dirs):
+    """The same seed gives the same tokens; a request's tokens do not depend on
+    its batch (its stream is seeded by its index among the prompts)."""
+    from picolm_b200.api import generate, model_load
+    eng = model_load(model_dirs["B_sharp"], dtype="float32", max_batch=4)
+    prompts = [random_tokens(n, 384, 80 + i) for i, n in enumerate([4, 9, 2, 20])]
+    a = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[])
+    b = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[])
+    c = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=8, stop_ids=[])
+    assert a == b and a != c
+    one_by_one = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[],
+                          max_batch=1)
+    assert one_by_one == a
+
+
+def test_command_line(model_dirs):
+    cfg, w = P.load_model(model_dirs["A_sharp"])
+    want = [P.greedy(cfg, w, p, 5) for p in ([5, 6, 7], [9])]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
+                        "-p", "5,6,7; 9", "-n", "5", "-t", "0", "--dtype", "float32", "--stop-id", "-1"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = [[int(t) for t in ln.split()] for ln in r.stdout.strip().splitlines()]
+    assert lines == want
+    assert "Prefill: 4 tokens" in r.stderr and "Generation: 10 tokens" in r.stderr
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
+                        "--list-tensors"], capture_output=True, text=True, timeout=60)
+    assert "model.layers.1.mlp.down_proj.weight\t[64, 172]\tBF16" in r.stdout

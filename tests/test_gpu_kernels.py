@@ -116,6 +116,7 @@ def test_attention_rows_finds_a_far_key(dtype, H, G, hd):
         k, v = torch.randn(n, G, hd) * 0.3, torch.randn(n, G, hd)
         q = torch.randn(new[b], H, hd) * 0.3
         far = n // 7
+        k[far] *= 3.0                                        # the far key stands out; the others stay small
         for h in range(H):
             q[-1, h] = k[far, h // (H // G)] * (40.0 / (k[far, h // (H // G)].norm() ** 2)) * math.sqrt(hd)
         ks.append(k), vs.append(v), qs.append(q)
