@@ -1,0 +1,283 @@
+#!/usr/bin/env python3
+"""Benchmark of picolm_b200 on one B200: decode tokens/s (the headline, batch 8)
+with its HBM roofline, prefill of 2,048 tokens with its tensor-core fraction,
+decode at batch 1 and 64, and the same decode measured end to end through the
+Python entry point (host token ids in, host token ids out).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  The model has the layer sizes
+of BASELINE.json's configs[2] (Llama-3.2-1B shape) with random weights; every
+timed step reads all weights (2.5 GB, far more than the 126 MB L2), so no L2
+flush is needed between steps.  Prints one JSON line.
+"""
+import argparse
+import json
+import os
+import re
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}     # an earlier measurement on this pool
+
+
+def bench_config():
+    """The sizes of BASELINE.json's configs[2], read from its text."""
+    text = ""
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            text = json.load(f)["configs"][2]
+    except (OSError, KeyError, IndexError, ValueError):
+        pass
+
+    def num(pattern, default):
+        m = re.search(pattern, text)
+        return int(m.group(1).replace(",", "")) if m else default
+
+    cfg = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": num(r"(\d+) layers", 16), "hidden_size": num(r"hidden (\d+)", 2048),
+        "num_attention_heads": num(r"(\d+) heads", 32), "num_key_value_heads": num(r"(\d+) KV heads", 8),
+        "head_dim": num(r"head_dim (\d+)", 64), "intermediate_size": num(r"intermediate (\d+)", 8192),
+        "vocab_size": num(r"vocab (\d+)", 128256), "rope_theta": float(num(r"rope_theta (\d+)", 500000)),
+        "rope_scaling": {"rope_type": "llama3", "factor": float(num(r"factor (\d+)", 32)),
+                         "low_freq_factor": float(num(r"low_freq (\d+)", 1)),
+                         "high_freq_factor": float(num(r"high_freq (\d+)", 4)),
+                         "original_max_position_embeddings": num(r"original (\d+)", 8192)},
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": "tied" in text or not text,
+        "hidden_act": "silu", "bos_token_id": 128000, "eos_token_id": 128001,
+    }
+    m = re.search(r"rms_norm_eps ([0-9.e-]+)", text)
+    if m:
+        cfg["rms_norm_eps"] = float(m.group(1).rstrip("."))
+    return cfg, num(r"context (\d+)", 4096), num(r"prefill at ([\d,]+) tokens", 2048), num(r"seed (\d+)", 2)
+
+
+def peaks():
+    p = dict(FALLBACK_PEAKS)
+    src = "fallback"
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if k in m:
+                p[k] = float(m[k])
+        src = "measured"
+    except (OSError, ValueError):
+        pass
+    return p, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].startswith("Active") for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def reference_arm():
+    """The reference is a C program (Makefile, no Python package): the offline
+    pip install of it fails, and it reads GGUF files with a tokenizer, none of
+    which exist here."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "whoreson/picolm has no setup.py/pyproject.toml: `pip install --no-index "
+                                     "--target baseline/_ref /root/reference` fails (not a Python project)"}))
+    return 0
+
+
+def prefill_flops(cfg, T):
+    d, F, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    H, G, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = 2 * T * d * (H + 2 * G) * hd + 2 * T * H * hd * d + 2 * T * d * 2 * F + 2 * T * F * d
+    attn = 2 * 2 * H * hd * T * (T + 1) // 2                     # causal QK^T and PV
+    return L * (per_layer + attn) + 2 * d * cfg["vocab_size"]    # LM head on the last row only
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 decode points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"picolm_b200 is a one-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from picolm_b200 import ops
+    from picolm_b200.api import generate
+    from picolm_b200.config import config_from_dict
+    from picolm_b200.engine import Engine
+    from picolm_b200.weights import write_random_model
+
+    cfg_dict, context, prefill_tokens, seed = bench_config()
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_dict)
+    pk, pk_src = peaks()
+    torch.cuda.set_device(0)
+    prompt_len = prefill_tokens
+    B = args.batch
+    points_b = [] if args.skip_points else [1, 64]
+    max_b = max([B] + points_b)
+
+    with tempfile.TemporaryDirectory() as tmp:
+        t0 = time.time()
+        write_random_model(cfg, seed, tmp, norm_std=0.0)
+        engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * context, max_seqs=max_b,
+                                    max_seq_tokens=context)
+    print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr)
+    g = torch.Generator().manual_seed(seed)
+    vocab = cfg.vocab_size
+
+    def prompts(n):
+        return [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(n)]
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    # ---------------------------------------------------------------- prefill
+    reps = 5
+    times = []
+    for i in range(args.warmup + reps):
+        p = prompts(1)[0]
+        s = engine.new_sequence()
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        engine.step([(s, p)])
+        b.record()
+        torch.cuda.synchronize()
+        engine.end_sequence(s)
+        if i >= args.warmup:
+            times.append(a.elapsed_time(b))
+    pf_ms = statistics.median(times)
+    flops = prefill_flops(cfg_dict, prefill_tokens)
+    prefill = {"value": round(prefill_tokens / pf_ms * 1e3, 1), "tokens": prefill_tokens, "ms": round(pf_ms, 3),
+               "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ----------------------------------------------------------------- decode
+    def decode_run(batch, steps, warmup, sample_clocks=False):
+        slots = [engine.new_sequence() for _ in range(batch)]
+        ps = prompts(batch)
+        toks = []
+        for lo in range(0, batch, 8):                            # prompts in, eight sequences at a time
+            logits = engine.step([(slots[i], ps[i]) for i in range(lo, min(lo + 8, batch))])
+            toks += ops.argmax(logits).tolist()
+        for _ in range(warmup):
+            toks = ops.argmax(engine.step([(s, [t]) for s, t in zip(slots, toks)])).tolist()
+        n0 = ops.launch_count()
+        a, b = ev(), ev()
+        sampler = ClockSampler() if sample_clocks else None
+        if sampler:
+            sampler.__enter__()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            toks = ops.argmax(engine.step([(s, [t]) for s, t in zip(slots, toks)])).tolist()
+        b.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.__exit__()
+        ms = a.elapsed_time(b) / steps
+        launches = ops.launch_count() - n0
+        ctx_mean = prompt_len + warmup + (steps + 1) / 2.0
+        for s in slots:
+            engine.end_sequence(s)
+        return ms, launches, ctx_mean, (sampler.summary() if sampler else None)
+
+    ms, launches, ctx_mean, clocks = decode_run(B, args.steps, args.warmup, sample_clocks=True)
+    value = B / ms * 1e3
+    w_bytes = engine.model.weight_bytes_per_step()
+    kv_bytes = engine.cache.kv_bytes_per_token() * ctx_mean * B
+    achieved = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
+    points = {}
+    for pb in points_b:
+        pms, _, _, _ = decode_run(pb, min(args.steps, 32), args.warmup)
+        points[f"decode_b{pb}"] = round(pb / pms * 1e3, 1)
+
+    # ------------------------------------------- end to end, host ids in and out
+    gen_new = args.warmup + args.steps
+    ps = prompts(B)
+    generate(engine, ps, max_tokens=4, temperature=0.0, stop_ids=[], max_batch=B)            # warm-up
+    engine.reset_counters()
+    outs, stats = generate(engine, ps, max_tokens=gen_new, temperature=0.0, stop_ids=[], max_batch=B,
+                           return_stats=True)
+    c = engine.counters
+    e2e = {"value": round((stats.generated_tokens - B) / stats.generation_seconds, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": int(c["h2d_bytes"] / max(c["steps"], 1)),
+           "d2h_bytes_per_step": int(c["d2h_bytes"] / max(c["steps"], 1)),
+           "prefill_tokens_per_s": round(stats.prefill_tokens / stats.prefill_seconds, 1)}
+
+    out = {
+        "metric": "decode tokens/s (Llama-3.2-1B shape, bf16, batch 8, 1 B200)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random token ids, random-init weights N(0, 0.02)", "impl": "ours",
+        "config": {"model": "Llama-3.2-1B shape", "layers": cfg.num_hidden_layers, "layers_in_config": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied": cfg.tie_word_embeddings, "global_batch": B, "seq_len": context, "prompt_len": prompt_len,
+                   "prefill_tokens": prefill_tokens, "parallelism": "none (1 GPU)",
+                   "l2": "every step reads all weights (2.5 GB > 126 MB L2); no flush"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,6 +45,16 @@ class Engine:
                                    max_seq_tokens=longest)
         model.prepare(self.cache.max_seq_tokens)
         self.vocab_size = spec.vocab_size
+        self.reset_counters()
+
+    def reset_counters(self) -> None:
+        """Bytes copied between host and device by the steps since the last reset."""
+        self.counters = {"steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+
+    def to_host(self, tokens: torch.Tensor):
+        """Sampled token ids as a host list (one device-to-host copy)."""
+        self.counters["d2h_bytes"] += tokens.numel() * tokens.element_size()
+        return tokens.tolist()
 
     # ----------------------------------------------------------- construction
     @staticmethod
@@ -98,6 +108,8 @@ class Engine:
                                  f"[0, {self.vocab_size})")
         self.cache.reserve([(slot, len(toks)) for slot, toks in entries])
         batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
+        self.counters["steps"] += 1
+        self.counters["h2d_bytes"] += batch.h2d_bytes
         logits = self.model.forward(batch, self.cache)
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))

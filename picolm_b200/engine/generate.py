@@ -84,6 +84,11 @@ def finish_reason(token: int, n_generated: int, max_new: int, stop_ids, length_a
     return None
 
 
+def _to_host(engine, tokens):
+    fetch = getattr(engine, "to_host", None)
+    return fetch(tokens) if fetch is not None else tokens.tolist()
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_ids: Optional[Sequence[int]] = None,
              max_batch: Optional[int] = None,
@@ -125,7 +130,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
             engine.synchronize()
             t0 = time.perf_counter()
             logits = engine.step([(slots[i], batch[i].prompt) for i in live])
-            tokens = sampler.sample(logits).tolist()
+            tokens = _to_host(engine, sampler.sample(logits))
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prefill_tokens += sum(len(r.prompt) for r in batch)
             stats.steps += 1
@@ -149,7 +154,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
                 feed = [(slots[live[row]], [int(tokens[row])]) for row in still]
                 live = [live[row] for row in still]
                 logits = engine.step(feed)
-                tokens = sampler.sample(logits).tolist()
+                tokens = _to_host(engine, sampler.sample(logits))
                 stats.steps += 1
             stats.generation_seconds += time.perf_counter() - t0
         finally:

@@ -30,6 +30,7 @@ class StepBatch:
     want_rows: torch.Tensor               # int32 [n_want] flat token indices
     block_tables: List[torch.Tensor]      # per kv group: int32 [B, pages per sequence]
     seq_slot_long: Optional[torch.Tensor] = None     # int64 [B], for indexing state tensors
+    h2d_bytes: int = 0                    # size of the one host-to-device copy that brought all of the above
 
 
 def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], cache, device) -> StepBatch:
@@ -92,4 +93,5 @@ def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], c
         seq_kv_len=dviews[5], want_rows=dviews[6],
         block_tables=[dviews[7 + gi].view(B, P) for gi in range(n_groups)],
         seq_slot_long=dviews[3].to(torch.int64),
+        h2d_bytes=int(host.nbytes),
     )

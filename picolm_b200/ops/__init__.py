@@ -51,8 +51,19 @@ def _fn(library: str, name: str, extra_flags=()):
     return f
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (one per successful call of
+    an entry point that launches one kernel)."""
+    return _launches
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += kernels
         return
     if code < 0:
         raise KernelError(f"{what}: refused ({_CODES.get(code, code)})")
