@@ -33,6 +33,7 @@ NVCC_FLAGS = [
 LIBRARIES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu"],
     "gemm_simt": ["gemm_simt.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
     "attention_simt": ["attention_simt.cu"],
     "sampling": ["sampling.cu"],
 }
@@ -147,6 +148,13 @@ def compile_library(name: str, extra_flags: Sequence[str] = (), verbose: bool = 
             os.remove(tmp)
         raise BuildError(f"nvcc failed on {name}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
+    prefix = f"libplm_{name.replace('@', '_')}-"
+    for old in os.listdir(build_dir()):                  # builds of older sources
+        if old.startswith(prefix) and old.endswith(".so") and os.path.join(build_dir(), old) != out:
+            try:
+                os.remove(os.path.join(build_dir(), old))
+            except OSError:
+                pass
     _say(f"compiled {name} in {time.time() - t0:.1f} s -> {out}")
     if verbose and log:
         print(log, file=sys.stderr)

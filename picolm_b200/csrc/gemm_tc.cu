@@ -1,0 +1,438 @@
+// out[T, F] = X[T, K] * W[F, K]^T in bfloat16 with fp32 accumulation on the
+// fifth-generation tensor cores: operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma issued by one thread,
+// the accumulator in tensor memory, read back with tcgen05.ld for the epilogue.
+//
+// This is the reference's matmul / matmul_batch, out[b*d + i] = W[i, :] . x[b, :]
+// with W row-major [out_features, in_features] (picolm/tensor.c:1394-1418,
+// picolm/tensor.c:2174), for 16-bit weights (picolm/quant.c:133-153), as one
+// tensor-core kernel.
+//
+// One CTA computes one 128 x BN tile of D = P * Q^T, where P is the operand on
+// the 128 TMEM lanes and Q the operand on the BN accumulator columns:
+//   wide   (T > 64):  P = X (tokens), Q = W (features): BN = 128 or 256
+//   skinny (T <= 64): P = W (features), Q = X (tokens): BN = 16..64, so that a
+//                     decode step streams each weight once with full tiles, and
+//                     K is split over gridDim.z CTAs so that all SMs pull from
+//                     HBM; the fp32 partials go to a workspace and are summed in
+//                     a fixed order by a second kernel.
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the CTA records
+// where in `status`, stops issuing, drains what it has in flight, frees its
+// tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;                  // rows of P per tile (TMEM lanes)
+constexpr int BK = 64;                   // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;   // polls of mbarrier.try_wait before giving up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and records `where`) if the phase did not complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (status) atomicCAS(status, 0, where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
+// (64 elements) with the 128-byte swizzle that TMA wrote: 8-row groups are 1024
+// bytes apart (SBO), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ void store_vec8(T* p, const uint32_t* r);
+template <> __device__ __forceinline__ void store_vec8<float>(float* p, const uint32_t* r) {
+    reinterpret_cast<uint4*>(p)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+    reinterpret_cast<uint4*>(p)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+template <> __device__ __forceinline__ void store_vec8<bf16>(bf16* p, const uint32_t* r) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8); }
+__host__ __device__ constexpr size_t smem_bytes_for(int bn) {
+    return (size_t)stages_for(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+
+// P: [p_rows, K], Q: [q_rows, K], both bf16 K-major, described by the tensor maps.
+// SWAP = false: out[p, q] (tokens on P);  SWAP = true: out[q, p] (tokens on Q).
+// gridDim = (P tiles, Q tiles, K splits).  With more than one split, OutT is
+// float and the CTA writes its partial sum to out + blockIdx.z * split_stride.
+template <int BN, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               OutT* __restrict__ out, int p_rows, int q_rows, int K, long ldo, int kb_per_split, long split_stride,
+               int* __restrict__ status) {
+    constexpr int STAGES = stages_for(BN);
+    constexpr uint32_t P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                       // tiles need 1024-byte alignment
+    const uint32_t p_smem = base, q_smem = base + STAGES * P_BYTES;
+    const uint32_t bars = q_smem + STAGES * Q_BYTES;                     // full[STAGES], empty[STAGES], tmem_full
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tmem_full = bars + 16 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 16 * STAGES + 8 - raw));
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
+    const int n_kb_total = (K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(n_kb_total, kb_begin + kb_per_split);
+    const int n_kb = kb_end - kb_begin;                                  // >= 1 by construction of the grid
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (*(volatile int*)&s_abort) break;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1, status, 1)) { s_abort = 1; break; }
+                mbar_expect_tx(full0 + 8 * s, P_BYTES + Q_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(p_smem + s * P_BYTES, &map_p, full0 + 8 * s, k, p0);
+                tma_load_2d(q_smem + s * Q_BYTES, &map_q, full0 + 8 * s, k, q0);
+                issued = i + 1;
+            }
+            if (*(volatile int*)&s_abort) {
+                // drain: every load this thread issued must land before the CTA's shared memory goes away
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (*(volatile int*)&s_abort) { ok = false; break; }
+                if (!mbar_wait(full0 + 8 * s, phase, status, 2)) { s_abort = 1; ok = false; break; }
+                tc_fence_after();
+                const uint64_t pd = smem_desc_sw128(p_smem + s * P_BYTES);
+                const uint64_t qd = smem_desc_sw128(q_smem + s * Q_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc_mma_bf16(tmem_base, pd + (uint64_t)(k * UMMA_K * 2 / 16), qd + (uint64_t)(k * UMMA_K * 2 / 16),
+                                idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(empty0 + 8 * s);              // the stage is free once these MMAs have read it
+            }
+            tc_commit(tmem_full);                       // arrives when every MMA issued so far is done
+        }
+    } else {
+        // ----------------------------------------------------------- epilogue
+        const int quarter = warp & 3;                   // the TMEM lanes this warp may read
+        const bool ready = mbar_wait(tmem_full, 0, status, 3);
+        if (!ready) s_abort = 1;
+        tc_fence_after();
+        if (ready && !*(volatile int*)&s_abort) {
+            const int p = p0 + quarter * 32 + lane;     // row of P held by this thread
+            OutT* dst = out + (size_t)blockIdx.z * split_stride;
+            constexpr int CHUNK = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += CHUNK) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+                if (CHUNK == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
+                tc_wait_ld();
+                if (!SWAP) {
+                    if (p < p_rows) {
+                        OutT* rowp = dst + (size_t)p * ldo + q0 + c;
+                        const bool vec = (q0 + c + CHUNK <= q_rows) && ((((size_t)p * ldo + q0 + c) * sizeof(OutT)) % 16 == 0);
+                        if (vec) {
+#pragma unroll
+                            for (int j = 0; j < CHUNK; j += 8) store_vec8<OutT>(rowp + j, r + j);
+                        } else {
+                            for (int j = 0; j < CHUNK; ++j)
+                                if (q0 + c + j < q_rows) rowp[j] = from_f32<OutT>(__uint_as_float(r[j]));
+                        }
+                    }
+                } else {
+                    if (p < p_rows) {
+#pragma unroll
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int q = q0 + c + j;   // a token; lanes write consecutive features: coalesced
+                            if (q < q_rows) dst[(size_t)q * ldo + p] = from_f32<OutT>(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        if (*(volatile int*)&s_abort && lane == 0) {
+            // MMAs that were issued still read shared memory and write TMEM: let them finish (bounded)
+            mbar_wait(tmem_full, 0, nullptr, 0);
+        }
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// out[i] = sum over splits of partial[s][i], in ascending s.  VEC: total is a
+// multiple of 4, so every split's slice starts on a 16-byte boundary.
+template <typename OutT, bool VEC>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int splits, size_t total) {
+    if (VEC) {
+        const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+        if (i >= total) return;
+        float4 acc = *reinterpret_cast<const float4*>(partial + i);
+        for (int s = 1; s < splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)s * total + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        out[i] = from_f32<OutT>(acc.x); out[i + 1] = from_f32<OutT>(acc.y);
+        out[i + 2] = from_f32<OutT>(acc.z); out[i + 3] = from_f32<OutT>(acc.w);
+    } else {
+        const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= total) return;
+        float acc = partial[i];
+        for (int s = 1; s < splits; ++s) acc += partial[(size_t)s * total + i];
+        out[i] = from_f32<OutT>(acc);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bf16 row-major matrix with leading dimension ld (elements); boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* ptr, long rows, long K, long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return PLM_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? PLM_OK : PLM_ERR_ALIGN;
+}
+
+template <int BN, bool SWAP, typename OutT>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, OutT* out, int p_rows, int q_rows, int K, long ldo,
+           int splits, int kb_per_split, long split_stride, int* status, cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = smem_bytes_for(BN);
+    auto kern = gemm_tc_kernel<BN, SWAP, OutT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN, splits);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(mp, mq, out, p_rows, q_rows, K, ldo, kb_per_split, split_stride, status);
+    return plm_launch_status();
+}
+
+template <typename OutT>
+int launch_reduce(const float* partial, OutT* out, int splits, size_t total, cudaStream_t stream) {
+    if (total % 4 == 0) {
+        const size_t threads = total / 4;
+        splitk_reduce_kernel<OutT, true><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(partial, out, splits, total);
+    } else {
+        splitk_reduce_kernel<OutT, false><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(partial, out, splits, total);
+    }
+    return plm_launch_status();
+}
+
+}  // namespace
+
+// Whether plm_gemm_tc takes this problem: bf16 operands whose rows start on
+// 16-byte boundaries (TMA's rule: K and the leading dimensions are multiples of 8
+// elements, the base pointers 16-byte aligned).
+extern "C" int plm_gemm_tc_supported(const void* x, const void* w, int T, int F, int K, long ldx, long ldw) {
+    if (T <= 0 || F <= 0 || K <= 0) return 0;
+    if (K % 8 || ldx % 8 || ldw % 8) return 0;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return 0;
+    return 1;
+}
+
+// Number of K splits and fp32 workspace elements that plm_gemm_tc will use for a
+// problem (1 and 0 for the wide path).  Fixed by (T, F, K) alone.
+extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* workspace_elems) {
+    int splits = 1;
+    if (T <= 64) {
+        const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+        const int tiles = ((F + BM - 1) / BM) * ((T + bn - 1) / bn);
+        const int n_kb = (K + BK - 1) / BK;
+        int want = (2 * 148 + tiles - 1) / tiles;              // about two CTAs per SM
+        if (want > n_kb / 2) want = n_kb / 2;                  // at least two K blocks per split
+        if (want < 1) want = 1;
+        const int per = (n_kb + want - 1) / want;
+        splits = (n_kb + per - 1) / per;
+    }
+    *splits_out = splits;
+    *workspace_elems = splits > 1 ? (long)splits * T * F : 0;
+    return PLM_OK;
+}
+
+// out[T, F] (out_dtype, leading dimension ldo) = x[T, K] * w[F, K]^T.
+// `workspace` must hold the elements that plm_gemm_tc_plan reports; `status` is
+// a device int that is 0 unless a bounded wait ran out (then 1, 2 or 3: producer,
+// MMA issuer, epilogue).
+extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int T, int F, int K, long ldx,
+                           long ldw, long ldo, float* workspace, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (!plm_gemm_tc_supported(x, w, T, F, K, ldx, ldw)) return PLM_ERR_ALIGN;
+    if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    CUtensorMap mp, mq;
+    int rc;
+    if (T > 64) {
+        const int bn = (F >= 2048 && T >= 256) ? 256 : 128;
+        if ((rc = make_map(&mp, x, T, K, ldx, BM)) != PLM_OK) return rc;
+        if ((rc = make_map(&mq, w, F, K, ldw, bn)) != PLM_OK) return rc;
+        const int n_kb = (K + BK - 1) / BK;
+        if (bn == 256) {
+            return out_dtype == PLM_F32
+                ? launch<256, false, float>(mp, mq, (float*)out, T, F, K, ldo, 1, n_kb, 0, status, stream)
+                : launch<256, false, bf16>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
+        }
+        return out_dtype == PLM_F32
+            ? launch<128, false, float>(mp, mq, (float*)out, T, F, K, ldo, 1, n_kb, 0, status, stream)
+            : launch<128, false, bf16>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
+    }
+    // skinny: weights on the TMEM lanes, tokens on the accumulator columns
+    int splits;
+    long ws_elems;
+    plm_gemm_tc_plan(T, F, K, &splits, &ws_elems);
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    const int n_kb = (K + BK - 1) / BK;
+    const int per = (n_kb + splits - 1) / splits;
+    if ((rc = make_map(&mp, w, F, K, ldw, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mq, x, T, K, ldx, bn)) != PLM_OK) return rc;
+    if (splits > 1) {
+        if (!workspace) return PLM_ERR_SHAPE;
+        const long stride = (long)T * F;
+        if (ldo != F) return PLM_ERR_SHAPE;
+        if (bn == 16) rc = launch<16, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        else if (bn == 32) rc = launch<32, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        else rc = launch<64, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        if (rc != PLM_OK) return rc;
+        return out_dtype == PLM_F32 ? launch_reduce<float>(workspace, (float*)out, splits, (size_t)stride, stream)
+                                    : launch_reduce<bf16>(workspace, (bf16*)out, splits, (size_t)stride, stream);
+    }
+    if (out_dtype == PLM_F32) {
+        if (bn == 16) return launch<16, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+        if (bn == 32) return launch<32, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+        return launch<64, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    }
+    if (bn == 16) return launch<16, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    if (bn == 32) return launch<32, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    return launch<64, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+}

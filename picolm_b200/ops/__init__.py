@@ -24,6 +24,9 @@ _SIGNATURES = {
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
+    "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
+    "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
+    "plm_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _l, _l],
     "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
@@ -207,6 +210,66 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device int that kernels with bounded waits write to when a wait runs
+    out (0: all well).  One per device."""
+    key = torch.device(device)
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=key)
+        _status[key] = t
+    return t
+
+
+def check_status(device="cuda:0") -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (this
+    synchronises with the device)."""
+    t = _status.get(torch.device(device))
+    if t is None:
+        return
+    code = int(t.item())
+    if code:
+        t.zero_()
+        where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
+        raise KernelError(f"a tensor-core kernel gave up waiting on an mbarrier ({where}); its output is not valid")
+
+
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes a @ w^T: both bfloat16, K a multiple of
+    8 (rows start on 16-byte boundaries, as TMA needs) and at least one K block."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    (M, K), (N, K2) = a.shape, w.shape
+    if K != K2 or K < 64:
+        return False
+    return bool(_fn("gemm_tc", "plm_gemm_tc_supported")(_p(a), _p(w), M, N, K, K, K))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bf16 in, fp32
+    accumulate).  With M <= 64 the weights take the 128-row side of the MMA and K
+    is split; the fp32 partial sums pass through a scratch buffer."""
+    _dev(a, "a"), _dev(w, "w")
+    if not gemm_tc_supported(a, w):
+        raise KernelError(f"gemm_tc: a {tuple(a.shape)} {a.dtype} @ w {tuple(w.shape)} {w.dtype} is not supported "
+                          f"(bfloat16, K a multiple of 8 and >= 64, 16-byte aligned)")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    splits, ws_elems = ctypes.c_int(0), ctypes.c_long(0)
+    _fn("gemm_tc", "plm_gemm_tc_plan")(M, N, K, ctypes.byref(splits), ctypes.byref(ws_elems))
+    ws = torch.empty((ws_elems.value,), dtype=torch.float32, device=a.device) if ws_elems.value else None
+    _check(_fn("gemm_tc", "plm_gemm_tc")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), M, N, K, K, K, N, _p(ws), _p(status_word(a.device)), _stream()),
+        "gemm_tc", kernels=2 if ws is not None else 1)
+    return out
+
+
 # ------------------------------------------------------------------ attention
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                    tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
@@ -263,6 +326,8 @@ def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, to
 def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
     types and shape, never by the model."""
+    if gemm_tc_supported(a, w):
+        return gemm_tc(a, w, out_dtype)
     return gemm_simt(a, w, out_dtype)
 
 

@@ -269,3 +269,46 @@ def test_sample_distribution():
     p = torch.softmax(logits[0].double() / 0.7, dim=0)
     chi2 = (n * (freq - p) ** 2 / p).sum().item()
     assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [
+    (1, 128, 64), (8, 3072, 2048), (16, 200, 264), (17, 256, 512), (33, 130, 1024), (64, 2048, 8192),
+    (65, 128, 64), (128, 128, 128), (200, 136, 328), (300, 2048, 192), (256, 4096, 512), (1000, 264, 2048)])
+def test_gemm_tc(out_dtype, M, N, K):
+    """The tcgen05 kernel against a float64 product of the same bf16 inputs: the
+    skinny path (weights on the MMA's 128 rows, K split, partials reduced) and the
+    wide path with both tile widths, ragged edges in every dimension, K tails that
+    are no multiple of the 64-wide stage."""
+    from picolm_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    # structure that a transposed, shifted or partly skipped tile cannot reproduce
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    ref = a.double() @ w.double().t()
+    assert ops.gemm_tc_supported(a.to(DEV), w.to(DEV))
+    out = ops.gemm_tc(a.to(DEV), w.to(DEV), DT[out_dtype])
+    ops.check_status(DEV)
+    assert out.dtype == DT[out_dtype] and out.shape == (M, N)
+    got = out.double().cpu()
+    if out_dtype == "float32":
+        assert torch.allclose(got, ref, atol=2e-3, rtol=1e-4)          # fp32 accumulation of exact bf16 products
+    else:
+        assert torch.allclose(got, ref, atol=2e-2, rtol=1e-2)
+    # the same rows in a bigger batch give the same values (beyond rounding)
+    simt = ops.gemm_simt(a.to(DEV), w.to(DEV), torch.float32).double().cpu()
+    assert torch.allclose(simt, ref, atol=2e-3, rtol=1e-4)
+
+
+def test_gemm_tc_refuses_what_tma_cannot_address():
+    from picolm_b200 import ops
+    a = torch.zeros(4, 172, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 172, dtype=torch.bfloat16, device=DEV)
+    assert not ops.gemm_tc_supported(a, w)                             # rows of 344 bytes: not 16-byte aligned
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.gemm_tc(a, w, torch.float32)
+    assert not ops.gemm_tc_supported(a.float(), w.float())
+    out = ops.linear(a, w, torch.float32)                              # the dispatcher falls to the any-size kernel
+    assert out.shape == (4, 64)
