@@ -1,0 +1,493 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync
+// m16n8k16, fp32 accumulation, fp32 softmax statistics), compiled for one head
+// size: -DPLM_HD=<head_dim>, a multiple of 16 up to 256.
+//
+// For a query at position p, head h, KV head g = h / (H/G):
+//   s_t = (q_h . K[t, g]) * scale for lo <= t <= p;  out_h = softmax(s) . V[:, g]
+// with the running (max, sum, acc) recurrence of the reference's attn_core
+// (picolm/model_attention.c:43-140) applied to 64 keys (prefill) or 16 keys
+// (decode) at a time, and the reference's idea of serving all H/G query heads of
+// a KV head from one pass over its keys (picolm/model_attention.c:142-150).
+//
+// Two kernels:
+//   prefill  one CTA per (sequence, KV head, tile of 64 query rows); a row is a
+//            (token, head-in-group) pair, so the heads of a group share every
+//            K/V page that is loaded.  Causal, ragged over sequences.
+//   decode   one CTA per (token, KV head x row group, split of the keys): the
+//            splits' partial (max, sum, acc) go to a workspace and a small kernel
+//            merges them with exp(m_i - m) weights, as the reference's split
+//            kernel does (picolm/backend_gpu_kernels.cu:802, :911).
+// K and V pages are [64 keys][HD] contiguous in the cache; they are copied to
+// shared memory with cp.async (rows padded by 16 bytes so that ldmatrix has no
+// bank conflicts) in a multi-stage ring.
+#include "common.cuh"
+
+#ifndef PLM_HD
+#define PLM_HD 64
+#endif
+
+namespace {
+
+constexpr int HD = PLM_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head_dim must be a multiple of 16 up to 256");
+constexpr int LDS = HD + 8;                 // padded row length in elements
+constexpr int TILE_ELEMS = 64 * LDS;        // one 64-row tile
+constexpr int NT = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// 16 bytes if `full`, else zeros (the source is not read)
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool full) {
+    const int n = full ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Copy one page tile (64 rows of HD bf16, contiguous in global memory) into a padded smem tile.
+// Rows at and beyond `valid` (places of the page that hold no key yet) are filled with zeros, so
+// that whatever an earlier owner of the page left there cannot reach a sum.
+__device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, int valid) {
+    constexpr int CPR = HD / 8;             // 16-byte chunks per row
+    for (int c = threadIdx.x; c < 64 * CPR; c += NT) {
+        const int row = c / CPR, col = c - row * CPR;
+        cp_async16_zfill(smem_u32(dst + row * LDS + col * 8), src + row * HD + col * 8, row < valid);
+    }
+}
+
+// S[16 x 8*NKT] += Q[16 x HD] . K^T for keys [key0, key0 + 8*NKT) of a tile; q_rows points at the
+// warp's 16 query rows in shared memory.
+template <int NKT>
+__device__ __forceinline__ void qk_tile(float (&s)[NKT][4], const bf16* q_rows, const bf16* k_tile, int key0, int lane) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t a[4];
+        ldsm_x4(a, smem_u32(q_rows + (lane & 15) * LDS + ks * 16 + (lane >> 4) * 8));
+#pragma unroll
+        for (int j = 0; j < NKT; j += 2) {
+            uint32_t b[4];
+            const int key = key0 + j * 8 + (lane & 7) + (lane >> 4) * 8;
+            ldsm_x4(b, smem_u32(k_tile + key * LDS + ks * 16 + ((lane >> 3) & 1) * 8));
+            mma_bf16(s[j], a, b[0], b[1]);
+            mma_bf16(s[j + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x HD] += P[16 x 8*NKT] . V for keys [key0, key0 + 8*NKT) of a tile; P comes from the score
+// accumulators (already exponentiated), repacked as the A operand.
+template <int NKT>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[NKT][4], const bf16* v_tile, int key0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NKT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+        a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+        a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+        a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+        const int key = key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; dt += 2) {
+            uint32_t b[4];
+            ldsm_x4_t(b, smem_u32(v_tile + key * LDS + dt * 8 + (lane >> 4) * 8));
+            mma_bf16(o[dt], a, b[0], b[1]);
+            mma_bf16(o[dt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Scale, mask and fold one block of scores into the running softmax of the thread's two rows
+// (row_lo = lane/4, row_hi = lane/4 + 8).  Scores become probabilities in place.
+// key_base: position of the block's first key; pos_*: each row's own position (keys above it are
+// masked); lo_*: first key each row may see.
+template <int NKT>
+__device__ __forceinline__ void softmax_block(float (&s)[NKT][4], float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
+                                              float scale_log2, int key_base, int pos_lo, int pos_hi, int lo_lo,
+                                              int lo_hi, int lane) {
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NKT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
+            const int hi = e >> 1;
+            const bool ok = hi ? (key <= pos_hi && key >= lo_hi) : (key <= pos_lo && key >= lo_lo);
+            const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+            s[j][e] = v;
+            mx[hi] = fmaxf(mx[hi], v);
+        }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+        mx[hi] = fmaxf(mx[hi], __shfl_xor_sync(0xffffffffu, mx[hi], 1));
+        mx[hi] = fmaxf(mx[hi], __shfl_xor_sync(0xffffffffu, mx[hi], 2));
+        const float m_new = fmaxf(m[hi], mx[hi]);
+        m_use[hi] = (m_new == -INFINITY) ? 0.f : m_new;         // a row that has seen no key yet
+        alpha[hi] = exp2f(m[hi] - m_use[hi]);                    // m = -inf gives 0
+        m[hi] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NKT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[j][e] - m_use[e >> 1]);
+            s[j][e] = p;
+            sum[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+        sum[hi] += __shfl_xor_sync(0xffffffffu, sum[hi], 1);
+        sum[hi] += __shfl_xor_sync(0xffffffffu, sum[hi], 2);
+        l[hi] = l[hi] * alpha[hi] + sum[hi];
+    }
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; ++dt) {
+        o[dt][0] *= alpha[0]; o[dt][1] *= alpha[0];
+        o[dt][2] *= alpha[1]; o[dt][3] *= alpha[1];
+    }
+}
+
+// ------------------------------------------------------------------- prefill
+constexpr int PF_STAGES = 2;
+constexpr size_t PF_SMEM = (size_t)(1 + 2 * PF_STAGES) * TILE_ELEMS * sizeof(bf16);
+
+__global__ void __launch_bounds__(NT)
+attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                    bf16* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_kv_len,
+                    const int* __restrict__ block_table, int max_pages, int H, int G, float scale_log2, int window) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_s = q_s + TILE_ELEMS;                     // [PF_STAGES][64][LDS]
+    bf16* v_s = k_s + PF_STAGES * TILE_ELEMS;
+    const int b = blockIdx.z, g = blockIdx.y;
+    const int R = H / G;
+    const int t0 = seq_start[b], n_new = seq_start[b + 1] - t0;
+    const int rows_total = n_new * R;
+    const int n_tiles = (rows_total + 63) / 64;
+    if ((int)blockIdx.x >= n_tiles) return;
+    const int tile = n_tiles - 1 - blockIdx.x;        // the longest tiles first
+    const int row0 = tile * 64;
+    const int kv_len = seq_kv_len[b];
+    const int pos0 = kv_len - n_new;                  // position of the sequence's first new token
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* pages = block_table + (size_t)b * max_pages;
+
+    // the tile's query rows: row -> (token = row / R, head = g*R + row % R)
+    {
+        constexpr int CPR = HD / 8;
+        for (int c = threadIdx.x; c < 64 * CPR; c += NT) {
+            const int lr = c / CPR, col = c - lr * CPR;
+            const int grow = row0 + lr;
+            bf16* dst = q_s + lr * LDS + col * 8;
+            if (grow < rows_total) {
+                const int tok = grow / R, r = grow - tok * R;
+                cp_async16(smem_u32(dst), q + ((size_t)(t0 + tok) * H + g * R + r) * HD + col * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+    const int last_row = min(rows_total, row0 + 64) - 1;
+    const int pos_min = pos0 + row0 / R, pos_max = pos0 + last_row / R;
+    const int first_key = (window > 0 && pos_min - window + 1 > 0) ? pos_min - window + 1 : 0;
+    const int page_first = first_key / PLM_PAGE, page_last = pos_max / PLM_PAGE;
+    const int n_pages = page_last - page_first + 1;
+
+    auto issue = [&](int i) {                          // page i of this tile's range into stage i % PF_STAGES
+        const size_t base = ((size_t)pages[page_first + i] * G + g) * PLM_PAGE * HD;
+        const int valid = kv_len - (page_first + i) * PLM_PAGE;
+        load_tile(k_s + (i % PF_STAGES) * TILE_ELEMS, kc + base, valid);
+        load_tile(v_s + (i % PF_STAGES) * TILE_ELEMS, vc + base, valid);
+    };
+    issue(0);
+    cp_commit();
+
+    // this thread's two rows
+    const int r_lo = row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int pos_lo = r_lo < rows_total ? pos0 + r_lo / R : -1;
+    const int pos_hi = r_hi < rows_total ? pos0 + r_hi / R : -1;
+    const int lo_lo = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+    const int lo_hi = (window > 0 && pos_hi - window + 1 > 0) ? pos_hi - window + 1 : 0;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int i = 0; i < n_pages; ++i) {
+        if (i + 1 < n_pages) issue(i + 1);
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();
+        const bf16* kt = k_s + (i % PF_STAGES) * TILE_ELEMS;
+        const bf16* vt = v_s + (i % PF_STAGES) * TILE_ELEMS;
+        const int key_base = (page_first + i) * PLM_PAGE;
+        // a warp whose rows all lie before this page has nothing to do here (causal)
+        const int warp_pos_max = pos0 + min(last_row, row0 + warp * 16 + 15) / R;
+        if (key_base <= warp_pos_max && row0 + warp * 16 < rows_total) {
+            float s[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            qk_tile<8>(s, q_s + warp * 16 * LDS, kt, 0, lane);
+            softmax_block<8>(s, o, m, l, scale_log2, key_base, pos_lo, pos_hi, lo_lo, lo_hi, lane);
+            pv_tile<8>(o, s, vt, 0, lane);
+        }
+        __syncthreads();                               // the stage may be overwritten by the next issue
+    }
+    cp_wait<0>();
+
+    const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+        const int grow = hi ? r_hi : r_lo;
+        if (grow >= rows_total) continue;
+        const int tok = grow / R, r = grow - tok * R;
+        bf16* dst = out + ((size_t)(t0 + tok) * H + g * R + r) * HD + (lane & 3) * 2;
+        const float inv = hi ? inv_hi : inv_lo;
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; ++dt)
+            *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack_bf16(o[dt][2 * hi] * inv, o[dt][2 * hi + 1] * inv);
+    }
+}
+
+// -------------------------------------------------------------------- decode
+constexpr int DC_STAGES = 3;
+constexpr size_t DC_TILES_BYTES = (size_t)(2 * DC_STAGES) * TILE_ELEMS * sizeof(bf16);
+constexpr size_t DC_Q_BYTES = (size_t)16 * LDS * sizeof(bf16);
+constexpr size_t DC_MERGE_BYTES = (size_t)4 * 16 * (HD + 2) * sizeof(float);
+constexpr size_t DC_SMEM = DC_Q_BYTES + (DC_TILES_BYTES > DC_MERGE_BYTES ? DC_TILES_BYTES : DC_MERGE_BYTES);
+
+// grid = (splits, G * row_groups, tokens).  ws_o [tokens*H, splits, HD] and ws_ml [tokens*H, splits, 2]
+// receive the partial results when splits > 1; with one split the output is written directly.
+__global__ void __launch_bounds__(NT)
+attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                   bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
+                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                   int max_pages, int H, int G, float scale_log2, int window, int row_groups) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw + DC_Q_BYTES);
+    bf16* v_s = k_s + DC_STAGES * TILE_ELEMS;
+    float* merge = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES);      // reused after the last tile
+    const int n_splits = gridDim.x, split = blockIdx.x;
+    const int g = blockIdx.y / row_groups, rg = blockIdx.y - g * row_groups;
+    const int t = blockIdx.z;
+    const int R = H / G;
+    const int h0 = g * R + rg * 16;                     // first head of this row group
+    const int n_rows = min(16, R - rg * 16);
+    const int pos = tok_pos[t];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int page_first = lo / PLM_PAGE, page_last = pos / PLM_PAGE;
+    const int total_pages = page_last - page_first + 1;
+    const int per = (total_pages + n_splits - 1) / n_splits;
+    const int p_begin = page_first + split * per;
+    const int p_end = min(page_last + 1, p_begin + per);
+    const int n_pages = p_end - p_begin;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
+
+    if (n_pages <= 0) {                                 // an empty split: weight zero in the merge
+        for (int r = threadIdx.x; r < n_rows; r += NT) {
+            float* ml = ws_ml + (((size_t)t * H + h0 + r) * n_splits + split) * 2;
+            ml[0] = -INFINITY; ml[1] = 0.f;
+        }
+        return;
+    }
+    {
+        constexpr int CPR = HD / 8;
+        for (int c = threadIdx.x; c < 16 * CPR; c += NT) {
+            const int r = c / CPR, col = c - r * CPR;
+            bf16* dst = q_s + r * LDS + col * 8;
+            if (r < n_rows) cp_async16(smem_u32(dst), q + ((size_t)t * H + h0 + r) * HD + col * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    auto issue = [&](int i) {
+        const size_t base = ((size_t)pages[p_begin + i] * G + g) * PLM_PAGE * HD;
+        const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
+        load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
+        load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
+    };
+#pragma unroll
+    for (int i = 0; i < DC_STAGES - 1; ++i) {
+        if (i < n_pages) issue(i);
+        cp_commit();
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int i = 0; i < n_pages; ++i) {
+        if (i + DC_STAGES - 1 < n_pages) issue(i + DC_STAGES - 1);
+        cp_commit();
+        cp_wait<DC_STAGES - 1>();
+        __syncthreads();
+        const bf16* kt = k_s + (i % DC_STAGES) * TILE_ELEMS;
+        const bf16* vt = v_s + (i % DC_STAGES) * TILE_ELEMS;
+        const int key_base = (p_begin + i) * PLM_PAGE + warp * 16;       // this warp's 16 keys of the page
+        if (key_base <= pos) {
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            qk_tile<2>(s, q_s, kt, warp * 16, lane);
+            softmax_block<2>(s, o, m, l, scale_log2, key_base, pos, pos, lo, lo, lane);
+            pv_tile<2>(o, s, vt, warp * 16, lane);
+        }
+        __syncthreads();
+    }
+    cp_wait<0>();
+    __syncthreads();
+
+    // merge the four warps' partial results: merge[w][row][0..HD) = acc, [HD] = m, [HD+1] = l
+    {
+        float* mine = merge + (size_t)warp * 16 * (HD + 2);
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            const int r = (lane >> 2) + hi * 8;
+#pragma unroll
+            for (int dt = 0; dt < HD / 8; ++dt) {
+                mine[r * (HD + 2) + dt * 8 + (lane & 3) * 2] = o[dt][2 * hi];
+                mine[r * (HD + 2) + dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * hi + 1];
+            }
+            if ((lane & 3) == 0) {
+                mine[r * (HD + 2) + HD] = m[hi];
+                mine[r * (HD + 2) + HD + 1] = l[hi];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rows * HD; idx += NT) {
+        const int r = idx / HD, d = idx - r * HD;
+        float mw[4], mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            mw[w] = merge[((size_t)w * 16 + r) * (HD + 2) + HD];
+            mm = fmaxf(mm, mw[w]);
+        }
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mm);
+            acc += wgt * merge[((size_t)w * 16 + r) * (HD + 2) + d];
+            ll += wgt * merge[((size_t)w * 16 + r) * (HD + 2) + HD + 1];
+        }
+        const size_t row = (size_t)t * H + h0 + r;
+        if (n_splits == 1) {
+            out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        } else {
+            ws_o[(row * n_splits + split) * HD + d] = acc;
+            if (d == 0) {
+                ws_ml[(row * n_splits + split) * 2] = mm;
+                ws_ml[(row * n_splits + split) * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// out[row, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp2(m_s - max m): one block per (token, head).
+__global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                  bf16* __restrict__ out, int n_splits) {
+    const size_t row = blockIdx.x;
+    float mm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, ws_ml[(row * n_splits + s) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f, ll = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = ws_ml[(row * n_splits + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float wgt = exp2f(ms - mm);
+            acc += wgt * ws_o[(row * n_splits + s) * HD + d];
+            ll += wgt * ws_ml[(row * n_splits + s) * 2 + 1];
+        }
+        out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    }
+}
+
+template <typename K>
+int set_smem(K kern, size_t bytes) {
+    if (bytes <= 48 * 1024) return PLM_OK;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    return e == cudaSuccess ? PLM_OK : (int)e;
+}
+
+}  // namespace
+
+extern "C" int plm_attn_head_dim() { return HD; }
+
+// Prefill: q [T, H, HD], out [T, H*HD]; the step's sequences are described by seq_start [B+1]
+// (offsets of each sequence's new tokens) and seq_kv_len [B] (length after the step);
+// max_new is the largest number of new tokens of a sequence.
+extern "C" int plm_attn_prefill(const void* q, const void* kc, const void* vc, void* out, const int* seq_start,
+                                const int* seq_kv_len, const int* block_table, int max_pages, int n_seqs, int max_new,
+                                int H, int G, float scale, int window, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || H % G || n_seqs > 65535 || G > 65535) return PLM_ERR_SHAPE;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(attn_prefill_kernel, PF_SMEM);
+        if (rc != PLM_OK) return rc;
+        configured = true;
+    }
+    const int R = H / G;
+    dim3 grid(((size_t)max_new * R + 63) / 64, G, n_seqs);
+    attn_prefill_kernel<<<grid, NT, PF_SMEM, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
+                                                       seq_start, seq_kv_len, block_table, max_pages, H, G,
+                                                       scale * LOG2E, window);
+    return plm_launch_status();
+}
+
+// Floats of workspace that plm_attn_decode needs for (tokens, H, splits): acc then (m, l).
+extern "C" long plm_attn_decode_workspace(int n_tokens, int H, int n_splits) {
+    return n_splits > 1 ? (long)n_tokens * H * n_splits * (HD + 2) : 0;
+}
+
+// Decode: one query token per row of q [T, H, HD], at position tok_pos[t] of sequence tok_seq[t].
+extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, void* out, float* workspace,
+                               const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
+                               int n_tokens, int H, int G, float scale, int window, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535) return PLM_ERR_SHAPE;
+    if (n_splits > 1 && !workspace) return PLM_ERR_SHAPE;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(attn_decode_kernel, DC_SMEM);
+        if (rc != PLM_OK) return rc;
+        configured = true;
+    }
+    const int R = H / G, row_groups = (R + 15) / 16;
+    if (G * row_groups > 65535) return PLM_ERR_SHAPE;
+    float* ws_o = workspace;
+    float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
+    dim3 grid(n_splits, G * row_groups, n_tokens);
+    attn_decode_kernel<<<grid, NT, DC_SMEM, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o,
+                                                      ws_ml, tok_pos, tok_seq, block_table, max_pages, H, G,
+                                                      scale * LOG2E, window, row_groups);
+    int rc = plm_launch_status();
+    if (rc != PLM_OK || n_splits == 1) return rc;
+    attn_merge_kernel<<<n_tokens * H, HD < 64 ? 32 : 64, 0, stream>>>(ws_o, ws_ml, (bf16*)out, n_splits);
+    return plm_launch_status();
+}

@@ -35,9 +35,21 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_simt": ["gemm_simt.cu"],
     "gemm_tc": ["gemm_tc.cu"],
     "attention_simt": ["attention_simt.cu"],
+    "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh"]
+
+# Libraries that are specialised at compile time.  At run time only the variant a
+# model needs is built (`attention_variant`); the build check builds these.
+VARIANTS: Dict[str, Dict[str, List[str]]] = {
+    "attention_mma": {f"hd{hd}": [f"-DPLM_HD={hd}"] for hd in (64, 128)},
+}
+
+
+def attention_variant(head_dim: int):
+    """(library name, extra flags) of the tensor-core attention for a head size."""
+    return f"attention_mma@hd{head_dim}", [f"-DPLM_HD={head_dim}"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -182,6 +194,16 @@ def load_library(name: str, extra_flags: Sequence[str] = ()) -> ctypes.CDLL:
 def build_all(names: Optional[Iterable[str]] = None, jobs: int = 4, verbose: bool = False) -> List[str]:
     """Compile every library (in parallel); used by the build check."""
     from concurrent.futures import ThreadPoolExecutor
-    names = list(names or LIBRARIES)
+    if names is None:
+        names = [n for n in LIBRARIES if n not in VARIANTS]
+        for base, variants in VARIANTS.items():
+            names += [f"{base}@{v}" for v in variants]
+    names = list(names)
+
+    def one(n):
+        base, _, variant = n.partition("@")
+        flags = VARIANTS[base][variant] if variant else ()
+        return compile_library(n, flags, verbose=verbose)
+
     with ThreadPoolExecutor(max_workers=jobs) as pool:
-        return list(pool.map(lambda n: compile_library(n, verbose=verbose), names))
+        return list(pool.map(one, names))

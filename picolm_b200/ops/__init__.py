@@ -10,7 +10,7 @@ from typing import Optional
 
 import torch
 
-from ..csrc.build import load_library
+from ..csrc.build import attention_variant, load_library
 
 PAGE_TOKENS = 64            # tokens per cache page; PLM_PAGE in csrc/common.cuh
 
@@ -28,6 +28,8 @@ _SIGNATURES = {
     "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
     "plm_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _l, _l],
     "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
 }
@@ -291,6 +293,73 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     return out
 
 
+def attention_mma_supported(q: torch.Tensor) -> bool:
+    """The tensor-core attention takes bfloat16 and head sizes that are multiples of 16 up to 256."""
+    hd = q.shape[-1]
+    return q.dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 256
+
+
+def _attn_check(q, k_cache, v_cache, num_kv_heads):
+    _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
+    T, H, hd = q.shape
+    if not attention_mma_supported(q):
+        raise KernelError(f"attention: {q.dtype} with head_dim {hd} is not supported by the tensor-core kernel "
+                          f"(bfloat16, head_dim a multiple of 16 up to 256)")
+    if k_cache.dtype != q.dtype or k_cache.shape[1:] != (num_kv_heads, PAGE_TOKENS, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"attention: the cache must be [pages, {num_kv_heads}, {PAGE_TOKENS}, {hd}] of {q.dtype}")
+    if H % num_kv_heads:
+        raise KernelError("attention: the number of heads is not a multiple of the number of KV heads")
+    return T, H, hd
+
+
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
+                      seq_kv_len: torch.Tensor, block_table: torch.Tensor, max_new: int, num_kv_heads: int,
+                      scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q [T, H, hd])
+    over its keys 0..seq_kv_len[b]-1 in the paged cache; returns [T, H*hd]."""
+    T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
+    _i32(seq_start, "seq_start"), _i32(seq_kv_len, "seq_kv_len"), _i32(block_table, "block_table")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    lib, flags = attention_variant(hd)
+    _check(_fn(lib, "plm_attn_prefill", flags)(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
+        block_table.shape[1], seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale), int(window or 0),
+        _stream()), "attention_prefill")
+    return out
+
+
+_SM_COUNT = 148
+
+
+def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Into how many ranges the decode kernel cuts each sequence's keys: enough
+    CTAs to keep every SM pulling from HBM, at least one page per range."""
+    row_groups = (num_heads // num_kv_heads + 15) // 16
+    ctas = max(1, n_tokens * num_kv_heads * row_groups)
+    pages = max(1, (max_kv_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
+    return max(1, min(pages, (4 * _SM_COUNT + ctas - 1) // ctas))
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
+                     tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
+                     n_splits: int, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of single query tokens (one per row of q [T, H, hd], at position tok_pos[t] of sequence
+    tok_seq[t]) over the paged cache, the keys of each cut into `n_splits` ranges whose partial results pass
+    through a scratch buffer; returns [T, H*hd]."""
+    T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
+    _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=q.device) if n_splits > 1 else None
+    lib, flags = attention_variant(hd)
+    _check(_fn(lib, "plm_attn_decode", flags)(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
+        block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
+        "attention_decode", kernels=2 if n_splits > 1 else 1)
+    return out
+
+
 # ------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """First index of each row's maximum, int32 [rows]."""
@@ -334,5 +403,12 @@ def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
 def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> torch.Tensor:
     """Causal attention of the step's queries over their sequences' cached keys
     and values (`kv` is a `KVLayerCache`)."""
+    if attention_mma_supported(q):
+        if step.is_decode:
+            splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1)
+            return attention_decode(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
+                                    splits, window=kv.window)
+        return attention_prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table,
+                                 max(step.new_lens), num_kv_heads, scale, window=kv.window)
     return attention_rows(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                           window=kv.window)

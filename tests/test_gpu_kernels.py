@@ -312,3 +312,81 @@ def test_gemm_tc_refuses_what_tma_cannot_address():
     assert not ops.gemm_tc_supported(a.float(), w.float())
     out = ops.linear(a, w, torch.float32)                              # the dispatcher falls to the any-size kernel
     assert out.shape == (4, 64)
+
+
+def _attn_case(H, G, hd, lens, new, seed, far_scale=40.0):
+    """Sequences of `lens` keys whose last `new` positions are the queries; in every sequence the key at
+    len // 7 matches the last query of every head strongly."""
+    torch.manual_seed(seed)
+    ks, vs, qs = [], [], []
+    for b, n in enumerate(lens):
+        k, v = torch.randn(n, G, hd) * 0.3, torch.randn(n, G, hd)
+        q = torch.randn(new[b], H, hd) * 0.5
+        far = n // 7
+        k[far] *= 3.0
+        for h in range(H):
+            kk = k[far, h // (H // G)]
+            q[-1, h] = kk * (far_scale / kk.norm() ** 2) * math.sqrt(hd)
+        ks.append(k.to(torch.bfloat16).float()), vs.append(v.to(torch.bfloat16).float())
+        qs.append(q.to(torch.bfloat16).float())
+    return ks, vs, qs
+
+
+def _attn_ref(ks, vs, qs, lens, new, H, hd, scale, window=None):
+    ref = []
+    for b, n in enumerate(lens):
+        full_q = torch.zeros(n, H, hd)
+        full_q[n - new[b]:] = qs[b]
+        ref.append(P.attention(full_q, ks[b], vs[b], scale, window)[n - new[b]:].reshape(new[b], H * hd))
+    return torch.cat(ref)
+
+
+@pytest.mark.parametrize("window", [None, 90])
+@pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (6, 2, 48), (5, 5, 16), (32, 1, 128), (3, 1, 32), (4, 2, 256)])
+def test_attention_prefill_mma(H, G, hd, window):
+    """Ragged prefill on the tensor cores: whole prompts, a one-token sequence, a chunk that continues a
+    cached prefix (300 keys, 70 of them new), lengths that straddle pages and query tiles."""
+    from picolm_b200 import ops
+    lens, new = [300, 1, 65, 130, 64], [70, 1, 65, 130, 3]
+    ks, vs, qs = _attn_case(H, G, hd, lens, new, H * 7 + hd)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attn_ref(ks, vs, qs, lens, new, H, hd, scale, window)
+    kc, vc, table = _paged(ks, vs, lens, 20, torch.bfloat16, 11)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    out = ops.attention_prefill(torch.cat(qs).to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV),
+                                torch.tensor(starts, dtype=torch.int32, device=DEV),
+                                torch.tensor(lens, dtype=torch.int32, device=DEV), table.to(DEV), max(new), G, scale,
+                                window=window)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    if window is None:                                   # the far key carries the last row of the first sequence
+        row = out.float().cpu()[new[0] - 1].reshape(H, hd)
+        for h in range(H):
+            assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
+
+
+@pytest.mark.parametrize("window", [None, 90])
+@pytest.mark.parametrize("n_splits", [1, 3, 16])
+@pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (6, 2, 48), (5, 5, 16), (40, 1, 128), (3, 1, 32), (4, 2, 256)])
+def test_attention_decode_mma(H, G, hd, n_splits, window):
+    """Decode on the tensor cores with the keys cut into ranges: sequences of very unequal lengths (some
+    ranges stay empty), more heads per KV head than one row group holds, a far key that must be found."""
+    from picolm_b200 import ops
+    lens = [700, 1, 65, 130, 64, 257]
+    new = [1] * len(lens)
+    ks, vs, qs = _attn_case(H, G, hd, lens, new, H * 3 + hd + n_splits)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attn_ref(ks, vs, qs, lens, new, H, hd, scale, window)
+    kc, vc, table = _paged(ks, vs, lens, 30, torch.bfloat16, 13)
+    out = ops.attention_decode(torch.cat(qs).to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV),
+                               torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV),
+                               torch.arange(len(lens), dtype=torch.int32, device=DEV), table.to(DEV), G, scale,
+                               n_splits, window=window)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    if window is None:
+        row = out.float().cpu()[0].reshape(H, hd)
+        for h in range(H):
+            assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
