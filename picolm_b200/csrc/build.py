@@ -38,7 +38,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "gemm_tc_static.h"]
 
 # Libraries that are specialised at compile time.  At run time only the variant a
 # model needs is built (`attention_variant`); the build check builds these.

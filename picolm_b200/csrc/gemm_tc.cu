@@ -436,3 +436,54 @@ extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtyp
     if (bn == 32) return launch<32, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     return launch<64, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
 }
+
+// ------------------------------------------------- the entry point that allocates nothing
+// See gemm_tc_static.h for whom this is and what it costs.  The partial sums of the split-K
+// product go to this file-scope array instead of a caller-provided workspace.
+#include "gemm_tc_static.h"
+
+static __device__ __align__(256) float plm_static_scratch[PLM_GEMM_TC_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+// Device address of plm_static_scratch on each device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use: the address comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+float* g_scratch_ptr[MAX_DEVICES];
+}  // namespace
+
+extern "C" const char* plm_gemm_tc_static_strerror(int code) {
+    switch (code) {
+        case PLM_OK: return "ok";
+        case PLM_ERR_DTYPE: return "unsupported element type (out_dtype must be 0 = float32 or 1 = bfloat16)";
+        case PLM_ERR_SHAPE: return "bad shape or leading dimension (ldo must equal F when K is split)";
+        case PLM_ERR_ALIGN: return "operands are not addressable by TMA (K and the leading dimensions must be "
+                                   "multiples of 8, the pointers 16-byte aligned)";
+        case PLM_ERR_UNSUPPORTED: return "the driver does not offer cuTensorMapEncodeTiled";
+        case PLM_ERR_SCRATCH_TOO_SMALL: return "the partial sums of this problem (splits * T * F floats) exceed the "
+                                               "library's fixed scratch array (PLM_GEMM_TC_STATIC_SCRATCH_FLOATS)";
+        case PLM_ERR_SCRATCH_SETUP: return "the device address of the library's scratch array could not be obtained";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown refusal";
+    }
+}
+
+extern "C" int plm_gemm_tc_static(const void* x, const void* w, void* out, int out_dtype, int T, int F, int K, long ldx,
+                                  long ldw, long ldo, int* status, cudaStream_t stream) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return PLM_ERR_SCRATCH_SETUP;
+    if (g_scratch_ptr[dev] == nullptr) {                 // set-up, once per device, that device being current
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, plm_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return PLM_ERR_SCRATCH_SETUP;
+        g_scratch_ptr[dev] = p;
+    }
+    if (T <= 0 || F <= 0) return PLM_OK;
+    int splits = 1;
+    long need = 0;
+    plm_gemm_tc_plan(T, F, K, &splits, &need);
+    if (need > (long)PLM_GEMM_TC_STATIC_SCRATCH_FLOATS) return PLM_ERR_SCRATCH_TOO_SMALL;
+    return plm_gemm_tc(x, w, out, out_dtype, T, F, K, ldx, ldw, ldo, g_scratch_ptr[dev], status, stream);
+}
