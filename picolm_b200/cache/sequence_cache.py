@@ -21,6 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .allocator import CacheFull, IndexPool
@@ -43,6 +44,7 @@ class KVGroup:
     pages: Dict[int, List[int]] = field(default_factory=dict)     # slot -> page of each 64-position block (0: none)
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
+    table: Optional[np.ndarray] = None          # int32 [slots, pages per sequence]: `pages` as rows, 0-padded
 
     def ordinal(self, layer: int) -> int:
         return self.layers.index(layer)
@@ -106,6 +108,8 @@ class SequenceCache:
                 self.state_specs[layer] = spec
             else:
                 raise ValueError(f"layer {layer}: unknown cache kind {spec.kind!r}")
+        for g in self.kv_groups:
+            g.table = np.zeros((max_seqs, self.pages_per_seq), dtype=np.int32)
         if allocate_storage:
             for g in self.kv_groups:
                 shape = (len(g.layers), n_pages + 1, g.spec.num_kv_heads, PAGE_TOKENS, g.spec.head_dim)
@@ -134,6 +138,7 @@ class SequenceCache:
             for p in g.pages.pop(slot):
                 if p:
                     g.pool.give_back(p)
+            g.table[slot, :] = 0
         del self.lengths[slot]
         self.slots.give_back(slot)
 
@@ -169,7 +174,9 @@ class SequenceCache:
         for g in self.kv_groups:
             for s, n in requests:
                 for _ in range(self._new_pages_needed(g, s, n)):
-                    g.pages[s].append(g.pool.take())
+                    page = g.pool.take()
+                    g.table[s, len(g.pages[s])] = page
+                    g.pages[s].append(page)
 
     def advance(self, slot: int, n_new: int) -> None:
         """The step wrote `n_new` positions of `slot`.  Pages of windowed groups
@@ -186,10 +193,11 @@ class SequenceCache:
                 if pages[b]:
                     g.pool.give_back(pages[b])
                     pages[b] = 0
+                    g.table[slot, b] = 0
 
-    def block_table_rows(self, group: int, slots: Sequence[int]) -> List[List[int]]:
-        g = self.kv_groups[group]
-        return [g.pages[s] for s in slots]
+    def block_table_rows(self, group: int, slots: Sequence[int]) -> np.ndarray:
+        """int32 [len(slots), pages per sequence]: the page of every 64-position block of each slot (0: none)."""
+        return self.kv_groups[group].table[np.asarray(slots, dtype=np.int64)]
 
     # ------------------------------------------------------------- accounting
     def check(self) -> None:
@@ -206,6 +214,11 @@ class SequenceCache:
                 raise AssertionError("pages in use and pages held by sequences differ")
             if set(g.pages) != self.slots._used:
                 raise AssertionError("page lists are kept for slots that are not in use")
+            for s in range(self.max_seqs):
+                want = g.pages.get(s, [])
+                row = g.table[s]
+                if list(row[:len(want)]) != list(want) or row[len(want):].any():
+                    raise AssertionError(f"the page table row of slot {s} differs from its page list")
 
     def kv_bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.kv_dtype).element_size()

@@ -1,0 +1,118 @@
+"""A decode step as a CUDA graph: for a fixed (padded) batch size the kernels
+of one step are captured once and replayed, so that a step costs one metadata
+copy and one graph launch instead of a launch per kernel from Python.
+
+The graph runs the same `Model.forward` on the same parts and kernels as an
+ordinary step; only the step's metadata lives in fixed device buffers that are
+refilled before every replay.  Batches are padded to the next size that has a
+graph; padding rows are single tokens of an empty sequence whose block table
+points at the cache's null page, so they read and write nothing that a real
+sequence sees, and their logits are dropped.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .step_batch import StepBatch
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def bucket_for(n: int) -> Optional[int]:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return None
+
+
+class DecodeGraph:
+    def __init__(self, engine, batch: int):
+        self.engine = engine
+        self.batch = B = batch
+        cache = engine.cache
+        dev = engine.runtime.device
+        P = cache.pages_per_seq
+        n_groups = len(cache.kv_groups)
+        # layout: tok_ids, tok_seq, tok_pos, seq_slot, seq_start, seq_kv_len, want_rows, block tables
+        self.sizes = [B, B, B, B, B + 1, B, B] + [B * P] * n_groups
+        total = sum(self.sizes)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.h, self.d = [], []
+        o = 0
+        for n in self.sizes:
+            self.h.append(self.host_np[o:o + n])
+            self.d.append(self.dev[o:o + n])
+            o += n
+        self.h[1][:] = np.arange(B)                       # tok_seq: one token per sequence
+        self.h[4][:] = np.arange(B + 1)                   # seq_start
+        self.h[6][:] = np.arange(B)                       # want_rows: every row
+        self.tables_h = [self.h[7 + g].reshape(B, P) for g in range(n_groups)]
+        self.step = StepBatch(
+            n_seqs=B, n_tokens=B, n_want=B, slots=[0] * B, new_lens=[1] * B, start_pos=[0] * B,
+            max_position=cache.max_seq_tokens - 1,        # splits and table bounds are fixed for the longest sequence
+            is_decode=True, tok_ids=self.d[0], tok_seq=self.d[1], tok_pos=self.d[2], seq_slot=self.d[3],
+            seq_start=self.d[4], seq_kv_len=self.d[5], want_rows=self.d[6],
+            block_tables=[self.d[7 + g].view(B, P) for g in range(n_groups)],
+            seq_slot_long=None, h2d_bytes=int(self.host_np.nbytes))
+        self.copied = torch.cuda.Event()                  # the last metadata copy has left the pinned buffer
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    def _fill(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> None:
+        n, B = len(slots), self.batch
+        cache = self.engine.cache
+        h = self.h
+        self.copied.synchronize()                         # do not overwrite what a pending copy still reads
+        h[0][:n] = tokens
+        h[0][n:] = 0
+        h[2][:n] = positions
+        h[2][n:] = 0
+        h[3][:n] = slots
+        h[3][n:] = 0
+        h[5][:n] = h[2][:n] + 1
+        h[5][n:] = 1
+        for g, table in enumerate(self.tables_h):
+            table[:n] = cache.block_table_rows(g, slots)
+            table[n:] = 0                                 # the null page
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+    def capture(self) -> None:
+        from .. import ops
+        eng = self.engine
+        self._fill([], [], [])
+        # once outside the capture: first-call set-up of every kernel, allocator warm-up
+        eng.model.forward(self.step, eng.cache)
+        torch.cuda.synchronize()
+        n0 = ops.launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        # Nothing may be freed while the stream is capturing: collect what is dead now and keep the
+        # collector off until the capture has ended (a dead engine's graphs and buffers would
+        # otherwise be destroyed in the middle of it, which CUDA refuses).
+        import gc
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = eng.model.forward(self.step, eng.cache)
+        finally:
+            if was_enabled:
+                gc.enable()
+        self.launches = ops.launch_count() - n0
+        ops.count_launches(-self.launches)                # the capture itself ran nothing
+
+    def run(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> torch.Tensor:
+        """Replay for `len(slots)` real sequences; returns logits [len(slots), vocab],
+        valid until the next replay of this graph."""
+        from .. import ops
+        self._fill(slots, tokens, positions)
+        self.graph.replay()
+        ops.count_launches(self.launches)
+        return self.logits[:len(slots)]

@@ -27,7 +27,7 @@ from .step_batch import StepBatch, build_step_batch
 
 class Engine:
     def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
-                 max_seq_tokens: Optional[int] = None):
+                 max_seq_tokens: Optional[int] = None, use_graphs: Optional[bool] = None):
         """`max_tokens`: the most tokens that live sequences hold at any time, each
         sequence's count rounded up to a multiple of the page size.  `max_seqs`:
         the most sequences alive at once (default: one per page).
@@ -45,6 +45,11 @@ class Engine:
                                    max_seq_tokens=longest)
         model.prepare(self.cache.max_seq_tokens)
         self.vocab_size = spec.vocab_size
+        # Decode steps replay a CUDA graph when every mixer says that its forward only launches
+        # work that depends on the step through device buffers (`graph_safe`).
+        safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
+        self._graphs: Dict[int, "DecodeGraph"] = {}
         self.reset_counters()
 
     def reset_counters(self) -> None:
@@ -59,14 +64,15 @@ class Engine:
     # ----------------------------------------------------------- construction
     @staticmethod
     def from_folder(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
-                    max_seq_tokens: Optional[int] = None, device="cuda:0") -> "Engine":
+                    max_seq_tokens: Optional[int] = None, device="cuda:0",
+                    use_graphs: Optional[bool] = None) -> "Engine":
         """Load `model_dir` (config.json + safetensors); the model class is chosen
         by config.json's `architectures` through the registry."""
         runtime = Runtime.create(dtype, device)
         config = read_config(model_dir)
         model = Model(spec_of(config), runtime)
         load_weights(model, model_dir)
-        eng = Engine(model, max_tokens, max_seqs, max_seq_tokens)
+        eng = Engine(model, max_tokens, max_seqs, max_seq_tokens, use_graphs=use_graphs)
         eng.config = config
         return eng
 
@@ -107,10 +113,35 @@ class Engine:
                 raise ValueError(f"slot {slot}: token id {lo if lo < 0 else hi} is outside the vocabulary "
                                  f"[0, {self.vocab_size})")
         self.cache.reserve([(slot, len(toks)) for slot, toks in entries])
-        batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
+        logits = None
+        if self.use_graphs and all(len(toks) == 1 for _, toks in entries):
+            logits = self._decode_with_graph(entries, wants)
+        if logits is None:
+            batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
+            self.counters["h2d_bytes"] += batch.h2d_bytes
+            logits = self.model.forward(batch, self.cache)
         self.counters["steps"] += 1
-        self.counters["h2d_bytes"] += batch.h2d_bytes
-        logits = self.model.forward(batch, self.cache)
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))
         return logits
+
+    def _decode_with_graph(self, entries, wants) -> Optional[torch.Tensor]:
+        """One token for each sequence through the captured graph of the batch's size class.  Returns None
+        if this step cannot use one (batch too large, or places wanted that are not exactly [0])."""
+        from .decode_graph import DecodeGraph, bucket_for
+        n = len(entries)
+        bucket = bucket_for(n)
+        if bucket is None:
+            return None
+        n_want = sum(len(w) for w in wants)
+        if n_want not in (0, n) or any(list(w) not in ([], [0]) for w in wants):
+            return None
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = DecodeGraph(self, bucket)
+            g.capture()
+            self._graphs[bucket] = g
+        slots = [s for s, _ in entries]
+        logits = g.run(slots, [t[0] for _, t in entries], [self.cache.length(s) for s in slots])
+        self.counters["h2d_bytes"] += g.step.h2d_bytes
+        return logits if n_want else None

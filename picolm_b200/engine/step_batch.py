@@ -73,9 +73,7 @@ def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], c
     seq_start[:] = offs
     want_rows[:] = want_flat
     for gi in range(n_groups):
-        table = views[7 + gi].reshape(B, P)
-        for b, pages in enumerate(cache.block_table_rows(gi, slots)):
-            table[b, :len(pages)] = pages
+        views[7 + gi].reshape(B, P)[:] = cache.block_table_rows(gi, slots)
     pinned = torch.from_numpy(host)
     if torch.device(device).type == "cuda":
         pinned = pinned.pin_memory()

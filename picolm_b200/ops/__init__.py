@@ -20,9 +20,11 @@ _vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 _SIGNATURES = {
     "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
-    "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_rmsnorm": [_vp, _vp, _i, _l, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
-    "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_swiglu_partials": [_vp, _i, _l, _vp, _i, _i, _i, _vp],
+    "plm_rope_store": [_vp, _i, _l, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_gemm_tc_partials": [_vp, _vp, _i, _i, _i, _l, _l, _vp, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
     "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
@@ -38,6 +40,32 @@ _fn_cache = {}
 
 class KernelError(RuntimeError):
     pass
+
+
+class PartialSums:
+    """A matrix product [T, F] that is still the sum of `splits` fp32 partial sums
+    (the K splits of the skinny tensor-core product): `parts` is [splits, T, F].
+    `rmsnorm` (as delta), `swiglu` and `rope_store` add the parts up themselves,
+    which saves the separate reduction kernel; `reduced()` gives the plain tensor."""
+
+    def __init__(self, parts: torch.Tensor, out_dtype: torch.dtype):
+        self.parts = parts
+        self.out_dtype = out_dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def splits(self) -> int:
+        return self.parts.shape[0]
+
+    @property
+    def stride(self) -> int:
+        return self.parts.shape[1] * self.parts.shape[2]
+
+    def reduced(self) -> torch.Tensor:
+        return self.parts.sum(dim=0).to(self.out_dtype) if self.splits > 1 else self.parts[0].to(self.out_dtype)
 
 
 _CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", -4: "unsupported option",
@@ -56,6 +84,11 @@ def _fn(library: str, name: str, extra_flags=()):
     return f
 
 
+def as_tensor(x) -> torch.Tensor:
+    """A plain tensor of what `linear(..., defer_reduce=True)` returned."""
+    return x.reduced() if isinstance(x, PartialSums) else x
+
+
 _launches = 0
 
 
@@ -63,6 +96,12 @@ def launch_count() -> int:
     """Kernels launched through this module so far (one per successful call of
     an entry point that launches one kernel)."""
     return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for kernels that ran (or did not run) outside `_check`: the replays of a CUDA graph."""
+    global _launches
+    _launches += n
 
 
 def _check(code: int, what: str, kernels: int = 1) -> None:
@@ -135,9 +174,14 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     T, d = x.shape
     if weight.shape != (d,):
         raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
+    d_splits, d_stride = 1, 0
+    if isinstance(delta, PartialSums):
+        d_splits, d_stride, delta = delta.splits, delta.stride, delta.parts
+        if tuple(delta.shape[1:]) != (T, d):
+            raise KernelError("delta must be shaped like x")
     if delta is not None:
         _dev(delta, "delta")
-        if delta.dtype != torch.float32 or delta.shape != x.shape:
+        if delta.dtype != torch.float32 or delta.numel() != d_splits * T * d:
             raise KernelError("delta must be float32 and shaped like x")
     n_rows = T
     if rows is not None:
@@ -146,13 +190,23 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     if out is None:
         out = torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
     _check(_fn("elementwise", "plm_rmsnorm")(
-        _p(x), _p(delta), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
-        float(eps), _stream()), "rmsnorm")
+        _p(x), _p(delta), d_splits, d_stride, _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows),
+        n_rows, d, float(eps), _stream()), "rmsnorm")
     return out
 
 
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """gate_up [T, 2F] (gate columns first) -> silu(gate) * up, [T, F]."""
+    if isinstance(gate_up, PartialSums):
+        T, F2 = gate_up.shape
+        if F2 % 2:
+            raise KernelError("gate_up must have an even number of columns")
+        if out is None:
+            out = torch.empty((T, F2 // 2), dtype=gate_up.out_dtype, device=gate_up.parts.device)
+        _check(_fn("elementwise", "plm_swiglu_partials")(
+            _p(gate_up.parts), gate_up.splits, gate_up.stride, _p(out), _dt(out, "out"), T, F2 // 2, _stream()),
+            "swiglu")
+        return out
     _dev(gate_up, "gate_up")
     T, F2 = gate_up.shape
     if F2 % 2:
@@ -172,18 +226,21 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
     """Rotate the query and key heads of `qkv` [T, (H+2G)*hd] by their tokens'
     positions; write queries to `q_out` [T, H, hd] and keys/values into the paged
     cache [pages, G, PAGE_TOKENS, hd]."""
+    q_splits, q_stride, q_dtype = 0, 0, None
+    if isinstance(qkv, PartialSums):
+        q_splits, q_stride, q_dtype, qkv = qkv.splits, qkv.stride, qkv.out_dtype, qkv.parts[0]
     _dev(qkv, "qkv")
     _dev(q_out, "q_out")
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
     T = qkv.shape[0]
     H, G, hd = num_heads, num_kv_heads, head_dim
-    if qkv.shape[1] != (H + 2 * G) * hd or q_out.shape != (T, H, hd) or q_out.dtype != qkv.dtype:
+    if qkv.shape[1] != (H + 2 * G) * hd or q_out.shape != (T, H, hd) or q_out.dtype != (q_dtype or qkv.dtype):
         raise KernelError("rope_store: qkv / q_out shapes do not match the head counts")
     if store:
         for c, n in ((k_cache, "k_cache"), (v_cache, "v_cache")):
             _dev(c, n)
-            if c.dtype != qkv.dtype or c.shape[1:] != (G, PAGE_TOKENS, hd):
-                raise KernelError(f"rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd}] of {qkv.dtype}")
+            if c.dtype != q_out.dtype or c.shape[1:] != (G, PAGE_TOKENS, hd):
+                raise KernelError(f"rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd}] of {q_out.dtype}")
     if cos is not None:
         _dev(cos, "cos"), _dev(sin, "sin")
         if cos.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape:
@@ -191,7 +248,8 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
     if pairing not in ("half", "adjacent"):
         raise KernelError(f"rope_store: unknown pairing {pairing!r}")
     _check(_fn("elementwise", "plm_rope_store")(
-        _p(qkv), _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None, _dt(qkv, "qkv"),
+        _p(qkv), q_splits, q_stride, _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None,
+        _dt(q_out, "q_out"),
         _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1], T, H, G, hd,
         rotary_dim, 0 if pairing == "half" else 1, 1 if store else 0, _stream()), "rope_store")
 
@@ -270,6 +328,21 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
         _p(a), _p(w), _p(out), _dt(out, "out"), M, N, K, K, K, N, _p(ws), _p(status_word(a.device)), _stream()),
         "gemm_tc", kernels=2 if ws is not None else 1)
     return out
+
+
+def gemm_tc_partials(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> PartialSums:
+    """The skinny tensor-core product (M <= 64) left as its K splits' partial sums."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if M > 64 or not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc_partials: needs a supported bfloat16 problem with at most 64 rows")
+    splits, ws_elems = ctypes.c_int(0), ctypes.c_long(0)
+    _fn("gemm_tc", "plm_gemm_tc_plan")(M, N, K, ctypes.byref(splits), ctypes.byref(ws_elems))
+    parts = torch.empty((splits.value, M, N), dtype=torch.float32, device=a.device)
+    _check(_fn("gemm_tc", "plm_gemm_tc_partials")(
+        _p(a), _p(w), M, N, K, K, K, _p(parts), _p(status_word(a.device)), _stream()), "gemm_tc_partials")
+    return PartialSums(parts, out_dtype)
 
 
 # ------------------------------------------------------------------ attention
@@ -392,10 +465,14 @@ def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, to
 
 
 # ---------------------------------------------------------------- dispatchers
-def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, defer_reduce: bool = False):
     """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
-    types and shape, never by the model."""
+    types and shape, never by the model.  With `defer_reduce` the result may come
+    back as `PartialSums` for a consumer that adds the K splits up itself
+    (`rmsnorm`'s delta, `swiglu`, `rope_store`)."""
     if gemm_tc_supported(a, w):
+        if defer_reduce and a.shape[0] <= 64:
+            return gemm_tc_partials(a, w, out_dtype)
         return gemm_tc(a, w, out_dtype)
     return gemm_simt(a, w, out_dtype)
 

@@ -43,6 +43,6 @@ class GatedMLP(Part):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     def forward(self, h, step):
-        gate_up = ops.linear(h, self.w_gate_up, self.runtime.dtype)
+        gate_up = ops.linear(h, self.w_gate_up, self.runtime.dtype, defer_reduce=True)
         act = ops.swiglu(gate_up)
-        return ops.linear(act, self.w_down, torch.float32)
+        return ops.linear(act, self.w_down, torch.float32, defer_reduce=True)

@@ -36,6 +36,10 @@ class Attention(Part):
     1/sqrt(head_dim)), window (None: all keys), position (a PartSpec of the
     position family), q_name/k_name/v_name/o_name (relative tensor names)."""
 
+    # forward() launches kernels whose dependence on the step goes through device buffers only
+    # (apart from sizes fixed per batch size), so a decode step may be captured in a CUDA graph
+    graph_safe = True
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         p = self.params
@@ -73,8 +77,8 @@ class Attention(Part):
 
     def forward(self, h, step, cache):
         dt = self.runtime.dtype
-        qkv = ops.linear(h, self.w_qkv, dt)
+        qkv = ops.linear(h, self.w_qkv, dt, defer_reduce=True)
         q = torch.empty((h.shape[0], self.H, self.hd), dtype=dt, device=h.device)
         self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
         ctx = ops.attention(q, cache, step, self.G, self.scale)
-        return ops.linear(ctx, self.w_o, torch.float32)
+        return ops.linear(ctx, self.w_o, torch.float32, defer_reduce=True)
