@@ -1,0 +1,134 @@
+"""Times one kernel at given sizes with CUDA events and prints what it achieved
+against the bytes it has to move or the flops it has to do.
+
+    python -m picolm_b200.bench_kernels gemm --m 8 --n 16384 --k 2048
+    python -m picolm_b200.bench_kernels attention_decode --batch 8 --ctx 2048 --heads 32 --kv-heads 8 --head-dim 64
+    python -m picolm_b200.bench_kernels attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
+
+Operands rotate through copies that together exceed the L2 cache, so every
+timed launch reads its weights or its cache from HBM.  `--iters` launches are
+timed after `--warmup` untimed ones; `--once` runs a single launch (for a
+profiler).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _time(fn, n_variants, iters, warmup):
+    for i in range(warmup):
+        fn(i % n_variants)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(iters):
+        fn(i % n_variants)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def bench_gemm(args):
+    from . import ops
+    M, N, K = args.m, args.n, args.k
+    w_bytes = N * K * 2
+    copies = max(2, math.ceil(2 * L2_BYTES / w_bytes))
+    ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(min(copies, 24))]
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
+    defer = args.defer and M <= 64
+
+    def run(i):
+        if defer:
+            ops.gemm_tc_partials(a, ws[i], out_dtype)
+        else:
+            ops.gemm_tc(a, ws[i], out_dtype)
+
+    sec = _time(run, len(ws), 1 if args.once else args.iters, 0 if args.once else args.warmup)
+    ops.check_status()
+    bytes_moved = w_bytes + M * K * 2 + M * N * (4 if out_dtype == torch.float32 else 2)
+    flops = 2.0 * M * N * K
+    return {"kernel": "gemm_tc", "m": M, "n": N, "k": K, "us": round(sec * 1e6, 2),
+            "GB/s": round(bytes_moved / sec / 1e9, 1), "TFLOP/s": round(flops / sec / 1e12, 2), "weight_copies": len(ws)}
+
+
+def _paged_cache(batch, ctx, G, hd, n_copies):
+    pages_per_seq = (ctx + 63) // 64
+    n_pages = batch * pages_per_seq + 1
+    caches = []
+    for _ in range(n_copies):
+        caches.append((torch.randn(n_pages, G, 64, hd, device="cuda").to(torch.bfloat16),
+                       torch.randn(n_pages, G, 64, hd, device="cuda").to(torch.bfloat16)))
+    table = (torch.arange(batch * pages_per_seq, dtype=torch.int32, device="cuda") + 1).view(batch, pages_per_seq)
+    return caches, table.contiguous()
+
+
+def bench_attention_decode(args):
+    from . import ops
+    B, C, H, G, hd = args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim
+    kv_bytes = B * C * G * hd * 2 * 2
+    caches, table = _paged_cache(B, C, G, hd, min(16, max(2, math.ceil(2 * L2_BYTES / kv_bytes))))
+    q = torch.randn(B, H, hd, device="cuda").to(torch.bfloat16)
+    pos = torch.full((B,), C - 1, dtype=torch.int32, device="cuda")
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    splits = args.splits or ops.decode_splits(B, H, G, C)
+
+    def run(i):
+        ops.attention_decode(q, caches[i][0], caches[i][1], pos, seq, table, G, 1.0 / math.sqrt(hd), splits)
+
+    sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
+    return {"kernel": "attention_decode", "batch": B, "ctx": C, "heads": H, "kv_heads": G, "head_dim": hd,
+            "splits": splits, "us": round(sec * 1e6, 2), "GB/s": round(kv_bytes / sec / 1e9, 1)}
+
+
+def bench_attention_prefill(args):
+    from . import ops
+    T, H, G, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
+    caches, table = _paged_cache(1, T, G, hd, 2)
+    q = torch.randn(T, H, hd, device="cuda").to(torch.bfloat16)
+    start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    kvlen = torch.tensor([T], dtype=torch.int32, device="cuda")
+
+    def run(i):
+        ops.attention_prefill(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
+
+    sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
+    flops = 2.0 * 2 * H * hd * T * (T + 1) / 2
+    return {"kernel": "attention_prefill", "tokens": T, "heads": H, "kv_heads": G, "head_dim": hd,
+            "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 2)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m picolm_b200.bench_kernels", description=__doc__.split("\n\n")[0])
+    ap.add_argument("kernel", choices=["gemm", "attention_decode", "attention_prefill"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=16384)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--out", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--defer", action="store_true", help="gemm: leave the K splits unreduced (skinny problems)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--once", action="store_true", help="one launch, no warm-up (for a profiler)")
+    args = ap.parse_args(argv)
+    fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
+          "attention_prefill": bench_attention_prefill}[args.kernel]
+    print(json.dumps(fn(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -182,6 +182,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_s = q_s + TILE_ELEMS;                     // [PF_STAGES][64][LDS]
     bf16* v_s = k_s + PF_STAGES * TILE_ELEMS;
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.z, g = blockIdx.y;
     const int R = H / G;
     const int t0 = seq_start[b], n_new = seq_start[b + 1] - t0;
@@ -292,6 +294,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw + DC_Q_BYTES);
     bf16* v_s = k_s + DC_STAGES * TILE_ELEMS;
     float* merge = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES);      // reused after the last tile
+    pdl_launch_dependents();
+    pdl_wait();
     const int n_splits = gridDim.x, split = blockIdx.x;
     const int g = blockIdx.y / row_groups, rg = blockIdx.y - g * row_groups;
     const int t = blockIdx.z;
@@ -411,6 +415,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
 // out[row, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp2(m_s - max m): one block per (token, head).
 __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                   bf16* __restrict__ out, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t row = blockIdx.x;
     float mm = -INFINITY;
     for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, ws_ml[(row * n_splits + s) * 2]);
@@ -454,10 +460,9 @@ extern "C" int plm_attn_prefill(const void* q, const void* kc, const void* vc, v
     }
     const int R = H / G;
     dim3 grid(((size_t)max_new * R + 63) / 64, G, n_seqs);
-    attn_prefill_kernel<<<grid, NT, PF_SMEM, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
-                                                       seq_start, seq_kv_len, block_table, max_pages, H, G,
-                                                       scale * LOG2E, window);
-    return plm_launch_status();
+    return plm_status_of(launch_pdl(attn_prefill_kernel, grid, dim3(NT), PF_SMEM, stream, (const bf16*)q, (const bf16*)kc,
+                                    (const bf16*)vc, (bf16*)out, seq_start, seq_kv_len, block_table, max_pages, H, G,
+                                    scale * LOG2E, window));
 }
 
 // Floats of workspace that plm_attn_decode needs for (tokens, H, splits): acc then (m, l).
@@ -483,11 +488,10 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
     dim3 grid(n_splits, G * row_groups, n_tokens);
-    attn_decode_kernel<<<grid, NT, DC_SMEM, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o,
-                                                      ws_ml, tok_pos, tok_seq, block_table, max_pages, H, G,
-                                                      scale * LOG2E, window, row_groups);
-    int rc = plm_launch_status();
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q, (const bf16*)kc,
+                                      (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq, block_table, max_pages,
+                                      H, G, scale * LOG2E, window, row_groups));
     if (rc != PLM_OK || n_splits == 1) return rc;
-    attn_merge_kernel<<<n_tokens * H, HD < 64 ? 32 : 64, 0, stream>>>(ws_o, ws_ml, (bf16*)out, n_splits);
-    return plm_launch_status();
+    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
+                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
 }

@@ -59,6 +59,33 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may begin while the kernel
+// before it on the stream is still running; pdl_wait() blocks until that kernel (and with it every
+// earlier one) has finished and its writes are visible.  So: before pdl_wait() a kernel may only
+// set itself up and read what no earlier kernel of the step writes (weights); it must not write
+// global memory.  pdl_launch_dependents() lets the next kernel begin its own set-up.  Without the
+// launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+static inline int plm_status_of(cudaError_t e) { return e == cudaSuccess ? PLM_OK : (int)e; }
+
 static inline int plm_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? PLM_OK : (int)e;

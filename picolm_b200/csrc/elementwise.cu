@@ -15,6 +15,8 @@
 template <typename Tw>
 __global__ void embed_kernel(const int* __restrict__ tok, const Tw* __restrict__ table, float* __restrict__ out,
                              int d, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = tok[t];
     if (id < 0 || id >= vocab) id = 0;   // ids are checked on the host; never read outside the table
@@ -29,12 +31,10 @@ extern "C" int plm_embed(const int* tok, const void* table, int table_dtype, flo
     if (d <= 0 || vocab <= 0) return PLM_ERR_SHAPE;
     const int nt = d >= 1024 ? 256 : 128;
     if (table_dtype == PLM_F32)
-        embed_kernel<float><<<n_tokens, nt, 0, stream>>>(tok, (const float*)table, out, d, vocab);
-    else if (table_dtype == PLM_BF16)
-        embed_kernel<bf16><<<n_tokens, nt, 0, stream>>>(tok, (const bf16*)table, out, d, vocab);
-    else
-        return PLM_ERR_DTYPE;
-    return plm_launch_status();
+        return plm_status_of(launch_pdl(embed_kernel<float>, n_tokens, nt, 0, stream, tok, (const float*)table, out, d, vocab));
+    if (table_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, stream, tok, (const bf16*)table, out, d, vocab));
+    return PLM_ERR_DTYPE;
 }
 
 // -------------------------------------------------------------------- RMSNorm
@@ -46,7 +46,8 @@ extern "C" int plm_embed(const int* tok, const void* table, int table_dtype, flo
 // else is in the batch.
 __device__ __forceinline__ float sum_splits(const float* __restrict__ p, int splits, size_t stride) {
     float v = p[0];
-    for (int s = 1; s < splits; ++s) v += p[(size_t)s * stride];
+#pragma unroll 8
+    for (int s = 1; s < splits; ++s) v += p[(size_t)s * stride];      // loads run ahead, adds stay in order
     return v;
 }
 
@@ -55,6 +56,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                const Tw* __restrict__ w, To* __restrict__ out, const int* __restrict__ rows, int d,
                                float eps, int write_back) {
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * d;
@@ -81,9 +84,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 template <typename Tw, typename To>
 static int rmsnorm_launch(float* x, const float* delta, int splits, long split_stride, const void* w, void* out,
                           const int* rows, int n_rows, int d, float eps, int write_back, cudaStream_t stream) {
-    rmsnorm_kernel<Tw, To, 256><<<n_rows, 256, 0, stream>>>(x, delta, splits, (size_t)split_stride, (const Tw*)w,
-                                                            (To*)out, rows, d, eps, write_back);
-    return plm_launch_status();
+    // enough threads that a row's loads are all in flight at once; the block size (and with it the
+    // order of the sum of squares) depends on the row's width only
+    if (d > 1024)
+        return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta, splits,
+                                        (size_t)split_stride, (const Tw*)w, (To*)out, rows, d, eps, write_back));
+    return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta, splits,
+                                    (size_t)split_stride, (const Tw*)w, (To*)out, rows, d, eps, write_back));
 }
 
 // delta: null, or `delta_splits` (>= 1) partial sums of [T, d] floats, `delta_stride` floats apart.
@@ -108,6 +115,8 @@ extern "C" int plm_rmsnorm(float* x, const float* delta, int delta_splits, long 
 // gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  out[T,F] = silu(gate) * up.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -126,12 +135,10 @@ extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int 
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == PLM_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, F, total);
-    else if (dtype == PLM_BF16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, total);
-    else
-        return PLM_ERR_DTYPE;
-    return plm_launch_status();
+        return plm_status_of(launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, F, total));
+    if (dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, F, total));
+    return PLM_ERR_DTYPE;
 }
 
 // gate_up comes as `splits` fp32 partial sums [T, 2F] of the product that made it.  Each sum is
@@ -139,6 +146,8 @@ extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int 
 template <typename T>
 __global__ void swiglu_partials_kernel(const float* __restrict__ parts, int splits, size_t stride, T* __restrict__ out,
                                        int F, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t step = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += step) {
@@ -158,12 +167,12 @@ extern "C" int plm_swiglu_partials(const float* parts, int splits, long stride, 
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (out_dtype == PLM_F32)
-        swiglu_partials_kernel<float><<<blocks, 256, 0, stream>>>(parts, splits, (size_t)stride, (float*)out, F, total);
-    else if (out_dtype == PLM_BF16)
-        swiglu_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(parts, splits, (size_t)stride, (bf16*)out, F, total);
-    else
-        return PLM_ERR_DTYPE;
-    return plm_launch_status();
+        return plm_status_of(launch_pdl(swiglu_partials_kernel<float>, blocks, 256, 0, stream, parts, splits,
+                                        (size_t)stride, (float*)out, F, total));
+    if (out_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(swiglu_partials_kernel<bf16>, blocks, 256, 0, stream, parts, splits,
+                                        (size_t)stride, (bf16*)out, F, total));
+    return PLM_ERR_DTYPE;
 }
 
 // ------------------------------------------------- RoPE + write into the cache
@@ -184,6 +193,8 @@ __global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_spli
                                   const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
                                   const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                                   int max_pages, int H, int G, int hd, int rot_dim, int pairing, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int half = hd / 2, rot_half = rot_dim / 2;
@@ -203,7 +214,7 @@ __global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_spli
         page_base = (size_t)(page < 0 ? 0 : page) * G;
         in_page = pos % PLM_PAGE;
     }
-    for (int item = threadIdx.x; item < n_heads * half; item += blockDim.x) {
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_heads * half; item += gridDim.y * blockDim.x) {
         const int head = item / half, j = item - head * half;
         int ia, ib;
         bool rotate = (j < rot_half) && cos_t != nullptr;
@@ -253,16 +264,17 @@ extern "C" int plm_rope_store(const void* qkv, int qkv_splits, long qkv_stride, 
     if (H <= 0 || G <= 0 || hd <= 0 || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return PLM_ERR_SHAPE;
     if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
     const int items = (H + 2 * G) * (hd / 2);
-    const int nt = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+    const int nt_threads = items >= 128 ? 128 : 64;
+    int chunks = (items + nt_threads - 1) / nt_threads;
+    if (chunks > 64) chunks = 64;
+    const dim3 nt(nt_threads), grid_rs(n_tokens, chunks);
     if (dtype == PLM_F32)
-        rope_store_kernel<float, float><<<n_tokens, nt, 0, stream>>>(
-            qkv, qkv_splits, (size_t)qkv_stride, (float*)q_out, (float*)kc, (float*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table,
-            max_pages, H, G, hd, rot_dim, pairing, store);
-    else if (dtype == PLM_BF16)
-        rope_store_kernel<bf16, bf16><<<n_tokens, nt, 0, stream>>>(
-            qkv, qkv_splits, (size_t)qkv_stride, (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table,
-            max_pages, H, G, hd, rot_dim, pairing, store);
-    else
-        return PLM_ERR_DTYPE;
-    return plm_launch_status();
+        return plm_status_of(launch_pdl(rope_store_kernel<float, float>, grid_rs, nt, 0, stream, qkv, qkv_splits,
+                                        (size_t)qkv_stride, (float*)q_out, (float*)kc, (float*)vc, cos_t, sin_t, tok_pos,
+                                        tok_seq, block_table, max_pages, H, G, hd, rot_dim, pairing, store));
+    if (dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(rope_store_kernel<bf16, bf16>, grid_rs, nt, 0, stream, qkv, qkv_splits,
+                                        (size_t)qkv_stride, (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos,
+                                        tok_seq, block_table, max_pages, H, G, hd, rot_dim, pairing, store));
+    return PLM_ERR_DTYPE;
 }

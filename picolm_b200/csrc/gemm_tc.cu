@@ -123,7 +123,8 @@ template <> __device__ __forceinline__ void store_vec8<bf16>(bf16* p, const uint
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8); }
+// skinny tiles (bn < 128) keep their ring small enough for two CTAs per SM
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 5); }
 __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
     return (size_t)stages_for(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
@@ -133,7 +134,7 @@ __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
 // gridDim = (P tiles, Q tiles, K splits).  With more than one split, OutT is
 // float and the CTA writes its partial sum to out + blockIdx.z * split_stride.
 template <int BN, bool SWAP, typename OutT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, (BN < 128 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                OutT* __restrict__ out, int p_rows, int q_rows, int K, long ldo, int kb_per_split, long split_stride,
                int* __restrict__ status) {
@@ -149,6 +150,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 16 * STAGES + 8 - raw));
     __shared__ int s_abort;
 
+    pdl_launch_dependents();                   // the next kernel may set itself up while this one runs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
     const int n_kb_total = (K + BK - 1) / BK;
@@ -177,17 +179,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
+        // The weight operand (P when SWAP, else Q) is written by no kernel of the step, so its
+        // first ring of loads is issued before pdl_wait(); the activation operand only after it.
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            const CUtensorMap* w_map = SWAP ? &map_p : &map_q;
+            const CUtensorMap* x_map = SWAP ? &map_q : &map_p;
+            const uint32_t w_smem = SWAP ? p_smem : q_smem, x_smem = SWAP ? q_smem : p_smem;
+            const uint32_t W_BYTES = SWAP ? P_BYTES : Q_BYTES, X_BYTES = SWAP ? Q_BYTES : P_BYTES;
+            const int w_row = SWAP ? p0 : q0, x_row = SWAP ? q0 : p0;
+            const int early = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < early; ++i) {              // the ring is empty: no wait needed
+                mbar_expect_tx(full0 + 8 * i, P_BYTES + Q_BYTES);
+                tma_load_2d(w_smem + i * W_BYTES, w_map, full0 + 8 * i, (kb_begin + i) * BK, w_row);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(x_smem + i * X_BYTES, x_map, full0 + 8 * i, (kb_begin + i) * BK, x_row);
+            int issued = early;
+            for (int i = early; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (i / STAGES) & 1;
                 if (*(volatile int*)&s_abort) break;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1, status, 1)) { s_abort = 1; break; }
                 mbar_expect_tx(full0 + 8 * s, P_BYTES + Q_BYTES);
                 const int k = (kb_begin + i) * BK;
-                tma_load_2d(p_smem + s * P_BYTES, &map_p, full0 + 8 * s, k, p0);
-                tma_load_2d(q_smem + s * Q_BYTES, &map_q, full0 + 8 * s, k, q0);
+                tma_load_2d(w_smem + s * W_BYTES, w_map, full0 + 8 * s, k, w_row);
+                tma_load_2d(x_smem + s * X_BYTES, x_map, full0 + 8 * s, k, x_row);
                 issued = i + 1;
             }
             if (*(volatile int*)&s_abort) {
@@ -220,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     } else {
         // ----------------------------------------------------------- epilogue
         const int quarter = warp & 3;                   // the TMEM lanes this warp may read
+        pdl_wait();                                     // the output may still be in use by an earlier kernel
         const bool ready = mbar_wait(tmem_full, 0, status, 3);
         if (!ready) s_abort = 1;
         tc_fence_after();
@@ -274,6 +292,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 // multiple of 4, so every split's slice starts on a 16-byte boundary.
 template <typename OutT, bool VEC>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int splits, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (VEC) {
         const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
         if (i >= total) return;
@@ -336,19 +356,19 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, OutT* out, int p_rows, 
         configured = true;
     }
     dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN, splits);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(mp, mq, out, p_rows, q_rows, K, ldo, kb_per_split, split_stride, status);
-    return plm_launch_status();
+    return plm_status_of(launch_pdl(kern, grid, dim3(NUM_THREADS), smem, stream, mp, mq, out, p_rows, q_rows, K, ldo,
+                                    kb_per_split, split_stride, status));
 }
 
 template <typename OutT>
 int launch_reduce(const float* partial, OutT* out, int splits, size_t total, cudaStream_t stream) {
     if (total % 4 == 0) {
         const size_t threads = total / 4;
-        splitk_reduce_kernel<OutT, true><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(partial, out, splits, total);
-    } else {
-        splitk_reduce_kernel<OutT, false><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(partial, out, splits, total);
+        return plm_status_of(launch_pdl(splitk_reduce_kernel<OutT, true>, dim3((unsigned)((threads + 255) / 256)),
+                                        dim3(256), 0, stream, partial, out, splits, total));
     }
-    return plm_launch_status();
+    return plm_status_of(launch_pdl(splitk_reduce_kernel<OutT, false>, dim3((unsigned)((total + 255) / 256)), dim3(256),
+                                    0, stream, partial, out, splits, total));
 }
 
 }  // namespace
@@ -371,7 +391,7 @@ extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* work
         const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         const int tiles = ((F + BM - 1) / BM) * ((T + bn - 1) / bn);
         const int n_kb = (K + BK - 1) / BK;
-        int want = (2 * 148 + tiles - 1) / tiles;              // about two CTAs per SM
+        int want = (2 * 148) / tiles;                          // one wave of two CTAs per SM, no tail
         if (want > n_kb / 2) want = n_kb / 2;                  // at least two K blocks per split
         if (want < 1) want = 1;
         const int per = (n_kb + want - 1) / want;

@@ -85,6 +85,8 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ lo
                                                     int* __restrict__ out) {
     __shared__ float redf[33];
     __shared__ int redi[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = block_argmax(logits + (size_t)blockIdx.x * ld, V, redf, redi);
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
@@ -191,8 +193,7 @@ sample_kernel(const float* __restrict__ logits, long ld, int V, float temperatur
 extern "C" int plm_argmax(const float* logits, long ld, int n_rows, int V, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return PLM_OK;
     if (V <= 0 || ld < V) return PLM_ERR_SHAPE;
-    argmax_kernel<<<n_rows, NT, 0, stream>>>(logits, ld, V, out);
-    return plm_launch_status();
+    return plm_status_of(launch_pdl(argmax_kernel, dim3(n_rows), dim3(NT), 0, stream, logits, ld, V, out));
 }
 
 // temperature > 0.  top_k <= 0 or >= V, top_p >= 1 and min_p <= 0 switch the
