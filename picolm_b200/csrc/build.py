@@ -34,11 +34,12 @@ LIBRARIES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu"],
     "gemm_simt": ["gemm_simt.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "gemm_tc_skinny": ["gemm_tc_skinny.cu"],
     "attention_simt": ["attention_simt.cu"],
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "gemm_tc_static.h"]
+HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
 
 # Libraries that are specialised at compile time.  At run time only the variant a
 # model needs is built (`attention_variant`); the build check builds these.

@@ -22,106 +22,11 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA records
 // where in `status`, stops issuing, drains what it has in flight, frees its
 // tensor memory and returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
+
+using namespace plm_tc;
 
 namespace {
-
-constexpr int BM = 128;                  // rows of P per tile (TMEM lanes)
-constexpr int BK = 64;                   // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;   // polls of mbarrier.try_wait before giving up
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (and records `where`) if the phase did not complete.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    if (status) atomicCAS(status, 0, where);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
-// (64 elements) with the 128-byte swizzle that TMA wrote: 8-row groups are 1024
-// bytes apart (SBO), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = BN.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-template <typename T> __device__ __forceinline__ void store_vec8(T* p, const uint32_t* r);
-template <> __device__ __forceinline__ void store_vec8<float>(float* p, const uint32_t* r) {
-    reinterpret_cast<uint4*>(p)[0] = make_uint4(r[0], r[1], r[2], r[3]);
-    reinterpret_cast<uint4*>(p)[1] = make_uint4(r[4], r[5], r[6], r[7]);
-}
-template <> __device__ __forceinline__ void store_vec8<bf16>(bf16* p, const uint32_t* r) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-}
 
 // skinny tiles (bn < 128) keep their ring small enough for two CTAs per SM
 __host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 5); }
@@ -133,7 +38,9 @@ __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
 // SWAP = false: out[p, q] (tokens on P);  SWAP = true: out[q, p] (tokens on Q).
 // gridDim = (P tiles, Q tiles, K splits).  With more than one split, OutT is
 // float and the CTA writes its partial sum to out + blockIdx.z * split_stride.
-template <int BN, bool SWAP, typename OutT>
+// EPI = 1 (wide path only): W's rows come in tiles of 64 gate rows followed by their 64 up rows, and
+// the kernel writes silu(gate) * up, each rounded to bf16 first, to out[p, q / 2] (q_rows / 2 columns).
+template <int BN, bool SWAP, typename OutT, int EPI = 0>
 __global__ void __launch_bounds__(NUM_THREADS, (BN < 128 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                OutT* __restrict__ out, int p_rows, int q_rows, int K, long ldo, int kb_per_split, long split_stride,
@@ -245,6 +152,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const int p = p0 + quarter * 32 + lane;     // row of P held by this thread
             OutT* dst = out + (size_t)blockIdx.z * split_stride;
             constexpr int CHUNK = BN >= 32 ? 32 : 16;
+            if (EPI == 1) {
+                if (BN >= 128 && !SWAP) {
+#pragma unroll 1
+                    for (int gq = 0; gq < BN; gq += 128) {
+                        if (q0 + gq >= q_rows) break;
+#pragma unroll 1
+                        for (int cc = 0; cc < 64; cc += 32) {
+                            uint32_t gt[32], up[32];
+                            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(gq + cc);
+                            tc_ld32(taddr, gt);
+                            tc_ld32(taddr + 64, up);
+                            tc_wait_ld();
+                            if (p < p_rows) {
+                                const int fo = (q0 + gq) / 2 + cc;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gt[j])));
+                                    const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j])));
+                                    gt[j] = __float_as_uint(g / (1.0f + expf(-g)) * u);
+                                }
+                                OutT* rowp = dst + (size_t)p * ldo + fo;
+                                if ((((size_t)p * ldo + fo) * sizeof(OutT)) % 16 == 0) {
+#pragma unroll
+                                    for (int j = 0; j < 32; j += 8) store_vec8<OutT>(rowp + j, gt + j);
+                                } else {
+                                    for (int j = 0; j < 32; ++j) rowp[j] = from_f32<OutT>(__uint_as_float(gt[j]));
+                                }
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK) {
                 uint32_t r[32];
@@ -313,43 +252,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __
     }
 }
 
-// ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A [rows, K] bf16 row-major matrix with leading dimension ld (elements); boxes of box_rows x 64.
-int make_map(CUtensorMap* map, const void* ptr, long rows, long K, long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return PLM_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? PLM_OK : PLM_ERR_ALIGN;
-}
-
-template <int BN, bool SWAP, typename OutT>
+template <int BN, bool SWAP, typename OutT, int EPI = 0>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, OutT* out, int p_rows, int q_rows, int K, long ldo,
            int splits, int kb_per_split, long split_stride, int* status, cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = smem_bytes_for(BN);
-    auto kern = gemm_tc_kernel<BN, SWAP, OutT>;
+    auto kern = gemm_tc_kernel<BN, SWAP, OutT, EPI>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -391,7 +299,7 @@ extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* work
         const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         const int tiles = ((F + BM - 1) / BM) * ((T + bn - 1) / bn);
         const int n_kb = (K + BK - 1) / BK;
-        int want = (2 * 148) / tiles;                          // one wave of two CTAs per SM, no tail
+        int want = (2 * 148 + tiles - 1) / tiles;              // about two CTAs per SM
         if (want > n_kb / 2) want = n_kb / 2;                  // at least two K blocks per split
         if (want < 1) want = 1;
         const int per = (n_kb + want - 1) / want;
@@ -455,6 +363,24 @@ extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtyp
     if (bn == 16) return launch<16, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     if (bn == 32) return launch<32, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     return launch<64, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+}
+
+// out[T, F/2] (bf16) = silu(gate) * up of x[T, K] * w[F, K]^T, where w holds tiles of 64 gate rows
+// followed by their 64 up rows (F a multiple of 128).  The wide path only (T > 64).
+extern "C" int plm_gemm_tc_wide_swiglu(const void* x, const void* w, void* out, int T, int F, int K, long ldx,
+                                       long ldw, long ldo, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (T <= 64) return PLM_ERR_UNSUPPORTED;
+    if (F % 128) return PLM_ERR_SHAPE;
+    if (!plm_gemm_tc_supported(x, w, T, F, K, ldx, ldw)) return PLM_ERR_ALIGN;
+    CUtensorMap mp, mq;
+    int rc;
+    const int bn = (F >= 2048 && T >= 256) ? 256 : 128;
+    if ((rc = make_map(&mp, x, T, K, ldx, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mq, w, F, K, ldw, bn)) != PLM_OK) return rc;
+    const int n_kb = (K + BK - 1) / BK;
+    if (bn == 256) return launch<256, false, bf16, 1>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
+    return launch<128, false, bf16, 1>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
 }
 
 // The split products only: `workspace` receives `splits` partial sums [T, F] in fp32 (splits as

@@ -1,0 +1,295 @@
+// out[T, F] = X[T, K] * W[F, K]^T for few tokens (T <= 64), the shape of a decode
+// step: the product is bound by reading W once from HBM, so W takes the 128-row
+// side of tcgen05.mma (full tiles), the tokens take 16, 32 or 64 accumulator
+// columns, and K is split over the CTAs of a thread-block cluster so that every
+// SM streams a share of W.
+//
+// The K splits' partial sums never go to global memory: each CTA of the cluster
+// parks its fp32 partial tile in its own shared memory, the cluster meets at a
+// barrier, and every CTA then sums a slice of the tile's rows over all CTAs'
+// shared memory (distributed shared memory, ascending rank: a fixed order) and
+// writes that slice of the result.  Epilogues:
+//   EPI_STORE   out = sum                                  (fp32 or bf16)
+//   EPI_SWIGLU  W's rows come in tiles of 64 gate rows followed by their 64 up rows;
+//               out[t, f] = silu(gate) * up, each rounded to bf16 first
+//               (picolm/model_core.c:2182-2193: hb = silu(Wg x) * (Wu x))
+// The reference's counterpart is its per-row matvec (picolm/tensor.c:839-1419).
+//
+// Warp roles and pipeline as in gemm_tc.cu; waits are bounded there and here.
+// With programmatic dependent launch the weight tiles of the first ring are
+// requested before the previous kernel has finished; activations only after.
+#include "tc_common.cuh"
+
+using namespace plm_tc;
+
+namespace {
+
+constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
+// ring depth: two CTAs of any tile width fit one SM (2 x ~100 KB)
+__host__ __device__ constexpr int stages_of(int bn) { return bn <= 32 ? 5 : 4; }
+constexpr int MAX_SPLITS = 8;               // portable cluster size
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+__host__ __device__ constexpr size_t skinny_smem(int bn) {
+    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256;
+}
+
+// W: [F, K] (P operand, 128 rows per tile), X: [T, K] (Q operand, BN rows).  grid = (F tiles, 1, S),
+// cluster = (1, 1, S).  out row stride ldo.  For EPI_SWIGLU, F counts W's rows (gate and up together)
+// and out has F/2 columns.
+template <int BN, int EPI, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      OutT* __restrict__ out, int F, int T, int K, long ldo, int kb_per_split, int* __restrict__ status) {
+    constexpr int STAGES = stages_of(BN);
+    constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    static_assert(BN * BM * 4 <= STAGES * (W_BYTES + X_BYTES), "the partial tile must fit the ring");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t w_smem = base, x_smem = base + STAGES * W_BYTES;
+    const uint32_t bars = x_smem + STAGES * X_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tmem_full = bars + 16 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 16 * STAGES + 8 - raw));
+    float* part = reinterpret_cast<float*>(smem_raw + (base - raw));     // [BN][128] partial tile, after the main loop
+    __shared__ int s_abort;
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * BM;
+    const uint32_t S = gridDim.z, rank = cluster_rank();
+    const int n_kb_total = (K + BK - 1) / BK;
+    const int kb_begin = (int)rank * kb_per_split;
+    const int kb_end = min(n_kb_total, kb_begin + kb_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int early = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < early; ++i) {                      // weights: nobody in this step writes them
+                mbar_expect_tx(full0 + 8 * i, W_BYTES + X_BYTES);
+                tma_load_2d(w_smem + i * W_BYTES, &map_w, full0 + 8 * i, (kb_begin + i) * BK, p0);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(x_smem + i * X_BYTES, &map_x, full0 + 8 * i, (kb_begin + i) * BK, 0);
+            int issued = early;
+            for (int i = early; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (*(volatile int*)&s_abort) break;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1, status, 1)) { s_abort = 1; break; }
+                mbar_expect_tx(full0 + 8 * s, W_BYTES + X_BYTES);
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, k, p0);
+                tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, k, 0);
+                issued = i + 1;
+            }
+            if (*(volatile int*)&s_abort)
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(BN);
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (*(volatile int*)&s_abort) break;
+                if (!mbar_wait(full0 + 8 * s, phase, status, 2)) { s_abort = 1; break; }
+                tc_fence_after();
+                const uint64_t wd = smem_desc_sw128(w_smem + s * W_BYTES);
+                const uint64_t xd = smem_desc_sw128(x_smem + s * X_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc_mma_bf16(tmem_base, wd + (uint64_t)(k * UMMA_K * 2 / 16), xd + (uint64_t)(k * UMMA_K * 2 / 16),
+                                idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(empty0 + 8 * s);
+            }
+            tc_commit(tmem_full);
+        }
+    } else {
+        // park this CTA's partial tile in shared memory: part[token][feature row]
+        const int quarter = warp & 3;
+        const bool ready = mbar_wait(tmem_full, 0, status, 3);
+        if (!ready) s_abort = 1;
+        tc_fence_after();
+        const int row = quarter * 32 + lane;
+        constexpr int CHUNK = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CHUNK) {
+            uint32_t r[32];
+            if (ready && n_kb > 0) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+                if (CHUNK == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK; ++j) r[j] = 0u;              // a CTA without K blocks adds nothing
+            }
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) part[(c + j) * BM + row] = __uint_as_float(r[j]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        if (*(volatile int*)&s_abort && lane == 0) mbar_wait(tmem_full, 0, nullptr, 0);
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    cluster_sync_all();                                            // every CTA's partial tile is in place
+
+    // ---- each CTA sums its slice of the tile's rows over all CTAs and writes it
+    pdl_wait();
+    const uint32_t part_addr = smem_u32(part);
+    uint32_t remote[MAX_SPLITS];
+#pragma unroll
+    for (uint32_t r = 0; r < MAX_SPLITS; ++r) remote[r] = r < S ? map_to_rank(part_addr, r) : 0u;
+    constexpr int ROWS = EPI == EPI_SWIGLU ? BM / 2 : BM;          // rows that produce an output column
+    const int slice = ROWS / (int)S;
+    const int items = slice * BN;
+    for (int it = threadIdx.x; it < items; it += NUM_THREADS) {
+        const int c = it / slice, pr = it - c * slice;
+        const int row = (int)rank * slice + pr;
+        const int t = c;
+        if (t >= T) continue;
+        if (EPI == EPI_STORE) {
+            const int f = p0 + row;
+            if (f >= F) continue;
+            float v = 0.f;
+#pragma unroll
+            for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+                if (r < S) v += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+            out[(size_t)t * ldo + f] = from_f32<OutT>(v);
+        } else {
+            const int fo = p0 / 2 + row;
+            if (fo >= F / 2) continue;
+            float g = 0.f, u = 0.f;
+#pragma unroll
+            for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+                if (r < S) {
+                    g += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+                    u += ld_cluster(remote[r] + (uint32_t)(c * BM + BM / 2 + row) * 4u);
+                }
+            g = __bfloat162float(__float2bfloat16_rn(g));
+            u = __bfloat162float(__float2bfloat16_rn(u));
+            out[(size_t)t * ldo + fo] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
+        }
+    }
+    __syncthreads();                                               // reconverge before the aligned barrier
+    cluster_sync_all();                                            // nobody reads this CTA's tile any more
+}
+
+template <int BN, int EPI, typename OutT>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T, int K, long ldo, int S, int* status,
+           cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = skinny_smem(BN);
+    auto kern = gemm_tc_skinny_kernel<BN, EPI, OutT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int n_kb = (K + BK - 1) / BK;
+    const int per = (n_kb + S - 1) / S;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((F + BM - 1) / BM, 1, S);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = S;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return plm_status_of(cudaLaunchKernelEx(&cfg, kern, mw, mx, out, F, T, K, ldo, per, status));
+}
+
+template <int EPI, typename OutT>
+int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T, int K, long ldo, int S,
+                int* status, cudaStream_t stream) {
+    if (bn == 16) return launch<16, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
+    if (bn == 32) return launch<32, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
+    return launch<64, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
+}
+
+}  // namespace
+
+// How many CTAs share a tile's K range: the largest power of two (at most 8) that keeps the grid
+// within one wave of two CTAs per SM and leaves every CTA at least two K blocks.  Fixed by (F, K).
+extern "C" int plm_gemm_tc_skinny_splits(int F, int K) {
+    const int tiles = (F + BM - 1) / BM;
+    const int n_kb = (K + BK - 1) / BK;
+    int S = MAX_SPLITS;
+    while (S > 1 && (tiles * S > 2 * 148 || n_kb < 2 * S)) S >>= 1;
+    return S;
+}
+
+// out[T, F'] = epilogue(x[T, K] * w[F, K]^T), T <= 64, bf16 operands.  epilogue 0: F' = F, out is
+// float32 (out_dtype 0) or bfloat16 (1).  epilogue 1 (SwiGLU): w holds tiles of 64 gate rows followed
+// by their 64 up rows (F a multiple of 128), F' = F / 2, out is bfloat16.
+extern "C" int plm_gemm_tc_skinny(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                  int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (T > 64) return PLM_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    const int S = plm_gemm_tc_skinny_splits(F, K);
+    CUtensorMap mw, mx;
+    int rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, bn)) != PLM_OK) return rc;
+    if (epilogue == EPI_SWIGLU)
+        return dispatch_bn<EPI_SWIGLU, bf16>(bn, mw, mx, (bf16*)out, F, T, K, ldo, S, status, stream);
+    if (out_dtype == PLM_F32) return dispatch_bn<EPI_STORE, float>(bn, mw, mx, (float*)out, F, T, K, ldo, S, status, stream);
+    if (out_dtype == PLM_BF16) return dispatch_bn<EPI_STORE, bf16>(bn, mw, mx, (bf16*)out, F, T, K, ldo, S, status, stream);
+    return PLM_ERR_DTYPE;
+}

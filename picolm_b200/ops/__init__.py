@@ -24,6 +24,8 @@ _SIGNATURES = {
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "plm_swiglu_partials": [_vp, _i, _l, _vp, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _i, _l, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_wide_swiglu": [_vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_partials": [_vp, _vp, _i, _i, _i, _l, _l, _vp, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
@@ -330,6 +332,57 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
+def gemm_tc_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The decode-shaped tensor-core product: a [M <= 64, K] @ w [N, K]^T with the weights on the MMA's 128
+    rows and K split over a thread-block cluster whose CTAs add their partial tiles up through distributed
+    shared memory.  With `swiglu`, w holds tiles of 64 gate rows followed by their 64 up rows (see
+    `interleave_gate_up`) and the result is silu(gate) * up, [M, N/2] in bfloat16."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if M > 64 or not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc_skinny: needs a supported bfloat16 problem with at most 64 rows")
+    if swiglu:
+        if N % 128:
+            raise KernelError("gemm_tc_skinny: the interleaved gate/up matrix must have a multiple of 128 rows")
+        out_dtype = torch.bfloat16
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
+        _p(status_word(a.device)), _stream()), "gemm_tc_skinny")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[gate | up] as one matrix whose rows come in tiles of 64 gate rows followed by the 64 up rows of
+    the same features, so that a 128-row MMA tile holds both branches of 64 outputs and the product's
+    epilogue can apply SwiGLU.  Needs a number of features that is a multiple of 64."""
+    F, K = gate.shape
+    if up.shape != gate.shape or F % 64:
+        raise KernelError("interleave_gate_up: gate and up must have the same shape with a multiple of 64 rows")
+    return torch.stack([gate.view(F // 64, 64, K), up.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
+    whose epilogue applies the activation; [M, F] in bfloat16."""
+    _dev(a, "a"), _dev(w_gate_up, "w_gate_up")
+    M, K = a.shape
+    N = w_gate_up.shape[0]
+    if not gemm_tc_supported(a, w_gate_up) or N % 128:
+        raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
+    if M <= 64:
+        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    _check(_fn("gemm_tc", "plm_gemm_tc_wide_swiglu")(
+        _p(a), _p(w_gate_up), _p(out), M, N, K, K, K, N // 2, _p(status_word(a.device)), _stream()),
+        "gemm_tc_wide_swiglu")
+    return out
+
+
 def gemm_tc_partials(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> PartialSums:
     """The skinny tensor-core product (M <= 64) left as its K splits' partial sums."""
     _dev(a, "a"), _dev(w, "w")
@@ -471,8 +524,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, defer_reduc
     back as `PartialSums` for a consumer that adds the K splits up itself
     (`rmsnorm`'s delta, `swiglu`, `rope_store`)."""
     if gemm_tc_supported(a, w):
-        if defer_reduce and a.shape[0] <= 64:
-            return gemm_tc_partials(a, w, out_dtype)
+        if a.shape[0] <= 64:
+            return gemm_tc_skinny(a, w, out_dtype)
         return gemm_tc(a, w, out_dtype)
     return gemm_simt(a, w, out_dtype)
 

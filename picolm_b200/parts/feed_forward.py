@@ -35,14 +35,21 @@ class GatedMLP(Part):
 
     def load(self, tensors):
         p = self.params
-        # one projection for both branches: rows [gate | up]
-        self.w_gate_up = _stack_rows([tensors[p["gate_name"]], tensors[p["up_name"]]])
+        gate, up = tensors[p["gate_name"]], tensors[p["up_name"]]
+        # One projection for both branches.  Where the tensor-core product can apply the activation
+        # in its epilogue, the rows are laid out in tiles of 64 gate rows and their 64 up rows;
+        # otherwise plainly [gate | up] with the activation as a kernel of its own.
+        self.fused = (gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape[0] % 64 == 0
+                      and gate.shape[1] % 8 == 0 and gate.shape[1] >= 64)
+        self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else _stack_rows([gate, up])
         self.w_down = tensors[p["down_name"]]
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     def forward(self, h, step):
-        gate_up = ops.linear(h, self.w_gate_up, self.runtime.dtype, defer_reduce=True)
-        act = ops.swiglu(gate_up)
-        return ops.linear(act, self.w_down, torch.float32, defer_reduce=True)
+        if self.fused:
+            act = ops.linear_swiglu(h, self.w_gate_up)
+        else:
+            act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype))
+        return ops.linear(act, self.w_down, torch.float32)

@@ -77,8 +77,8 @@ class Attention(Part):
 
     def forward(self, h, step, cache):
         dt = self.runtime.dtype
-        qkv = ops.linear(h, self.w_qkv, dt, defer_reduce=True)
+        qkv = ops.linear(h, self.w_qkv, dt)
         q = torch.empty((h.shape[0], self.H, self.hd), dtype=dt, device=h.device)
         self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
         ctx = ops.attention(q, cache, step, self.G, self.scale)
-        return ops.linear(ctx, self.w_o, torch.float32, defer_reduce=True)
+        return ops.linear(ctx, self.w_o, torch.float32)

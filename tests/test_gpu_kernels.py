@@ -390,3 +390,47 @@ def test_attention_decode_mma(H, G, hd, n_splits, window):
         row = out.float().cpu()[0].reshape(H, hd)
         for h in range(H):
             assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 3072, 2048), (16, 200, 264), (17, 256, 512), (33, 130, 1024),
+                                   (64, 2048, 8192), (5, 16384, 2048), (64, 40000, 128), (3, 2048, 2112)])
+def test_gemm_tc_skinny_cluster(out_dtype, M, N, K):
+    """The decode-shaped product whose K splits meet in distributed shared memory: every cluster size
+    (1, 2, 4, 8), all three token-tile widths, ragged feature edges, K ranges that leave a CTA of the
+    cluster with fewer (or no) K blocks."""
+    from picolm_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    ref = a.double() @ w.double().t()
+    out = ops.gemm_tc_skinny(a.to(DEV), w.to(DEV), DT[out_dtype])
+    ops.check_status(DEV)
+    tol_ = dict(atol=2e-3, rtol=1e-4) if out_dtype == "float32" else dict(atol=2e-2, rtol=1e-2)
+    assert torch.allclose(out.double().cpu(), ref, **tol_)
+    again = ops.gemm_tc_skinny(a.to(DEV), w.to(DEV), DT[out_dtype])
+    assert torch.equal(out, again)                          # a fixed order of the partial sums
+
+
+@pytest.mark.parametrize("M", [1, 8, 40, 64, 65, 300, 2048])
+@pytest.mark.parametrize("F,K", [(64, 64), (192, 328), (8192, 2048), (1088, 512)])
+def test_linear_swiglu_fused(M, F, K):
+    """SwiGLU in the product's epilogue (skinny and wide paths) against gate/up products and the plain
+    activation, with the rounding of gate and up to bf16 that the unfused path has."""
+    from picolm_b200 import ops
+    torch.manual_seed(M + F + K)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    gate = (torch.randn(F, K) / K ** 0.5).to(torch.bfloat16)
+    up = (torch.randn(F, K) / K ** 0.5).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate.to(DEV), up.to(DEV))
+    assert w.shape == (2 * F, K) and torch.equal(w[:64].cpu(), gate[:64]) and torch.equal(w[64:128].cpu(), up[:64])
+    out = ops.linear_swiglu(a.to(DEV), w)
+    ops.check_status(DEV)
+    g = (a.double() @ gate.double().t()).to(torch.bfloat16).float()
+    u = (a.double() @ up.double().t()).to(torch.bfloat16).float()
+    ref = P.swiglu(g, u)
+    assert out.shape == (M, F) and out.dtype == torch.bfloat16
+    # a gate or up value that sits on a bf16 rounding boundary may round the other way: allow one such step
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
