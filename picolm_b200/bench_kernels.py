@@ -22,11 +22,29 @@ import torch
 L2_BYTES = 126 * 1024 * 1024
 
 
+USE_GRAPH = False
+
+
 def _time(fn, n_variants, iters, warmup):
+    """Seconds per launch.  With USE_GRAPH the `iters` launches are captured into one CUDA graph and
+    the graph's replay is timed: launch overhead from Python (some 20 us a call) then does not hide
+    kernels that are shorter than it."""
     for i in range(warmup):
         fn(i % n_variants)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    if USE_GRAPH:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i % n_variants)
+        g.replay()
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
     a.record()
     for i in range(iters):
         fn(i % n_variants)
@@ -43,19 +61,15 @@ def bench_gemm(args):
     ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(min(copies, 24))]
     a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
-    defer = args.defer and M <= 64
 
     def run(i):
-        if defer:
-            ops.gemm_tc_partials(a, ws[i], out_dtype)
-        else:
-            ops.gemm_tc(a, ws[i], out_dtype)
+        ops.linear(a, ws[i], out_dtype)
 
     sec = _time(run, len(ws), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     ops.check_status()
     bytes_moved = w_bytes + M * K * 2 + M * N * (4 if out_dtype == torch.float32 else 2)
     flops = 2.0 * M * N * K
-    return {"kernel": "gemm_tc", "m": M, "n": N, "k": K, "us": round(sec * 1e6, 2),
+    return {"kernel": "linear (tensor cores)", "m": M, "n": N, "k": K, "us": round(sec * 1e6, 2),
             "GB/s": round(bytes_moved / sec / 1e9, 1), "TFLOP/s": round(flops / sec / 1e12, 2), "weight_copies": len(ws)}
 
 
@@ -112,7 +126,6 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--out", default="float32", choices=["float32", "bfloat16"])
-    ap.add_argument("--defer", action="store_true", help="gemm: leave the K splits unreduced (skinny problems)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -123,7 +136,10 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--once", action="store_true", help="one launch, no warm-up (for a profiler)")
+    ap.add_argument("--graph", action="store_true", help="time the launches as one CUDA graph (for short kernels)")
     args = ap.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = args.graph and not args.once
     fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
           "attention_prefill": bench_attention_prefill}[args.kernel]
     print(json.dumps(fn(args)))

@@ -40,21 +40,12 @@ extern "C" int plm_embed(const int* tok, const void* table, int table_dtype, flo
 // -------------------------------------------------------------------- RMSNorm
 // One block per output row.  Row r reads source row rows[r] (or r).  With a
 // delta the sum x + delta is normalised; it is written back to x unless rows are
-// gathered.  The delta may come as `splits` partial sums (the K splits of the
-// matrix product that made it), `split_stride` floats apart, added in ascending
-// order.  The reduction order depends on the row's width only, never on what
+// gathered.  The reduction order depends on the row's width only, never on what
 // else is in the batch.
-__device__ __forceinline__ float sum_splits(const float* __restrict__ p, int splits, size_t stride) {
-    float v = p[0];
-#pragma unroll 8
-    for (int s = 1; s < splits; ++s) v += p[(size_t)s * stride];      // loads run ahead, adds stay in order
-    return v;
-}
 
 template <typename Tw, typename To, int NT>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, size_t split_stride,
-                               const Tw* __restrict__ w, To* __restrict__ out, const int* __restrict__ rows, int d,
-                               float eps, int write_back) {
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const Tw* __restrict__ w,
+                               To* __restrict__ out, const int* __restrict__ rows, int d, float eps, int write_back) {
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -66,7 +57,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     for (int i = threadIdx.x; i < d; i += NT) {
         float v = xr[i];
         if (dr) {
-            v += sum_splits(dr + i, splits, split_stride);
+            v += dr[i];
             if (write_back) xr[i] = v;
         }
         ss += v * v;
@@ -76,38 +67,36 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     To* o = out + (size_t)r * d;
     for (int i = threadIdx.x; i < d; i += NT) {
         float v = xr[i];
-        if (dr && !write_back) v += sum_splits(dr + i, splits, split_stride);
+        if (dr && !write_back) v += dr[i];
         o[i] = from_f32<To>(v * scale * to_f32<Tw>(w[i]));
     }
 }
 
 template <typename Tw, typename To>
-static int rmsnorm_launch(float* x, const float* delta, int splits, long split_stride, const void* w, void* out,
-                          const int* rows, int n_rows, int d, float eps, int write_back, cudaStream_t stream) {
+static int rmsnorm_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows, int d,
+                          float eps, int write_back, cudaStream_t stream) {
     // enough threads that a row's loads are all in flight at once; the block size (and with it the
     // order of the sum of squares) depends on the row's width only
     if (d > 1024)
-        return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta, splits,
-                                        (size_t)split_stride, (const Tw*)w, (To*)out, rows, d, eps, write_back));
-    return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta, splits,
-                                    (size_t)split_stride, (const Tw*)w, (To*)out, rows, d, eps, write_back));
+        return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta,
+                                        (const Tw*)w, (To*)out, rows, d, eps, write_back));
+    return plm_status_of(launch_pdl(rmsnorm_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta, (const Tw*)w,
+                                    (To*)out, rows, d, eps, write_back));
 }
 
-// delta: null, or `delta_splits` (>= 1) partial sums of [T, d] floats, `delta_stride` floats apart.
-extern "C" int plm_rmsnorm(float* x, const float* delta, int delta_splits, long delta_stride, const void* w,
-                           int w_dtype, void* out, int out_dtype, const int* rows, int n_rows, int d, float eps,
-                           cudaStream_t stream) {
+extern "C" int plm_rmsnorm(float* x, const float* delta, const void* w, int w_dtype, void* out, int out_dtype,
+                           const int* rows, int n_rows, int d, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return PLM_OK;
-    if (d <= 0 || (delta && delta_splits < 1)) return PLM_ERR_SHAPE;
+    if (d <= 0) return PLM_ERR_SHAPE;
     const int write_back = (delta != nullptr && rows == nullptr) ? 1 : 0;
     if (w_dtype == PLM_F32 && out_dtype == PLM_F32)
-        return rmsnorm_launch<float, float>(x, delta, delta_splits, delta_stride, w, out, rows, n_rows, d, eps, write_back, stream);
+        return rmsnorm_launch<float, float>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
     if (w_dtype == PLM_BF16 && out_dtype == PLM_F32)
-        return rmsnorm_launch<bf16, float>(x, delta, delta_splits, delta_stride, w, out, rows, n_rows, d, eps, write_back, stream);
+        return rmsnorm_launch<bf16, float>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
     if (w_dtype == PLM_F32 && out_dtype == PLM_BF16)
-        return rmsnorm_launch<float, bf16>(x, delta, delta_splits, delta_stride, w, out, rows, n_rows, d, eps, write_back, stream);
+        return rmsnorm_launch<float, bf16>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
     if (w_dtype == PLM_BF16 && out_dtype == PLM_BF16)
-        return rmsnorm_launch<bf16, bf16>(x, delta, delta_splits, delta_stride, w, out, rows, n_rows, d, eps, write_back, stream);
+        return rmsnorm_launch<bf16, bf16>(x, delta, w, out, rows, n_rows, d, eps, write_back, stream);
     return PLM_ERR_DTYPE;
 }
 
@@ -141,40 +130,6 @@ extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int 
     return PLM_ERR_DTYPE;
 }
 
-// gate_up comes as `splits` fp32 partial sums [T, 2F] of the product that made it.  Each sum is
-// rounded to T first, so that the result is the one of the kernel above on the reduced product.
-template <typename T>
-__global__ void swiglu_partials_kernel(const float* __restrict__ parts, int splits, size_t stride, T* __restrict__ out,
-                                       int F, size_t total) {
-    pdl_launch_dependents();
-    pdl_wait();
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (; i < total; i += step) {
-        const size_t t = i / F;
-        const int c = (int)(i - t * F);
-        const float g = to_f32<T>(from_f32<T>(sum_splits(parts + t * 2 * F + c, splits, stride)));
-        const float u = to_f32<T>(from_f32<T>(sum_splits(parts + t * 2 * F + F + c, splits, stride)));
-        out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
-    }
-}
-
-extern "C" int plm_swiglu_partials(const float* parts, int splits, long stride, void* out, int out_dtype, int n_rows,
-                                   int F, cudaStream_t stream) {
-    if (n_rows <= 0) return PLM_OK;
-    if (F <= 0 || splits < 1) return PLM_ERR_SHAPE;
-    const size_t total = (size_t)n_rows * F;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    if (out_dtype == PLM_F32)
-        return plm_status_of(launch_pdl(swiglu_partials_kernel<float>, blocks, 256, 0, stream, parts, splits,
-                                        (size_t)stride, (float*)out, F, total));
-    if (out_dtype == PLM_BF16)
-        return plm_status_of(launch_pdl(swiglu_partials_kernel<bf16>, blocks, 256, 0, stream, parts, splits,
-                                        (size_t)stride, (bf16*)out, F, total));
-    return PLM_ERR_DTYPE;
-}
-
 // ------------------------------------------------- RoPE + write into the cache
 // qkv is [T, (H + 2G) * hd]: H query heads, then G key heads, then G value heads.
 // Query heads are rotated into q_out [T, H, hd]; key heads are rotated and
@@ -184,11 +139,8 @@ extern "C" int plm_swiglu_partials(const float* parts, int splits, long stride, 
 // pairing 0: (x[i], x[i + rot_dim/2]); pairing 1: (x[2i], x[2i+1]).  Elements at
 // and beyond rot_dim pass through.  store = 0 skips the cache (a layer that reads
 // another layer's cache).
-// With qkv_splits > 0 the projection arrives as that many fp32 partial sums (`qkv` then points at
-// floats, `qkv_stride` floats apart); each sum is rounded to Ta before it is used.
 template <typename Ta, typename Tc>
-__global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_splits, size_t qkv_stride,
-                                  Ta* __restrict__ q_out, Tc* __restrict__ kc,
+__global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q_out, Tc* __restrict__ kc,
                                   Tc* __restrict__ vc, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
                                   const int* __restrict__ tok_seq, const int* __restrict__ block_table,
@@ -199,12 +151,7 @@ __global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_spli
     const int pos = tok_pos[t];
     const int half = hd / 2, rot_half = rot_dim / 2;
     const int n_heads = H + 2 * G;
-    const Ta* row = reinterpret_cast<const Ta*>(qkv_any) + (size_t)t * n_heads * hd;
-    const float* prow = reinterpret_cast<const float*>(qkv_any) + (size_t)t * n_heads * hd;
-    auto load = [&](int idx) -> float {
-        if (qkv_splits > 0) return to_f32<Ta>(from_f32<Ta>(sum_splits(prow + idx, qkv_splits, qkv_stride)));
-        return to_f32<Ta>(row[idx]);
-    };
+    const Ta* row = qkv + (size_t)t * n_heads * hd;
     size_t page_base = 0;
     int in_page = 0;
     bool have_page = false;
@@ -223,8 +170,8 @@ __global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_spli
         } else {
             ia = rot_dim + 2 * (j - rot_half); ib = ia + 1;
         }
-        float a = load(head * hd + ia);
-        float b = load(head * hd + ib);
+        float a = to_f32<Ta>(row[head * hd + ia]);
+        float b = to_f32<Ta>(row[head * hd + ib]);
         if (head < H) {
             if (rotate) {
                 const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
@@ -255,8 +202,7 @@ __global__ void rope_store_kernel(const void* __restrict__ qkv_any, int qkv_spli
     }
 }
 
-extern "C" int plm_rope_store(const void* qkv, int qkv_splits, long qkv_stride, void* q_out, void* kc, void* vc,
-                              int dtype, const float* cos_t,
+extern "C" int plm_rope_store(const void* qkv, void* q_out, void* kc, void* vc, int dtype, const float* cos_t,
                               const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
                               int max_pages, int n_tokens, int H, int G, int hd, int rot_dim, int pairing, int store,
                               cudaStream_t stream) {
@@ -269,12 +215,12 @@ extern "C" int plm_rope_store(const void* qkv, int qkv_splits, long qkv_stride, 
     if (chunks > 64) chunks = 64;
     const dim3 nt(nt_threads), grid_rs(n_tokens, chunks);
     if (dtype == PLM_F32)
-        return plm_status_of(launch_pdl(rope_store_kernel<float, float>, grid_rs, nt, 0, stream, qkv, qkv_splits,
-                                        (size_t)qkv_stride, (float*)q_out, (float*)kc, (float*)vc, cos_t, sin_t, tok_pos,
+        return plm_status_of(launch_pdl(rope_store_kernel<float, float>, grid_rs, nt, 0, stream, (const float*)qkv,
+                                        (float*)q_out, (float*)kc, (float*)vc, cos_t, sin_t, tok_pos,
                                         tok_seq, block_table, max_pages, H, G, hd, rot_dim, pairing, store));
     if (dtype == PLM_BF16)
-        return plm_status_of(launch_pdl(rope_store_kernel<bf16, bf16>, grid_rs, nt, 0, stream, qkv, qkv_splits,
-                                        (size_t)qkv_stride, (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos,
+        return plm_status_of(launch_pdl(rope_store_kernel<bf16, bf16>, grid_rs, nt, 0, stream, (const bf16*)qkv,
+                                        (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos,
                                         tok_seq, block_table, max_pages, H, G, hd, rot_dim, pairing, store));
     return PLM_ERR_DTYPE;
 }

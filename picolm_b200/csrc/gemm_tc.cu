@@ -383,31 +383,6 @@ extern "C" int plm_gemm_tc_wide_swiglu(const void* x, const void* w, void* out, 
     return launch<128, false, bf16, 1>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
 }
 
-// The split products only: `workspace` receives `splits` partial sums [T, F] in fp32 (splits as
-// reported by plm_gemm_tc_plan; a single one is the whole product), for a consumer that adds them
-// up itself.  Skinny problems (T <= 64) only.
-extern "C" int plm_gemm_tc_partials(const void* x, const void* w, int T, int F, int K, long ldx, long ldw,
-                                    float* workspace, int* status, cudaStream_t stream) {
-    if (T <= 0 || F <= 0) return PLM_OK;
-    if (T > 64) return PLM_ERR_UNSUPPORTED;
-    if (!plm_gemm_tc_supported(x, w, T, F, K, ldx, ldw)) return PLM_ERR_ALIGN;
-    if (!workspace) return PLM_ERR_SHAPE;
-    int splits;
-    long ws_elems;
-    plm_gemm_tc_plan(T, F, K, &splits, &ws_elems);
-    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
-    const int n_kb = (K + BK - 1) / BK;
-    const int per = (n_kb + splits - 1) / splits;
-    CUtensorMap mp, mq;
-    int rc;
-    if ((rc = make_map(&mp, w, F, K, ldw, BM)) != PLM_OK) return rc;
-    if ((rc = make_map(&mq, x, T, K, ldx, bn)) != PLM_OK) return rc;
-    const long stride = (long)T * F;
-    if (bn == 16) return launch<16, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
-    if (bn == 32) return launch<32, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
-    return launch<64, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
-}
-
 // ------------------------------------------------- the entry point that allocates nothing
 // See gemm_tc_static.h for whom this is and what it costs.  The partial sums of the split-K
 // product go to this file-scope array instead of a caller-provided workspace.

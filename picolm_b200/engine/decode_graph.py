@@ -28,8 +28,18 @@ def bucket_for(n: int) -> Optional[int]:
     return None
 
 
+LENGTH_QUANTUM = 512          # sequence lengths are rounded up to this for the sizes a graph bakes in
+
+
+def length_class(max_len: int, longest: int) -> int:
+    """The length a graph is captured for: kernels that size their grids by the longest sequence
+    (how many ranges the decode attention cuts the keys into) get this instead of the true length,
+    so that a graph serves all steps until the batch's longest sequence grows past it."""
+    return min(longest, (max_len + LENGTH_QUANTUM - 1) // LENGTH_QUANTUM * LENGTH_QUANTUM)
+
+
 class DecodeGraph:
-    def __init__(self, engine, batch: int):
+    def __init__(self, engine, batch: int, max_len: int):
         self.engine = engine
         self.batch = B = batch
         cache = engine.cache
@@ -54,7 +64,7 @@ class DecodeGraph:
         self.tables_h = [self.h[7 + g].reshape(B, P) for g in range(n_groups)]
         self.step = StepBatch(
             n_seqs=B, n_tokens=B, n_want=B, slots=[0] * B, new_lens=[1] * B, start_pos=[0] * B,
-            max_position=cache.max_seq_tokens - 1,        # splits and table bounds are fixed for the longest sequence
+            max_position=max_len - 1,                     # the graph's length class (see length_class)
             is_decode=True, tok_ids=self.d[0], tok_seq=self.d[1], tok_pos=self.d[2], seq_slot=self.d[3],
             seq_start=self.d[4], seq_kv_len=self.d[5], want_rows=self.d[6],
             block_tables=[self.d[7 + g].view(B, P) for g in range(n_groups)],

@@ -49,7 +49,7 @@ class Engine:
         # work that depends on the step through device buffers (`graph_safe`).
         safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks)
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
-        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
         self.reset_counters()
 
     def reset_counters(self) -> None:
@@ -128,7 +128,7 @@ class Engine:
     def _decode_with_graph(self, entries, wants) -> Optional[torch.Tensor]:
         """One token for each sequence through the captured graph of the batch's size class.  Returns None
         if this step cannot use one (batch too large, or places wanted that are not exactly [0])."""
-        from .decode_graph import DecodeGraph, bucket_for
+        from .decode_graph import DecodeGraph, bucket_for, length_class
         n = len(entries)
         bucket = bucket_for(n)
         if bucket is None:
@@ -136,12 +136,14 @@ class Engine:
         n_want = sum(len(w) for w in wants)
         if n_want not in (0, n) or any(list(w) not in ([], [0]) for w in wants):
             return None
-        g = self._graphs.get(bucket)
-        if g is None:
-            g = DecodeGraph(self, bucket)
-            g.capture()
-            self._graphs[bucket] = g
         slots = [s for s, _ in entries]
-        logits = g.run(slots, [t[0] for _, t in entries], [self.cache.length(s) for s in slots])
+        positions = [self.cache.length(s) for s in slots]
+        key = (bucket, length_class(max(positions) + 1, self.cache.max_seq_tokens))
+        g = self._graphs.get(key)
+        if g is None:
+            g = DecodeGraph(self, key[0], key[1])
+            g.capture()
+            self._graphs[key] = g
+        logits = g.run(slots, [t[0] for _, t in entries], positions)
         self.counters["h2d_bytes"] += g.step.h2d_bytes
         return logits if n_want else None

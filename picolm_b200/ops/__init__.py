@@ -20,13 +20,11 @@ _vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 _SIGNATURES = {
     "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
-    "plm_rmsnorm": [_vp, _vp, _i, _l, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
-    "plm_swiglu_partials": [_vp, _i, _l, _vp, _i, _i, _i, _vp],
-    "plm_rope_store": [_vp, _i, _l, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_wide_swiglu": [_vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _vp, _vp],
-    "plm_gemm_tc_partials": [_vp, _vp, _i, _i, _i, _l, _l, _vp, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
     "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
@@ -44,32 +42,6 @@ class KernelError(RuntimeError):
     pass
 
 
-class PartialSums:
-    """A matrix product [T, F] that is still the sum of `splits` fp32 partial sums
-    (the K splits of the skinny tensor-core product): `parts` is [splits, T, F].
-    `rmsnorm` (as delta), `swiglu` and `rope_store` add the parts up themselves,
-    which saves the separate reduction kernel; `reduced()` gives the plain tensor."""
-
-    def __init__(self, parts: torch.Tensor, out_dtype: torch.dtype):
-        self.parts = parts
-        self.out_dtype = out_dtype
-
-    @property
-    def shape(self):
-        return self.parts.shape[1:]
-
-    @property
-    def splits(self) -> int:
-        return self.parts.shape[0]
-
-    @property
-    def stride(self) -> int:
-        return self.parts.shape[1] * self.parts.shape[2]
-
-    def reduced(self) -> torch.Tensor:
-        return self.parts.sum(dim=0).to(self.out_dtype) if self.splits > 1 else self.parts[0].to(self.out_dtype)
-
-
 _CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", -4: "unsupported option",
           -5: "the device wait ran out (see the status word)"}
 
@@ -84,11 +56,6 @@ def _fn(library: str, name: str, extra_flags=()):
         f.restype = ctypes.c_int
         _fn_cache[key] = f
     return f
-
-
-def as_tensor(x) -> torch.Tensor:
-    """A plain tensor of what `linear(..., defer_reduce=True)` returned."""
-    return x.reduced() if isinstance(x, PartialSums) else x
 
 
 _launches = 0
@@ -176,14 +143,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     T, d = x.shape
     if weight.shape != (d,):
         raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
-    d_splits, d_stride = 1, 0
-    if isinstance(delta, PartialSums):
-        d_splits, d_stride, delta = delta.splits, delta.stride, delta.parts
-        if tuple(delta.shape[1:]) != (T, d):
-            raise KernelError("delta must be shaped like x")
     if delta is not None:
         _dev(delta, "delta")
-        if delta.dtype != torch.float32 or delta.numel() != d_splits * T * d:
+        if delta.dtype != torch.float32 or delta.shape != x.shape:
             raise KernelError("delta must be float32 and shaped like x")
     n_rows = T
     if rows is not None:
@@ -192,23 +154,13 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     if out is None:
         out = torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
     _check(_fn("elementwise", "plm_rmsnorm")(
-        _p(x), _p(delta), d_splits, d_stride, _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows),
-        n_rows, d, float(eps), _stream()), "rmsnorm")
+        _p(x), _p(delta), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
+        float(eps), _stream()), "rmsnorm")
     return out
 
 
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """gate_up [T, 2F] (gate columns first) -> silu(gate) * up, [T, F]."""
-    if isinstance(gate_up, PartialSums):
-        T, F2 = gate_up.shape
-        if F2 % 2:
-            raise KernelError("gate_up must have an even number of columns")
-        if out is None:
-            out = torch.empty((T, F2 // 2), dtype=gate_up.out_dtype, device=gate_up.parts.device)
-        _check(_fn("elementwise", "plm_swiglu_partials")(
-            _p(gate_up.parts), gate_up.splits, gate_up.stride, _p(out), _dt(out, "out"), T, F2 // 2, _stream()),
-            "swiglu")
-        return out
     _dev(gate_up, "gate_up")
     T, F2 = gate_up.shape
     if F2 % 2:
@@ -228,15 +180,12 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
     """Rotate the query and key heads of `qkv` [T, (H+2G)*hd] by their tokens'
     positions; write queries to `q_out` [T, H, hd] and keys/values into the paged
     cache [pages, G, PAGE_TOKENS, hd]."""
-    q_splits, q_stride, q_dtype = 0, 0, None
-    if isinstance(qkv, PartialSums):
-        q_splits, q_stride, q_dtype, qkv = qkv.splits, qkv.stride, qkv.out_dtype, qkv.parts[0]
     _dev(qkv, "qkv")
     _dev(q_out, "q_out")
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
     T = qkv.shape[0]
     H, G, hd = num_heads, num_kv_heads, head_dim
-    if qkv.shape[1] != (H + 2 * G) * hd or q_out.shape != (T, H, hd) or q_out.dtype != (q_dtype or qkv.dtype):
+    if qkv.shape[1] != (H + 2 * G) * hd or q_out.shape != (T, H, hd) or q_out.dtype != qkv.dtype:
         raise KernelError("rope_store: qkv / q_out shapes do not match the head counts")
     if store:
         for c, n in ((k_cache, "k_cache"), (v_cache, "v_cache")):
@@ -250,8 +199,7 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
     if pairing not in ("half", "adjacent"):
         raise KernelError(f"rope_store: unknown pairing {pairing!r}")
     _check(_fn("elementwise", "plm_rope_store")(
-        _p(qkv), q_splits, q_stride, _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None,
-        _dt(q_out, "q_out"),
+        _p(qkv), _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None, _dt(qkv, "qkv"),
         _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1], T, H, G, hd,
         rotary_dim, 0 if pairing == "half" else 1, 1 if store else 0, _stream()), "rope_store")
 
@@ -383,21 +331,6 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def gemm_tc_partials(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> PartialSums:
-    """The skinny tensor-core product (M <= 64) left as its K splits' partial sums."""
-    _dev(a, "a"), _dev(w, "w")
-    M, K = a.shape
-    N = w.shape[0]
-    if M > 64 or not gemm_tc_supported(a, w):
-        raise KernelError("gemm_tc_partials: needs a supported bfloat16 problem with at most 64 rows")
-    splits, ws_elems = ctypes.c_int(0), ctypes.c_long(0)
-    _fn("gemm_tc", "plm_gemm_tc_plan")(M, N, K, ctypes.byref(splits), ctypes.byref(ws_elems))
-    parts = torch.empty((splits.value, M, N), dtype=torch.float32, device=a.device)
-    _check(_fn("gemm_tc", "plm_gemm_tc_partials")(
-        _p(a), _p(w), M, N, K, K, K, _p(parts), _p(status_word(a.device)), _stream()), "gemm_tc_partials")
-    return PartialSums(parts, out_dtype)
-
-
 # ------------------------------------------------------------------ attention
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                    tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
@@ -459,12 +392,16 @@ _SM_COUNT = 148
 
 
 def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """Into how many ranges the decode kernel cuts each sequence's keys: enough
-    CTAs to keep every SM pulling from HBM, at least one page per range."""
+    """Into how many ranges the decode kernel cuts each sequence's keys: about
+    eight pages a range (measured best at batch 8 and 64), more ranges when that
+    leaves SMs without a CTA, never less than two pages a range."""
     row_groups = (num_heads // num_kv_heads + 15) // 16
     ctas = max(1, n_tokens * num_kv_heads * row_groups)
     pages = max(1, (max_kv_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
-    return max(1, min(pages, (4 * _SM_COUNT + ctas - 1) // ctas))
+    splits = (pages + 7) // 8
+    if ctas * splits < _SM_COUNT:
+        splits = max(splits, min(max(1, pages // 2), (_SM_COUNT + ctas - 1) // ctas))
+    return max(1, min(pages, splits))
 
 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
@@ -518,11 +455,11 @@ def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, to
 
 
 # ---------------------------------------------------------------- dispatchers
-def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, defer_reduce: bool = False):
+def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
-    types and shape, never by the model.  With `defer_reduce` the result may come
-    back as `PartialSums` for a consumer that adds the K splits up itself
-    (`rmsnorm`'s delta, `swiglu`, `rope_store`)."""
+    types and shape, never by the model: the tensor cores for bfloat16 operands
+    that TMA can address (the cluster kernel for up to 64 rows, the wide kernel
+    beyond), the CUDA cores for everything else."""
     if gemm_tc_supported(a, w):
         if a.shape[0] <= 64:
             return gemm_tc_skinny(a, w, out_dtype)

@@ -67,7 +67,7 @@ def test_feed_forward_part(dtype):
     w = {n: (torch.randn(s.shape) * 0.1).to(DT[dtype]) for n, s in specs.items()}
     ff.load({n: t.to(DEV) for n, t in w.items()})
     h = torch.randn(11, d).to(DT[dtype])
-    out = ops.as_tensor(ff.forward(h.to(DEV), None))
+    out = ff.forward(h.to(DEV), None)
     assert out.dtype == torch.float32
     rnd = (lambda t: t.to(DT[dtype]).float())
     gate, up = rnd(P.linear(h.float(), w["g.weight"].float())), rnd(P.linear(h.float(), w["u.weight"].float()))
@@ -107,7 +107,7 @@ def test_attention_part_with_rope_options(dtype, pairing):
     g = cache.kv_groups[0]
     view = KVLayerCache(g.k[0], g.v[0], step.block_tables[0], None, True)
     h = torch.randn(sum(lens), d).to(DT[dtype])
-    out = ops.as_tensor(mixer.forward(h.to(DEV), step, view)).cpu()
+    out = mixer.forward(h.to(DEV), step, view).cpu()
     rnd = (lambda t: t.to(DT[dtype]).float())
     cos, sin = P.rope_table(max(lens), rot, 777.0, scaling)
     cos, sin = cos.float(), sin.float()
