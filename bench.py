@@ -144,6 +144,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 decode points")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch every kernel of a decode step by itself (for a profiler's launch list)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -175,7 +177,7 @@ def main():
         t0 = time.time()
         write_random_model(cfg, seed, tmp, norm_std=0.0)
         engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * context, max_seqs=max_b,
-                                    max_seq_tokens=context)
+                                    max_seq_tokens=context, use_graphs=False if args.no_graphs else None)
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr)
     g = torch.Generator().manual_seed(seed)
     vocab = cfg.vocab_size

@@ -72,9 +72,74 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// Four elements at a time, the row kept in registers between the two passes: for rows whose width
+// is a multiple of 4 and at most 16 * NT.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename Tw, typename To, int NT>
+__global__ void __launch_bounds__(NT)
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const Tw* __restrict__ w,
+                   To* __restrict__ out, const int* __restrict__ rows, int d, float eps, int write_back) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* xr = x + (size_t)src * d;
+    const float* dr = delta ? delta + (size_t)src * d : nullptr;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            v[k] = load4(xr + i);
+            if (dr) {
+                const float4 dv = load4(dr + i);
+                v[k].x += dv.x; v[k].y += dv.y; v[k].z += dv.z; v[k].w += dv.w;
+                if (write_back) store4(xr + i, v[k]);
+            }
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum<NT>(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    To* o = out + (size_t)r * d;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            const float4 wv = load4(w + i);
+            store4(o + i, make_float4(v[k].x * scale * wv.x, v[k].y * scale * wv.y, v[k].z * scale * wv.z,
+                                      v[k].w * scale * wv.w));
+        }
+    }
+}
+
 template <typename Tw, typename To>
 static int rmsnorm_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows, int d,
                           float eps, int write_back, cudaStream_t stream) {
+    if (d % 4 == 0 && d <= 16 * 1024) {
+        // the block size (and with it the order of the sum of squares) depends on the row's width only
+        if (d <= 16 * 256)
+            return plm_status_of(launch_pdl(rmsnorm_vec_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta,
+                                            (const Tw*)w, (To*)out, rows, d, eps, write_back));
+        return plm_status_of(launch_pdl(rmsnorm_vec_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta,
+                                        (const Tw*)w, (To*)out, rows, d, eps, write_back));
+    }
     // enough threads that a row's loads are all in flight at once; the block size (and with it the
     // order of the sum of squares) depends on the row's width only
     if (d > 1024)
@@ -202,6 +267,62 @@ __global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q
     }
 }
 
+// The common case eight pairs at a time: bf16, the whole head rotated (rot_dim == hd), half-split
+// pairing, head size a multiple of 16.  A thread takes x[j..j+8) and x[half+j..half+j+8) of one head
+// as two 16-byte loads and writes two 16-byte stores.
+__global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ kc,
+                                      bf16* __restrict__ vc, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                      int max_pages, int H, int G, int hd, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd / 2, groups = half / 8;
+    const int n_heads = H + 2 * G;
+    const bf16* row = qkv + (size_t)t * n_heads * hd;
+    size_t page_base = 0;
+    int in_page = 0;
+    bool have_page = false;
+    if (store) {
+        const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / PLM_PAGE];
+        have_page = page >= 0;
+        page_base = (size_t)(page < 0 ? 0 : page) * G;
+        in_page = pos % PLM_PAGE;
+    }
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_heads * groups; item += gridDim.y * blockDim.x) {
+        const int head = item / groups, j = (item - head * groups) * 8;
+        bf16* dst;
+        if (head < H) {
+            dst = q_out + ((size_t)t * H + head) * hd;
+        } else {
+            if (!store || !have_page) continue;
+            const int g = head < H + G ? head - H : head - H - G;
+            dst = (head < H + G ? kc : vc) + ((page_base + g) * PLM_PAGE + in_page) * hd;
+        }
+        uint4 lo = *reinterpret_cast<const uint4*>(row + head * hd + j);
+        uint4 hi = *reinterpret_cast<const uint4*>(row + head * hd + half + j);
+        if (head < H + G) {
+            const float4 c0 = load4(cos_t + (size_t)pos * half + j), c1 = load4(cos_t + (size_t)pos * half + j + 4);
+            const float4 s0 = load4(sin_t + (size_t)pos * half + j), s1 = load4(sin_t + (size_t)pos * half + j + 4);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a0 = __low2float(l2[k]), a1 = __high2float(l2[k]);
+                const float b0 = __low2float(h2[k]), b1 = __high2float(h2[k]);
+                l2[k] = __floats2bfloat162_rn(a0 * c[2 * k] - b0 * sn[2 * k], a1 * c[2 * k + 1] - b1 * sn[2 * k + 1]);
+                h2[k] = __floats2bfloat162_rn(a0 * sn[2 * k] + b0 * c[2 * k], a1 * sn[2 * k + 1] + b1 * c[2 * k + 1]);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + j) = lo;
+        *reinterpret_cast<uint4*>(dst + half + j) = hi;
+    }
+}
+
 extern "C" int plm_rope_store(const void* qkv, void* q_out, void* kc, void* vc, int dtype, const float* cos_t,
                               const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
                               int max_pages, int n_tokens, int H, int G, int hd, int rot_dim, int pairing, int store,
@@ -209,6 +330,14 @@ extern "C" int plm_rope_store(const void* qkv, void* q_out, void* kc, void* vc, 
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || hd <= 0 || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return PLM_ERR_SHAPE;
     if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
+    if (dtype == PLM_BF16 && pairing == 0 && rot_dim == hd && hd % 16 == 0 && cos_t != nullptr) {
+        const int vitems = (H + 2 * G) * (hd / 16);
+        int vchunks = (vitems + 127) / 128;
+        if (vchunks > 64) vchunks = 64;
+        return plm_status_of(launch_pdl(rope_store_vec_kernel, dim3(n_tokens, vchunks), dim3(128), 0, stream,
+                                        (const bf16*)qkv, (bf16*)q_out, (bf16*)kc, (bf16*)vc, cos_t, sin_t, tok_pos,
+                                        tok_seq, block_table, max_pages, H, G, hd, store));
+    }
     const int items = (H + 2 * G) * (hd / 2);
     const int nt_threads = items >= 128 ? 128 : 64;
     int chunks = (items + nt_threads - 1) / nt_threads;
