@@ -57,8 +57,8 @@ def bench_gemm(args):
     from . import ops
     M, N, K = args.m, args.n, args.k
     w_bytes = N * K * 2
-    copies = max(2, math.ceil(2 * L2_BYTES / w_bytes))
-    ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(min(copies, 24))]
+    copies = args.copies or min(24, max(2, math.ceil(2 * L2_BYTES / w_bytes)))
+    ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(copies)]
     a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
 
@@ -110,8 +110,10 @@ def bench_attention_prefill(args):
     start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
     kvlen = torch.tensor([T], dtype=torch.int32, device="cuda")
 
+    fn = ops.attention_prefill_tc if (ops.attention_tc_supported(q) and not args.mma) else ops.attention_prefill
+
     def run(i):
-        ops.attention_prefill(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
+        fn(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
 
     sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     flops = 2.0 * 2 * H * hd * T * (T + 1) / 2
@@ -133,6 +135,9 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
+    ap.add_argument("--copies", type=int, default=0,
+                    help="gemm: weight copies to rotate through (default: enough to exceed L2; 1 keeps them in L2)")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--once", action="store_true", help="one launch, no warm-up (for a profiler)")

@@ -1,0 +1,336 @@
+// Causal prefill attention over the paged cache on the fifth-generation tensor
+// cores, compiled for one head size (-DPLM_HD = 64 or 128).
+//
+// One CTA takes 128 query tokens of one head and walks that sequence's pages of
+// 64 keys.  Per page:
+//   S = Q K^T      tcgen05.mma, Q and K in shared memory (TMA, 128-byte swizzle), S in TMEM
+//   softmax        one thread per query row: tcgen05.ld its 64 scores, scale, mask, running
+//                  max / sum in fp32 (the recurrence of picolm/model_attention.c:43-140 taken a
+//                  page at a time), probabilities back to TMEM as bf16 (tcgen05.st)
+//   O += P V       tcgen05.mma with P from TMEM and V in shared memory (MN-major), the page's
+//                  product in TMEM; the thread adds it to its row of O in registers, rescaled
+// Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
+// 128 softmax threads.  With head size 64 the scores have two TMEM buffers, so the next page's
+// Q K^T runs while this page's softmax does.  Keys of a KV head are shared by its query heads
+// through L2 (consecutive CTAs work on the heads of one group).
+//
+// Waits on mbarriers are bounded as in gemm_tc.cu: a wait that runs out records where in
+// `status`, the CTA stops issuing work, lets what is in flight land, frees its TMEM and returns.
+#include "tc_common.cuh"
+
+#ifndef PLM_HD
+#define PLM_HD 64
+#endif
+
+using namespace plm_tc;
+
+namespace {
+
+constexpr int HD = PLM_HD;
+static_assert(HD == 64 || HD == 128, "the tcgen05 attention is built for head sizes 64 and 128");
+constexpr int CB = HD / 64;                       // 64-column blocks of a row (one 128-byte swizzle span each)
+constexpr int BQ = 128, BKV = 64;
+constexpr int STAGES = HD == 64 ? 3 : 2;
+constexpr int NSB = HD == 64 ? 2 : 1;             // score buffers in TMEM
+constexpr uint32_t Q_BLOCK = BQ * 128, KV_BLOCK = BKV * 128;       // bytes of one 64-column block
+constexpr uint32_t Q_BYTES = CB * Q_BLOCK, K_BYTES = CB * KV_BLOCK, V_BYTES = K_BYTES;
+constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
+constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = TM_P + 32, TMEM_COLS = 256;
+static_assert(TM_PV + HD <= TMEM_COLS, "TMEM budget");
+constexpr size_t SMEM = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// V tile [64 keys][64 columns] per block, 128-byte rows with TMA's 128-byte swizzle, used as the B
+// operand with N (the head's columns) contiguous: MN-major.  8-key groups are 1024 bytes apart
+// (stride offset), 64-column blocks KV_BLOCK bytes apart (leading offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(KV_BLOCK >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// D fp32, A and B bf16, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BQ >> 4) << 24);
+}
+
+// grid = (query tiles of the longest sequence, heads, sequences)
+__global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
+attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                       const int* __restrict__ seq_start, const int* __restrict__ seq_kv_len,
+                       const int* __restrict__ block_table, int max_pages, int H, int G, float scale_log2, int window,
+                       int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
+    const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
+    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * STAGES,
+                   s_full0 = kv_empty0 + 8 * STAGES, p_ready = s_full0 + 8 * NSB, pv_full = p_ready + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (pv_full + 8 - raw));
+    __shared__ int s_abort;
+
+    pdl_launch_dependents();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t0 = seq_start[b], n_new = seq_start[b + 1] - t0;          // inputs written before the step began
+    const int n_tiles = (n_new + BQ - 1) / BQ;
+    if ((int)blockIdx.x >= n_tiles) return;
+    const int tile = n_tiles - 1 - blockIdx.x;                          // the longest tiles first
+    const int kv_len = seq_kv_len[b];
+    const int pos0 = kv_len - n_new + tile * BQ;                         // position of the tile's first row
+    const int rows = min(BQ, n_new - tile * BQ);
+    const int g = h / (H / G);
+    const int pos_last = pos0 + rows - 1;
+    const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int page_first = first_key / BKV, page_last = pos_last / BKV;
+    const int n_pages = page_last - page_first + 1;
+    const int* pages = block_table + (size_t)b * max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int s = 0; s < NSB; ++s) mbar_init(s_full0 + 8 * s, 1);
+        mbar_init(p_ready, 128);
+        mbar_init(pv_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            pdl_wait();                                                  // q and the new keys come from the kernel before
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int cb = 0; cb < CB; ++cb)
+                tma_load_2d(q_smem + cb * Q_BLOCK, &map_q, q_full, h * HD + cb * 64, t0 + tile * BQ);
+            int issued = 0;
+            for (int i = 0; i < n_pages; ++i) {
+                const int s = i % STAGES;
+                if (*(volatile int*)&s_abort) break;
+                if (!mbar_wait(kv_empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; break; }
+                mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
+                const int row = (pages[page_first + i] * G + g) * BKV;
+                const uint32_t k_dst = kv_smem + s * STAGE_BYTES, v_dst = k_dst + K_BYTES;
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb) {
+                    tma_load_2d(k_dst + cb * KV_BLOCK, &map_k, kv_full0 + 8 * s, cb * 64, row);
+                    tma_load_2d(v_dst + cb * KV_BLOCK, &map_v, kv_full0 + 8 * s, cb * 64, row);
+                }
+                issued = i + 1;
+            }
+            if (*(volatile int*)&s_abort) {
+                mbar_wait(q_full, 0, nullptr, 0);
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    mbar_wait(kv_full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(BKV, false), idesc_o = instr_desc(HD, true);
+            auto qk = [&](int i) {                                       // S[i % NSB] = Q K(i)^T
+                const uint32_t k_smem = kv_smem + (i % STAGES) * STAGE_BYTES;
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_bf16(tmem + TM_S + (i % NSB) * 64,
+                                    smem_desc_sw128(q_smem + cb * Q_BLOCK) + (uint64_t)(k * 2),
+                                    smem_desc_sw128(k_smem + cb * KV_BLOCK) + (uint64_t)(k * 2), idesc_s,
+                                    (cb > 0 || k > 0) ? 1u : 0u);
+                tc_commit(s_full0 + 8 * (i % NSB));
+            };
+            bool ok = mbar_wait(q_full, 0, status, 2);
+            if (ok && NSB == 2) {
+                ok = mbar_wait(kv_full0, 0, status, 2);
+                if (ok) { tc_fence_after(); qk(0); }
+            }
+            for (int i = 0; i < n_pages && ok; ++i) {
+                if (*(volatile int*)&s_abort) { ok = false; break; }
+                const int nxt = NSB == 2 ? i + 1 : i;                    // the Q K^T to issue now
+                if (nxt < n_pages && (NSB == 1 || nxt > 0)) {
+                    if (!mbar_wait(kv_full0 + 8 * (nxt % STAGES), (nxt / STAGES) & 1, status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    qk(nxt);
+                }
+                if (!mbar_wait(p_ready, i & 1, status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t v_smem = kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)                       // O_page = P V(i), 16 keys a step
+                    tc_mma_bf16_ts(tmem + TM_PV, tmem + TM_P + k * 8, smem_desc_sw128_mn(v_smem + k * 2048), idesc_o,
+                                   k > 0 ? 1u : 0u);
+                tc_commit(pv_full);
+                tc_commit(kv_empty0 + 8 * (i % STAGES));
+            }
+            if (!ok) s_abort = 1;
+        }
+    } else {
+        // ----------------------------------------------------------------- softmax
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                               // this thread's query row
+        const int pos = r < rows ? pos0 + r : -1;                        // -1: no such row, everything masked
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_pages && ok; ++i) {
+            if (!mbar_wait(s_full0 + 8 * (i % NSB), (i / NSB) & 1, status, 3)) { ok = false; break; }
+            tc_fence_after();
+            const int key0 = (page_first + i) * BKV;
+            const bool need_mask = key0 + BKV - 1 > pos0 || key0 < (window > 0 ? pos_last - window + 1 : 0);
+            float mx = -INFINITY;
+            uint32_t s0[32], s1[32];
+            tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64, s0);
+            tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64 + 32, s1);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float a = __uint_as_float(s0[j]) * scale_log2, c = __uint_as_float(s1[j]) * scale_log2;
+                if (need_mask) {
+                    const int ka = key0 + j, kc2 = key0 + 32 + j;
+                    if (ka > pos || ka < lo) a = -INFINITY;
+                    if (kc2 > pos || kc2 < lo) c = -INFINITY;
+                } else if (pos < 0) {
+                    a = -INFINITY; c = -INFINITY;
+                }
+                s0[j] = __float_as_uint(a);
+                s1[j] = __float_as_uint(c);
+                mx = fmaxf(mx, fmaxf(a, c));
+            }
+            const float m_new = fmaxf(m, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m - m_use);
+            m = m_new;
+            float sum = 0.f;
+            uint32_t p[32];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float a0 = exp2f(__uint_as_float(s0[2 * j]) - m_use), a1 = exp2f(__uint_as_float(s0[2 * j + 1]) - m_use);
+                const float c0 = exp2f(__uint_as_float(s1[2 * j]) - m_use), c1 = exp2f(__uint_as_float(s1[2 * j + 1]) - m_use);
+                sum += (a0 + a1) + (c0 + c1);
+                __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pc = __floats2bfloat162_rn(c0, c1);
+                p[j] = *reinterpret_cast<uint32_t*>(&pa);               // keys 2j, 2j+1
+                p[16 + j] = *reinterpret_cast<uint32_t*>(&pc);          // keys 32+2j, 32+2j+1
+            }
+            l = l * alpha + sum;
+            tc_st32(tmem + lane_bits + TM_P, p);
+            tc_wait_st();
+            // places of the sequence's last page that hold no key yet: zero those rows of V, so that
+            // whatever an earlier owner of the page left there cannot reach the sum (0 * NaN)
+            const int valid = kv_len - key0;
+            if (valid < BKV) {
+                ok = mbar_wait(kv_full0 + 8 * (i % STAGES), (i / STAGES) & 1, status, 3);
+                uint8_t* v_ptr = smem_raw + (kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES - raw);
+                for (int idx = (int)threadIdx.x - 64; idx < (BKV - valid) * CB * 8; idx += 128) {
+                    const int row = valid + idx / (CB * 8), rest = idx % (CB * 8);
+                    *reinterpret_cast<uint4*>(v_ptr + (rest / 8) * KV_BLOCK + row * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            tc_fence_before();
+            mbar_arrive(p_ready);
+            if (!ok) break;
+            if (!mbar_wait(pv_full, i & 1, status, 3)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t pv[32];
+                tc_ld32(tmem + lane_bits + TM_PV + c, pv);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * alpha + __uint_as_float(pv[j]);
+            }
+        }
+        if (!ok) s_abort = 1;
+        if (ok && r < rows) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + ((size_t)(t0 + tile * BQ + r) * H + h) * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 v2 = __floats2bfloat162_rn(o[d + 2 * j] * inv, o[d + 2 * j + 1] * inv);
+                    w[j] = *reinterpret_cast<uint32_t*>(&v2);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+extern "C" int plm_attn_tc_head_dim() { return HD; }
+
+// q [T, H, HD] bf16, k/v cache [n_pages, G, 64, HD] bf16, out [T, H*HD] bf16.  seq_start [B+1]:
+// offsets of each sequence's new tokens; seq_kv_len [B]: its length after the step; max_new: the most
+// new tokens of a sequence.  `status`: a device int that stays 0 unless a bounded wait ran out.
+extern "C" int plm_attn_tc_prefill(const void* q, const void* kc, const void* vc, void* out, const int* seq_start,
+                                   const int* seq_kv_len, const int* block_table, int max_pages, int n_pages,
+                                   int n_tokens, int n_seqs, int max_new, int H, int G, float scale, int window,
+                                   int* status, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0 || n_tokens <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || H % G || n_seqs > 65535 || H > 65535) return PLM_ERR_SHAPE;
+    if ((((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out)) & 15) return PLM_ERR_ALIGN;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map(&mq, q, n_tokens, (long)H * HD, (long)H * HD, BQ)) != PLM_OK) return rc;
+    if ((rc = make_map(&mk, kc, (long)n_pages * G * BKV, HD, HD, BKV)) != PLM_OK) return rc;
+    if ((rc = make_map(&mv, vc, (long)n_pages * G * BKV, HD, HD, BKV)) != PLM_OK) return rc;
+    dim3 grid((max_new + BQ - 1) / BQ, H, n_seqs);
+    return plm_status_of(launch_pdl(attn_tc_prefill_kernel, grid, dim3(NUM_THREADS), SMEM, stream, mq, mk, mv, (bf16*)out,
+                                    seq_start, seq_kv_len, block_table, max_pages, H, G, scale * LOG2E, window, status));
+}

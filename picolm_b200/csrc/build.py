@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_tc_skinny": ["gemm_tc_skinny.cu"],
     "attention_simt": ["attention_simt.cu"],
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
+    "attention_tc": ["attention_tc.cu"],            # likewise, head sizes 64 and 128
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
@@ -45,12 +46,13 @@ HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
 # model needs is built (`attention_variant`); the build check builds these.
 VARIANTS: Dict[str, Dict[str, List[str]]] = {
     "attention_mma": {f"hd{hd}": [f"-DPLM_HD={hd}"] for hd in (64, 128)},
+    "attention_tc": {f"hd{hd}": [f"-DPLM_HD={hd}"] for hd in (64, 128)},
 }
 
 
-def attention_variant(head_dim: int):
-    """(library name, extra flags) of the tensor-core attention for a head size."""
-    return f"attention_mma@hd{head_dim}", [f"-DPLM_HD={head_dim}"]
+def attention_variant(head_dim: int, family: str = "attention_mma"):
+    """(library name, extra flags) of a tensor-core attention library for a head size."""
+    return f"{family}@hd{head_dim}", [f"-DPLM_HD={head_dim}"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "plm_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _l, _l],
     "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
@@ -388,6 +389,31 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     return out
 
 
+def attention_tc_supported(q: torch.Tensor) -> bool:
+    """The tcgen05 prefill attention takes bfloat16 and head sizes 64 and 128."""
+    return q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+
+
+def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
+                         seq_kv_len: torch.Tensor, block_table: torch.Tensor, max_new: int, num_kv_heads: int,
+                         scale: float, window: Optional[int] = None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`attention_prefill` on the tcgen05 tensor cores (scores and the page's output in tensor memory,
+    operands by TMA): same arguments, same result up to rounding; head sizes 64 and 128."""
+    T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
+    if not attention_tc_supported(q):
+        raise KernelError(f"attention_prefill_tc: head_dim {hd} of {q.dtype} is not supported (bfloat16, 64 or 128)")
+    _i32(seq_start, "seq_start"), _i32(seq_kv_len, "seq_kv_len"), _i32(block_table, "block_table")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    lib, flags = attention_variant(hd, "attention_tc")
+    _check(_fn(lib, "plm_attn_tc_prefill", flags)(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
+        block_table.shape[1], k_cache.shape[0], T, seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale),
+        int(window or 0), _p(status_word(q.device)), _stream()), "attention_prefill_tc")
+    return out
+
+
 _SM_COUNT = 148
 
 
@@ -475,7 +501,8 @@ def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> tor
             splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1)
             return attention_decode(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                                     splits, window=kv.window)
-        return attention_prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table,
-                                 max(step.new_lens), num_kv_heads, scale, window=kv.window)
+        prefill = attention_prefill_tc if attention_tc_supported(q) else attention_prefill
+        return prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table, max(step.new_lens),
+                       num_kv_heads, scale, window=kv.window)
     return attention_rows(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                           window=kv.window)

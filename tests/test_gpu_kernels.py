@@ -434,3 +434,34 @@ def test_linear_swiglu_fused(M, F, K):
     assert out.shape == (M, F) and out.dtype == torch.bfloat16
     # a gate or up value that sits on a bf16 rounding boundary may round the other way: allow one such step
     assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("window", [None, 90])
+@pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (32, 1, 128), (6, 3, 64), (4, 4, 128)])
+def test_attention_prefill_tcgen05(H, G, hd, window):
+    """The tcgen05 prefill attention in the same ragged setting as the mma.sync kernel: whole prompts, a
+    one-token sequence, a chunk after a cached prefix, lengths that straddle pages and 128-row query
+    tiles, a last page that is partly unwritten (NaN there must not reach the result), a far key that
+    carries a row, and a window's edge."""
+    from picolm_b200 import ops
+    lens, new = [300, 1, 65, 130, 64, 520], [70, 1, 65, 130, 3, 520]
+    ks, vs, qs = _attn_case(H, G, hd, lens, new, H * 11 + hd)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attn_ref(ks, vs, qs, lens, new, H, hd, scale, window)
+    kc, vc, table = _paged(ks, vs, lens, 30, torch.bfloat16, 17)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    args = (torch.cat(qs).to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV),
+            torch.tensor(starts, dtype=torch.int32, device=DEV), torch.tensor(lens, dtype=torch.int32, device=DEV),
+            table.to(DEV), max(new), G, scale)
+    out = ops.attention_prefill_tc(*args, window=window)
+    ops.check_status(DEV)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    mma = ops.attention_prefill(*args, window=window)
+    assert torch.allclose(out.float(), mma.float(), atol=3e-2, rtol=3e-2)
+    if window is None:
+        row = out.float().cpu()[new[0] - 1].reshape(H, hd)
+        for h in range(H):
+            assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
