@@ -7,8 +7,9 @@
 //   softmax        one thread per query row: tcgen05.ld its 64 scores, scale, mask, running
 //                  max / sum in fp32 (the recurrence of picolm/model_attention.c:43-140 taken a
 //                  page at a time), probabilities back to TMEM as bf16 (tcgen05.st)
-//   O += P V       tcgen05.mma with P from TMEM and V in shared memory (MN-major), the page's
-//                  product in TMEM; the thread adds it to its row of O in registers, rescaled
+//   O += P V       tcgen05.mma with P from TMEM and V in shared memory (MN-major), accumulating in
+//                  TMEM across pages; O is rescaled only when a row's maximum has outgrown the
+//                  reference it is kept against by a factor of 256
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
 // 128 softmax threads.  With head size 64 the scores have two TMEM buffers, so the next page's
 // Q K^T runs while this page's softmax does.  Keys of a KV head are shared by its query heads
@@ -35,11 +36,34 @@ constexpr int NSB = HD == 64 ? 2 : 1;             // score buffers in TMEM
 constexpr uint32_t Q_BLOCK = BQ * 128, KV_BLOCK = BKV * 128;       // bytes of one 64-column block
 constexpr uint32_t Q_BYTES = CB * Q_BLOCK, K_BYTES = CB * KV_BLOCK, V_BYTES = K_BYTES;
 constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = TM_P + 32, TMEM_COLS = 256;
+constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = TM_P + 2 * 32, TMEM_COLS = 256;      // two P buffers
 static_assert(TM_PV + HD <= TMEM_COLS, "TMEM budget");
 constexpr size_t SMEM = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Latency-critical waits (a handoff per page between the MMA issuer and the softmax threads): poll
+// with test_wait, which returns at once, instead of try_wait, which may park the thread for a while.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, int* status, int where) {
+    for (uint32_t i = 0; i < (1u << 26); ++i)
+        if (mbar_test(bar, parity)) return true;
+    if (status) atomicCAS(status, 0, where);
+    return false;
+}
+// 2^x by the special-function unit; 2^(-inf) = 0
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -78,7 +102,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn) {
 }
 
 // grid = (query tiles of the longest sequence, heads, sequences)
-__global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_kv_len,
@@ -90,8 +114,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
     const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * STAGES,
-                   s_full0 = kv_empty0 + 8 * STAGES, p_ready = s_full0 + 8 * NSB, pv_full = p_ready + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (pv_full + 8 - raw));
+                   s_full0 = kv_empty0 + 8 * STAGES, p_ready = s_full0 + 8 * NSB, pv_full0 = p_ready + 8;   // pv_full[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (pv_full0 + 16 - raw));
     __shared__ int s_abort;
 
     pdl_launch_dependents();
@@ -117,7 +141,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < NSB; ++s) mbar_init(s_full0 + 8 * s, 1);
         mbar_init(p_ready, 128);
-        mbar_init(pv_full, 1);
+        mbar_init(pv_full0, 1);
+        mbar_init(pv_full0 + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -188,14 +213,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tc_fence_after();
                     qk(nxt);
                 }
-                if (!mbar_wait(p_ready, i & 1, status, 2)) { ok = false; break; }
+                if (!mbar_spin(p_ready, i & 1, status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_smem = kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES;
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k)                       // O_page = P V(i), 16 keys a step
-                    tc_mma_bf16_ts(tmem + TM_PV, tmem + TM_P + k * 8, smem_desc_sw128_mn(v_smem + k * 2048), idesc_o,
-                                   k > 0 ? 1u : 0u);
-                tc_commit(pv_full);
+                    tc_mma_bf16_ts(tmem + TM_PV, tmem + TM_P + (i & 1) * 32 + k * 8,
+                                   smem_desc_sw128_mn(v_smem + k * 2048), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(pv_full0 + 8 * (i & 1));                     // P buffer i % 2 is free, O holds pages 0..i
                 tc_commit(kv_empty0 + 8 * (i % STAGES));
             }
             if (!ok) s_abort = 1;
@@ -207,13 +232,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int pos = r < rows ? pos0 + r : -1;                        // -1: no such row, everything masked
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        // O stays in tensor memory and the MMAs accumulate into it across pages.  Probabilities are
+        // taken relative to a reference maximum m_ref that is raised (and O rescaled) only when a
+        // row's maximum outgrows it by more than 2^RESCALE_LOG2, so most pages need no pass over O.
+        constexpr float RESCALE_LOG2 = 8.f;
+        float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_pages && ok; ++i) {
-            if (!mbar_wait(s_full0 + 8 * (i % NSB), (i / NSB) & 1, status, 3)) { ok = false; break; }
+            if (!mbar_spin(s_full0 + 8 * (i % NSB), (i / NSB) & 1, status, 3)) { ok = false; break; }
             tc_fence_after();
             const int key0 = (page_first + i) * BKV;
             const bool need_mask = key0 + BKV - 1 > pos0 || key0 < (window > 0 ? pos_last - window + 1 : 0);
@@ -222,37 +248,58 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64, s0);
             tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64 + 32, s1);
             tc_wait_ld();
+            if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                float a = __uint_as_float(s0[j]) * scale_log2, c = __uint_as_float(s1[j]) * scale_log2;
-                if (need_mask) {
+                for (int j = 0; j < 32; ++j) {
                     const int ka = key0 + j, kc2 = key0 + 32 + j;
-                    if (ka > pos || ka < lo) a = -INFINITY;
-                    if (kc2 > pos || kc2 < lo) c = -INFINITY;
-                } else if (pos < 0) {
-                    a = -INFINITY; c = -INFINITY;
+                    if (ka > pos || ka < lo) s0[j] = 0xff800000u;        // -inf
+                    if (kc2 > pos || kc2 < lo) s1[j] = 0xff800000u;
                 }
-                s0[j] = __float_as_uint(a);
-                s1[j] = __float_as_uint(c);
-                mx = fmaxf(mx, fmaxf(a, c));
+            } else if (pos < 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { s0[j] = 0xff800000u; s1[j] = 0xff800000u; }
             }
-            const float m_new = fmaxf(m, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m - m_use);
-            m = m_new;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[j]), __uint_as_float(s1[j])));
+            // the scale is positive, so the maximum of the scaled scores is the scaled maximum
+            const float m_cand = fmaxf(m_ref, mx * scale_log2);
+            const bool raise = m_cand > m_ref + RESCALE_LOG2 || (m_ref == -INFINITY && m_cand > -INFINITY);
+            // P has two buffers: page i writes the one that page i - 2 used, whose P V must be done
+            if (i > 1 && !mbar_spin(pv_full0 + 8 * (i & 1), ((i - 2) >> 1) & 1, status, 3)) { ok = false; break; }
+            if (__any_sync(0xffffffffu, raise)) {                        // tcgen05.ld/st are warp-wide
+                const float alpha = raise ? ex2(m_ref - m_cand) : 1.f;   // m_ref = -inf gives 0
+                if (i > 0) {
+                    // O may only be touched once every P V issued so far has landed in it
+                    if (!mbar_spin(pv_full0 + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, status, 3)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t ov[32];
+                        tc_ld32(tmem + lane_bits + TM_PV + c, ov);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+                        tc_st32(tmem + lane_bits + TM_PV + c, ov);
+                    }
+                }
+                if (raise) { l *= alpha; m_ref = m_cand; }
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             float sum = 0.f;
             uint32_t p[32];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float a0 = exp2f(__uint_as_float(s0[2 * j]) - m_use), a1 = exp2f(__uint_as_float(s0[2 * j + 1]) - m_use);
-                const float c0 = exp2f(__uint_as_float(s1[2 * j]) - m_use), c1 = exp2f(__uint_as_float(s1[2 * j + 1]) - m_use);
+            for (int j = 0; j < 16; ++j) {                              // p = 2^(s * scale - m_ref): one FFMA and one EX2 each
+                const float a0 = ex2(fmaf(__uint_as_float(s0[2 * j]), scale_log2, -m_use));
+                const float a1 = ex2(fmaf(__uint_as_float(s0[2 * j + 1]), scale_log2, -m_use));
+                const float c0 = ex2(fmaf(__uint_as_float(s1[2 * j]), scale_log2, -m_use));
+                const float c1 = ex2(fmaf(__uint_as_float(s1[2 * j + 1]), scale_log2, -m_use));
                 sum += (a0 + a1) + (c0 + c1);
                 __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pc = __floats2bfloat162_rn(c0, c1);
                 p[j] = *reinterpret_cast<uint32_t*>(&pa);               // keys 2j, 2j+1
                 p[16 + j] = *reinterpret_cast<uint32_t*>(&pc);          // keys 32+2j, 32+2j+1
             }
-            l = l * alpha + sum;
-            tc_st32(tmem + lane_bits + TM_P, p);
+            l += sum;
+            tc_st32(tmem + lane_bits + TM_P + (i & 1) * 32, p);
             tc_wait_st();
             // places of the sequence's last page that hold no key yet: zero those rows of V, so that
             // whatever an earlier owner of the page left there cannot reach the sum (0 * NaN)
@@ -268,31 +315,31 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             tc_fence_before();
             mbar_arrive(p_ready);
-            if (!ok) break;
-            if (!mbar_wait(pv_full, i & 1, status, 3)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t pv[32];
-                tc_ld32(tmem + lane_bits + TM_PV + c, pv);
-                tc_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * alpha + __uint_as_float(pv[j]);
-            }
         }
+        if (ok && !mbar_spin(pv_full0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, status, 3)) ok = false;
+        tc_fence_after();
         if (!ok) s_abort = 1;
-        if (ok && r < rows) {
+        if (ok) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(t0 + tile * BQ + r) * H + h) * HD;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                uint32_t w[4];
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t ov[32];
+                tc_ld32(tmem + lane_bits + TM_PV + c, ov);                // warp-wide, also for rows that are not written
+                tc_wait_ld();
+                if (r < rows) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 v2 = __floats2bfloat162_rn(o[d + 2 * j] * inv, o[d + 2 * j + 1] * inv);
-                    w[j] = *reinterpret_cast<uint32_t*>(&v2);
+                    for (int d = 0; d < 32; d += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(ov[d + 2 * j]) * inv,
+                                                                      __uint_as_float(ov[d + 2 * j + 1]) * inv);
+                            w[j] = *reinterpret_cast<uint32_t*>(&v2);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
