@@ -1,0 +1,69 @@
+"""The engine at the widths of a real model (Llama-3.2-1B's layer sizes, two layers): the tcgen05
+products, the tcgen05 prefill attention, the cluster kernel of decode and the CUDA graphs all run at
+the shapes that serving uses, against the plain implementation on the CPU."""
+import pytest
+import torch
+
+from harness import run_batch, run_tail, run_whole
+from plain import llama_plain as P
+from util import assert_close, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True, "hidden_act": "silu",
+    "bos_token_id": 128000, "eos_token_id": 128001,
+}
+
+
+@pytest.fixture(scope="module")
+def real(tmp_path_factory):
+    d = make_model_dir(str(tmp_path_factory.mktemp("real") / "m"), CONFIG, 2, sharpen=4.0)
+    cfg, w = P.load_model(d)
+    toks = {n: random_tokens(n, CONFIG["vocab_size"], 300 + n) for n in (200, 70, 33)}
+    ref = {}
+
+    def plain(n, dtype):
+        key = (n, dtype)
+        if key not in ref:
+            ref[key] = P.forward(cfg, w, toks[n], act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
+        return ref[key]
+
+    return d, toks, plain
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_real_widths_in_every_cut(real, dtype):
+    from picolm_b200.engine import Engine
+    d, toks, plain = real
+    eng = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 16, max_seqs=4)
+    for n in (200, 33):
+        assert_close(run_whole(eng, toks[n]), plain(n, dtype), dtype, f"real widths {dtype} whole {n}")
+    assert_close(run_tail(eng, toks[70], tail=32), plain(70, dtype), dtype, f"real widths {dtype} tail")
+    outs = run_batch(eng, [toks[200], toks[33], toks[70]], [150, 20, 64])
+    for n, got in zip((200, 33, 70), outs):
+        assert_close(got, plain(n, dtype), dtype, f"real widths {dtype} batch {n}")
+    eng.cache.check()
+    if dtype == "bfloat16":
+        from picolm_b200 import ops
+        ops.check_status()
+
+
+def test_graph_and_plain_launches_agree(real):
+    """A decode step replayed from a CUDA graph gives the logits of the same step launched kernel by
+    kernel, up to rounding: the graph sizes the decode attention's key ranges for its length class,
+    the plain launch for the true length, so the partial sums are cut differently."""
+    from picolm_b200.engine import Engine
+    d, toks, _ = real
+    outs = []
+    for graphs in (True, False):
+        eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 8, max_seqs=4, use_graphs=graphs)
+        outs.append(torch.cat(run_batch(eng, [toks[70], toks[33]], [40, 9])))
+        assert bool(eng._graphs) == graphs
+        del eng
+    assert_close(outs[0], outs[1], "bfloat16", "graph against plain launches")
