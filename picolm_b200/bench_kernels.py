@@ -63,7 +63,10 @@ def bench_gemm(args):
     out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
 
     def run(i):
-        ops.linear(a, ws[i], out_dtype)
+        if args.swiglu:
+            ops.linear_swiglu(a, ws[i])
+        else:
+            ops.linear(a, ws[i], out_dtype)
 
     sec = _time(run, len(ws), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     ops.check_status()
@@ -135,6 +138,7 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--swiglu", action="store_true", help="gemm: the product with the SwiGLU epilogue (n counts gate and up rows)")
     ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
     ap.add_argument("--copies", type=int, default=0,
                     help="gemm: weight copies to rotate through (default: enough to exceed L2; 1 keeps them in L2)")

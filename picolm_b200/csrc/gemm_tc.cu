@@ -167,11 +167,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             if (p < p_rows) {
                                 const int fo = (q0 + gq) / 2 + cc;
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gt[j])));
-                                    const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j])));
-                                    gt[j] = __float_as_uint(g / (1.0f + expf(-g)) * u);
-                                }
+                                for (int j = 0; j < 32; ++j)
+                                    gt[j] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[j]), __uint_as_float(up[j])));
                                 OutT* rowp = dst + (size_t)p * ldo + fo;
                                 if ((((size_t)p * ldo + fo) * sizeof(OutT)) % 16 == 0) {
 #pragma unroll

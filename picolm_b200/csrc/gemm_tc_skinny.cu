@@ -212,9 +212,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     g += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
                     u += ld_cluster(remote[r] + (uint32_t)(c * BM + BM / 2 + row) * 4u);
                 }
-            g = __bfloat162float(__float2bfloat16_rn(g));
-            u = __bfloat162float(__float2bfloat16_rn(u));
-            out[(size_t)t * ldo + fo] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
+            out[(size_t)t * ldo + fo] = from_f32<OutT>(swiglu_bf16(g, u));
         }
     }
     __syncthreads();                                               // reconverge before the aligned barrier

@@ -88,6 +88,17 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// silu(g) * u for the fused bf16 epilogues: g and u are rounded to bf16 first (as a separate
+// activation kernel would read them), then g / (1 + 2^(-g log2 e)) * u with the special-function
+// unit's 2^x and reciprocal, whose error is far below the bf16 rounding of the result.
+__device__ __forceinline__ float swiglu_bf16(float g, float u) {
+    g = __bfloat162float(__float2bfloat16_rn(g));
+    u = __bfloat162float(__float2bfloat16_rn(u));
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    return __fdividef(g, 1.0f + e) * u;
+}
+
 template <typename T> __device__ __forceinline__ void store_vec8(T* p, const uint32_t* r);
 template <> __device__ __forceinline__ void store_vec8<float>(float* p, const uint32_t* r) {
     reinterpret_cast<uint4*>(p)[0] = make_uint4(r[0], r[1], r[2], r[3]);
