@@ -38,9 +38,7 @@ __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
 // SWAP = false: out[p, q] (tokens on P);  SWAP = true: out[q, p] (tokens on Q).
 // gridDim = (P tiles, Q tiles, K splits).  With more than one split, OutT is
 // float and the CTA writes its partial sum to out + blockIdx.z * split_stride.
-// EPI = 1 (wide path only): W's rows come in tiles of 64 gate rows followed by their 64 up rows, and
-// the kernel writes silu(gate) * up, each rounded to bf16 first, to out[p, q / 2] (q_rows / 2 columns).
-template <int BN, bool SWAP, typename OutT, int EPI = 0>
+template <int BN, bool SWAP, typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, (BN < 128 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                OutT* __restrict__ out, int p_rows, int q_rows, int K, long ldo, int kb_per_split, long split_stride,
@@ -152,35 +150,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const int p = p0 + quarter * 32 + lane;     // row of P held by this thread
             OutT* dst = out + (size_t)blockIdx.z * split_stride;
             constexpr int CHUNK = BN >= 32 ? 32 : 16;
-            if (EPI == 1) {
-                if (BN >= 128 && !SWAP) {
-#pragma unroll 1
-                    for (int gq = 0; gq < BN; gq += 128) {
-                        if (q0 + gq >= q_rows) break;
-#pragma unroll 1
-                        for (int cc = 0; cc < 64; cc += 32) {
-                            uint32_t gt[32], up[32];
-                            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(gq + cc);
-                            tc_ld32(taddr, gt);
-                            tc_ld32(taddr + 64, up);
-                            tc_wait_ld();
-                            if (p < p_rows) {
-                                const int fo = (q0 + gq) / 2 + cc;
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    gt[j] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[j]), __uint_as_float(up[j])));
-                                OutT* rowp = dst + (size_t)p * ldo + fo;
-                                if ((((size_t)p * ldo + fo) * sizeof(OutT)) % 16 == 0) {
-#pragma unroll
-                                    for (int j = 0; j < 32; j += 8) store_vec8<OutT>(rowp + j, gt + j);
-                                } else {
-                                    for (int j = 0; j < 32; ++j) rowp[j] = from_f32<OutT>(__uint_as_float(gt[j]));
-                                }
-                            }
-                        }
-                    }
-                }
-            } else
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK) {
                 uint32_t r[32];
@@ -249,12 +218,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __
     }
 }
 
-template <int BN, bool SWAP, typename OutT, int EPI = 0>
+template <int BN, bool SWAP, typename OutT>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, OutT* out, int p_rows, int q_rows, int K, long ldo,
            int splits, int kb_per_split, long split_stride, int* status, cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = smem_bytes_for(BN);
-    auto kern = gemm_tc_kernel<BN, SWAP, OutT, EPI>;
+    auto kern = gemm_tc_kernel<BN, SWAP, OutT>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -360,24 +329,6 @@ extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtyp
     if (bn == 16) return launch<16, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     if (bn == 32) return launch<32, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     return launch<64, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
-}
-
-// out[T, F/2] (bf16) = silu(gate) * up of x[T, K] * w[F, K]^T, where w holds tiles of 64 gate rows
-// followed by their 64 up rows (F a multiple of 128).  The wide path only (T > 64).
-extern "C" int plm_gemm_tc_wide_swiglu(const void* x, const void* w, void* out, int T, int F, int K, long ldx,
-                                       long ldw, long ldo, int* status, cudaStream_t stream) {
-    if (T <= 0 || F <= 0) return PLM_OK;
-    if (T <= 64) return PLM_ERR_UNSUPPORTED;
-    if (F % 128) return PLM_ERR_SHAPE;
-    if (!plm_gemm_tc_supported(x, w, T, F, K, ldx, ldw)) return PLM_ERR_ALIGN;
-    CUtensorMap mp, mq;
-    int rc;
-    const int bn = (F >= 2048 && T >= 256) ? 256 : 128;
-    if ((rc = make_map(&mp, x, T, K, ldx, BM)) != PLM_OK) return rc;
-    if ((rc = make_map(&mq, w, F, K, ldw, bn)) != PLM_OK) return rc;
-    const int n_kb = (K + BK - 1) / BK;
-    if (bn == 256) return launch<256, false, bf16, 1>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
-    return launch<128, false, bf16, 1>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
 }
 
 // ------------------------------------------------- the entry point that allocates nothing

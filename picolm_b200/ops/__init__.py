@@ -24,7 +24,7 @@ _SIGNATURES = {
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
-    "plm_gemm_tc_wide_swiglu": [_vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
     "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
@@ -305,6 +305,30 @@ def gemm_tc_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swi
     return out
 
 
+def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
+    (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
+    tile's main loop).  With `swiglu`, w comes from `interleave_gate_up` and the result is
+    silu(gate) * up, [M, N/2] in bfloat16."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc_wide: needs bfloat16 operands that TMA can address")
+    if swiglu:
+        if N % 128:
+            raise KernelError("gemm_tc_wide: the interleaved gate/up matrix must have a multiple of 128 rows")
+        out_dtype = torch.bfloat16
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
+        _p(status_word(a.device)), _stream()), "gemm_tc_wide")
+    return out
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """[gate | up] as one matrix whose rows come in tiles of 64 gate rows followed by the 64 up rows of
     the same features, so that a 128-row MMA tile holds both branches of 64 outputs and the product's
@@ -325,11 +349,7 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
     if M <= 64:
         return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
-    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
-    _check(_fn("gemm_tc", "plm_gemm_tc_wide_swiglu")(
-        _p(a), _p(w_gate_up), _p(out), M, N, K, K, K, N // 2, _p(status_word(a.device)), _stream()),
-        "gemm_tc_wide_swiglu")
-    return out
+    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True)
 
 
 # ------------------------------------------------------------------ attention
@@ -489,7 +509,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     if gemm_tc_supported(a, w):
         if a.shape[0] <= 64:
             return gemm_tc_skinny(a, w, out_dtype)
-        return gemm_tc(a, w, out_dtype)
+        return gemm_tc_wide(a, w, out_dtype)
     return gemm_simt(a, w, out_dtype)
 
 

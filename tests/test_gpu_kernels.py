@@ -465,3 +465,24 @@ def test_attention_prefill_tcgen05(H, G, hd, window):
         row = out.float().cpu()[new[0] - 1].reshape(H, hd)
         for h in range(H):
             assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(65, 128, 64), (128, 128, 128), (200, 136, 328), (300, 2048, 192),
+                                   (256, 4096, 512), (1000, 264, 2048), (2048, 2560, 256), (5000, 2048, 64)])
+def test_gemm_tc_wide_persistent(out_dtype, M, N, K):
+    """The persistent prompt-shaped product: fewer tiles than SMs and many more, both tile widths, ragged
+    edges in every dimension, several tiles per CTA so that both accumulators and the barrier phases
+    across tiles are exercised."""
+    from picolm_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    a[M // 2, :] *= -2.0
+    ref = a.double() @ w.double().t()
+    out = ops.gemm_tc_wide(a.to(DEV), w.to(DEV), DT[out_dtype])
+    ops.check_status(DEV)
+    tol_ = dict(atol=2e-3, rtol=1e-4) if out_dtype == "float32" else dict(atol=2e-2, rtol=1e-2)
+    assert torch.allclose(out.double().cpu(), ref, **tol_)
