@@ -492,6 +492,9 @@ def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, to
     n, V = logits.shape
     if rng_state.numel() != n:
         raise KernelError("sample: one rng state per row is needed")
+    if V > 8 * 40 * 1024:
+        raise KernelError(f"sample: a vocabulary of {V} exceeds {8 * 40 * 1024}, the most the sampling kernel keeps "
+                          f"in the shared memory of its eight CTAs")
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(_fn("sampling", "plm_sample")(

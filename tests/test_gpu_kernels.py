@@ -257,6 +257,28 @@ def test_sample_against_the_reference_chain(temperature, top_k, top_p, min_p):
     assert back == states
 
 
+@pytest.mark.parametrize("V", [7, 4099, 50257, 128256])
+def test_sample_vocabulary_sizes(V):
+    """Vocabularies from fewer entries than the cluster has CTAs up to the largest in use: rows of very
+    different spread, one of them with a far token that carries almost all of the mass."""
+    from picolm_b200 import ops
+    from picolm_b200.sampling import stream_seed
+    torch.manual_seed(V)
+    logits = torch.randn(3, V) * torch.tensor([[0.5], [3.0], [8.0]])
+    logits[1, V - 1] = 40.0
+    states = [stream_seed(7, i) for i in range(3)]
+    rng = torch.tensor(states, dtype=torch.int64, device=DEV)
+    for params in ((0.8, 40, 0.9, 0.05), (1.1, 0, 0.95, 0.0)):
+        got = ops.sample(logits.to(DEV), rng, *params).cpu().tolist()
+        for r in range(3):
+            states[r], want = P.sample_index_order(logits[r], *params, states[r])
+            kept, _ = P.sampling_weights(logits[r], *params)
+            assert got[r] in set(kept)
+            if len(kept) <= 1000:                            # beyond that the order of a float32 sum decides
+                assert got[r] == want, f"V={V} row {r}: kernel drew {got[r]}, the plain chain {want}"
+    assert got[1] == V - 1
+
+
 def test_sample_distribution():
     """Over many draws the kernel's frequencies follow softmax(logits / T) on a small vocabulary."""
     from picolm_b200 import ops
