@@ -280,10 +280,17 @@ constexpr int DC_STAGES = 3;
 constexpr size_t DC_TILES_BYTES = (size_t)(2 * DC_STAGES) * TILE_ELEMS * sizeof(bf16);
 constexpr size_t DC_Q_BYTES = (size_t)16 * LDS * sizeof(bf16);
 constexpr size_t DC_MERGE_BYTES = (size_t)4 * 16 * (HD + 2) * sizeof(float);
-constexpr size_t DC_SMEM = DC_Q_BYTES + (DC_TILES_BYTES > DC_MERGE_BYTES ? DC_TILES_BYTES : DC_MERGE_BYTES);
+constexpr size_t DC_RESULT_BYTES = (size_t)16 * (HD + 2) * sizeof(float);          // what a CTA shows to its cluster
+constexpr size_t DC_AFTER_BYTES = DC_MERGE_BYTES + DC_RESULT_BYTES;
+constexpr size_t DC_SMEM = DC_Q_BYTES + (DC_TILES_BYTES > DC_AFTER_BYTES ? DC_TILES_BYTES : DC_AFTER_BYTES);
+constexpr int DC_MAX_CLUSTER = 8;                                                   // portable cluster size
 
-// grid = (splits, G * row_groups, tokens).  ws_o [tokens*H, splits, HD] and ws_ml [tokens*H, splits, 2]
-// receive the partial results when splits > 1; with one split the output is written directly.
+// grid = (splits, G * row_groups, tokens).  With one split the output is written directly.  With
+// CLUSTER the splits of a (token, KV head) are the CTAs of one thread-block cluster: each parks its
+// partial result in its own shared memory and the cluster merges them through distributed shared
+// memory, in split order.  Without it (more splits than a cluster holds) ws_o [tokens*H, splits, HD]
+// and ws_ml [tokens*H, splits, 2] receive the partial results for attn_merge_kernel.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(NT)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
@@ -294,6 +301,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw + DC_Q_BYTES);
     bf16* v_s = k_s + DC_STAGES * TILE_ELEMS;
     float* merge = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES);      // reused after the last tile
+    float* result = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES + DC_MERGE_BYTES);
     pdl_launch_dependents();
     pdl_wait();
     const int n_splits = gridDim.x, split = blockIdx.x;
@@ -313,14 +321,14 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
 
-    if (n_pages <= 0) {                                 // an empty split: weight zero in the merge
+    if (!CLUSTER && n_pages <= 0) {                     // an empty split: weight zero in the merge
         for (int r = threadIdx.x; r < n_rows; r += NT) {
             float* ml = ws_ml + (((size_t)t * H + h0 + r) * n_splits + split) * 2;
             ml[0] = -INFINITY; ml[1] = 0.f;
         }
         return;
     }
-    {
+    if (n_pages > 0) {                                  // (in a cluster an empty split still meets the others)
         constexpr int CPR = HD / 8;
         for (int c = threadIdx.x; c < 16 * CPR; c += NT) {
             const int r = c / CPR, col = c - r * CPR;
@@ -367,6 +375,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     __syncthreads();
 
     // merge the four warps' partial results: merge[w][row][0..HD) = acc, [HD] = m, [HD+1] = l
+    // (a split without pages leaves m = -inf and l = 0 here: weight zero below)
     {
         float* mine = merge + (size_t)warp * 16 * (HD + 2);
 #pragma unroll
@@ -400,7 +409,13 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
             ll += wgt * merge[((size_t)w * 16 + r) * (HD + 2) + HD + 1];
         }
         const size_t row = (size_t)t * H + h0 + r;
-        if (n_splits == 1) {
+        if (CLUSTER) {
+            result[r * (HD + 2) + d] = acc;
+            if (d == 0) {
+                result[r * (HD + 2) + HD] = mm;
+                result[r * (HD + 2) + HD + 1] = ll;
+            }
+        } else if (n_splits == 1) {
             out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
         } else {
             ws_o[(row * n_splits + split) * HD + d] = acc;
@@ -409,6 +424,40 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
                 ws_ml[(row * n_splits + split) * 2 + 1] = ll;
             }
         }
+    }
+    if (CLUSTER) {
+        // out[row, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp2(m_s - max m), splits in order;
+        // the outputs are dealt out over the cluster's CTAs
+        cluster_sync_all();
+        const uint32_t rank = cluster_rank();           // == split: the cluster spans grid x
+        for (int idx = (int)rank * NT + threadIdx.x; idx < n_rows * HD; idx += n_splits * NT) {
+            const int r = idx / HD, d = idx - r * HD;
+            float ms[DC_MAX_CLUSTER], ls[DC_MAX_CLUSTER], as[DC_MAX_CLUSTER];
+#pragma unroll
+            for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
+                if (sp < n_splits) {
+                    const uint32_t base = cluster_map(result + r * (HD + 2), (uint32_t)sp);
+                    ms[sp] = cluster_ld_f32(base + HD * 4);
+                    ls[sp] = cluster_ld_f32(base + (HD + 1) * 4);
+                    as[sp] = cluster_ld_f32(base + d * 4);
+                } else {
+                    ms[sp] = -INFINITY; ls[sp] = 0.f; as[sp] = 0.f;
+                }
+            }
+            float mm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) mm = fmaxf(mm, ms[sp]);
+            float acc = 0.f, ll = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
+                if (ms[sp] == -INFINITY) continue;
+                const float wgt = exp2f(ms[sp] - mm);
+                acc += wgt * as[sp];
+                ll += wgt * ls[sp];
+            }
+            out[((size_t)t * H + h0 + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        }
+        cluster_sync_all();                             // nobody reads this CTA's shared memory any more
     }
 }
 
@@ -471,26 +520,35 @@ extern "C" long plm_attn_decode_workspace(int n_tokens, int H, int n_splits) {
 }
 
 // Decode: one query token per row of q [T, H, HD], at position tok_pos[t] of sequence tok_seq[t].
+// With a workspace the ranges' partial results pass through it and a second kernel merges them;
+// without one (at most 8 ranges) the ranges are the CTAs of a cluster and merge in shared memory.
 extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, void* out, float* workspace,
                                const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
                                int n_tokens, int H, int G, float scale, int window, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535) return PLM_ERR_SHAPE;
-    if (n_splits > 1 && !workspace) return PLM_ERR_SHAPE;
     static bool configured = false;
     if (!configured) {
-        int rc = set_smem(attn_decode_kernel, DC_SMEM);
+        int rc = set_smem(attn_decode_kernel<false>, DC_SMEM);
+        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true>, DC_SMEM);
         if (rc != PLM_OK) return rc;
         configured = true;
     }
     const int R = H / G, row_groups = (R + 15) / 16;
     if (G * row_groups > 65535) return PLM_ERR_SHAPE;
+    dim3 grid(n_splits, G * row_groups, n_tokens);
+    if (n_splits > 1 && !workspace) {                       // the splits merge inside their cluster
+        if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
+                                                stream, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
+                                                (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
+                                                max_pages, H, G, scale * LOG2E, window, row_groups));
+    }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    dim3 grid(n_splits, G * row_groups, n_tokens);
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q, (const bf16*)kc,
-                                      (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq, block_table, max_pages,
-                                      H, G, scale * LOG2E, window, row_groups));
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q,
+                                      (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));

@@ -29,15 +29,6 @@ constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
 __host__ __device__ constexpr int stages_of(int bn) { return bn <= 32 ? 5 : 4; }
 constexpr int MAX_SPLITS = 8;               // portable cluster size
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
@@ -232,21 +223,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T
     }
     const int n_kb = (K + BK - 1) / BK;
     const int per = (n_kb + S - 1) / S;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((F + BM - 1) / BM, 1, S);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = 1;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = S;
-    cfg.attrs = attr;
-    cfg.numAttrs = 2;
-    return plm_status_of(cudaLaunchKernelEx(&cfg, kern, mw, mx, out, F, T, K, ldo, per, status));
+    return plm_status_of(launch_pdl_cluster(kern, dim3((F + BM - 1) / BM, 1, S), dim3(NUM_THREADS), dim3(1, 1, S), smem, stream,
+                                            mw, mx, out, F, T, K, ldo, per, status));
 }
 
 template <int EPI, typename OutT>

@@ -28,15 +28,6 @@ constexpr float FIX = 1099511627776.0f;       // 2^40: probabilities as fixed-po
 constexpr int BINS = 1024;                    // a radix digit has 10 bits
 constexpr int SLICE = BINS / CS;              // bins that one CTA merges over the cluster
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
     uint32_t r;
@@ -417,21 +408,7 @@ sample_kernel(const float* __restrict__ logits, long ld, int V, int chunk, float
 
 template <typename Kern, typename... Args>
 int launch_cluster(Kern kern, int n_rows, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_rows * CS);
-    cfg.blockDim = dim3(NT);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = CS;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 2;
-    return plm_status_of(cudaLaunchKernelEx(&cfg, kern, args...));
+    return plm_status_of(launch_pdl_cluster(kern, dim3(n_rows * CS), dim3(NT), dim3(CS, 1, 1), smem, stream, args...));
 }
 
 int chunk_of(int V) { return ((V + CS - 1) / CS + 3) & ~3; }

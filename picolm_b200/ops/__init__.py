@@ -437,6 +437,9 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 _SM_COUNT = 148
 
 
+DECODE_CLUSTER_SPLITS = 8       # up to this many ranges merge inside a thread-block cluster, without scratch
+
+
 def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
     """Into how many ranges the decode kernel cuts each sequence's keys: about
     eight pages a range (measured best at batch 8 and 64), more ranges when that
@@ -452,20 +455,28 @@ def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: 
 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                      tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
-                     n_splits: int, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     n_splits: int, window: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                     scratch: Optional[bool] = None) -> torch.Tensor:
     """Attention of single query tokens (one per row of q [T, H, hd], at position tok_pos[t] of sequence
-    tok_seq[t]) over the paged cache, the keys of each cut into `n_splits` ranges whose partial results pass
-    through a scratch buffer; returns [T, H*hd]."""
+    tok_seq[t]) over the paged cache, the keys of each cut into `n_splits` ranges.  Up to eight ranges are the
+    CTAs of a thread-block cluster and merge through its shared memory; more ranges, or more CTAs than
+    run at once, pass their partial results through a scratch buffer and a second kernel (`scratch` forces
+    one way or the other).  Returns [T, H*hd]."""
     T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
-    ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=q.device) if n_splits > 1 else None
+    # Clusters are scheduled as a whole: past one wave of CTAs that costs more than the second kernel saves.
+    ctas = T * num_kv_heads * ((H // num_kv_heads + 15) // 16) * n_splits
+    if scratch is None:
+        scratch = ctas > 3 * _SM_COUNT
+    scratch = n_splits > 1 and (scratch or n_splits > DECODE_CLUSTER_SPLITS)
+    ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=q.device) if scratch else None
     lib, flags = attention_variant(hd)
     _check(_fn(lib, "plm_attn_decode", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
-        "attention_decode", kernels=2 if n_splits > 1 else 1)
+        "attention_decode", kernels=2 if scratch else 1)
     return out
 
 

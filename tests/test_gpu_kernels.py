@@ -390,11 +390,12 @@ def test_attention_prefill_mma(H, G, hd, window):
 
 
 @pytest.mark.parametrize("window", [None, 90])
-@pytest.mark.parametrize("n_splits", [1, 3, 16])
+@pytest.mark.parametrize("n_splits,scratch", [(1, False), (2, False), (3, False), (3, True), (8, False), (16, True)])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (6, 2, 48), (5, 5, 16), (40, 1, 128), (3, 1, 32), (4, 2, 256)])
-def test_attention_decode_mma(H, G, hd, n_splits, window):
+def test_attention_decode_mma(H, G, hd, n_splits, scratch, window):
     """Decode on the tensor cores with the keys cut into ranges: sequences of very unequal lengths (some
-    ranges stay empty), more heads per KV head than one row group holds, a far key that must be found."""
+    ranges stay empty), more heads per KV head than one row group holds, a far key that must be found.
+    The ranges merge inside a thread-block cluster, or through a scratch buffer and a second kernel."""
     from picolm_b200 import ops
     lens = [700, 1, 65, 130, 64, 257]
     new = [1] * len(lens)
@@ -405,7 +406,7 @@ def test_attention_decode_mma(H, G, hd, n_splits, window):
     out = ops.attention_decode(torch.cat(qs).to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV),
                                torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV),
                                torch.arange(len(lens), dtype=torch.int32, device=DEV), table.to(DEV), G, scale,
-                               n_splits, window=window)
+                               n_splits, window=window, scratch=scratch)
     assert torch.isfinite(out).all()
     assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
     if window is None:
