@@ -165,6 +165,30 @@ extern "C" int plm_rmsnorm(float* x, const float* delta, const void* w, int w_dt
     return PLM_ERR_DTYPE;
 }
 
+// ------------------------------------------------ rows whose scale is still due
+// out[t, :] = bf16(x[t, :] * r[t]) with r[t] = 1 / sqrt(sum_p parts[p, t] / size + eps): what is left of
+// an RMSNorm whose weight a product's epilogue has already applied (x) and whose sums of squares it has
+// left as partial sums (parts [n_parts, ld_parts]).  One block per row, sums in a fixed order.
+__global__ void scale_rows_kernel(const bf16* __restrict__ x, const float* __restrict__ parts, int n_parts, int ld_parts,
+                                  float inv_size, float eps, bf16* __restrict__ out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int p = 0; p < n_parts; ++p) ss += parts[(size_t)p * ld_parts + t];
+    const float r = 1.0f / sqrtf(ss * inv_size + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        out[(size_t)t * d + i] = __float2bfloat16_rn(__bfloat162float(x[(size_t)t * d + i]) * r);
+}
+
+extern "C" int plm_scale_rows(const void* x, const float* parts, int n_parts, int ld_parts, int size, float eps,
+                              void* out, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0 || size <= 0 || n_parts <= 0 || ld_parts < n_rows) return PLM_ERR_SHAPE;
+    return plm_status_of(launch_pdl(scale_rows_kernel, dim3(n_rows), dim3(256), 0, stream, (const bf16*)x, parts, n_parts,
+                                    ld_parts, 1.0f / (float)size, eps, (bf16*)out, d));
+}
+
 // --------------------------------------------------------------------- SwiGLU
 // gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  out[T,F] = silu(gate) * up.
 template <typename T>

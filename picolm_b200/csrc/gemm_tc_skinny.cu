@@ -13,6 +13,9 @@
 //   EPI_SWIGLU  W's rows come in tiles of 64 gate rows followed by their 64 up rows;
 //               out[t, f] = silu(gate) * up, each rounded to bf16 first
 //               (picolm/model_core.c:2182-2193: hb = silu(Wg x) * (Wu x))
+//   EPI_RESIDUAL  the product in front of an RMSNorm: the residual add, the norm's weight and
+//               the rows' sums of squares in the epilogue (struct Fuse below);
+//   SCALE       the product behind it: each token's results times that token's 1/rms.
 // The reference's counterpart is its per-row matvec (picolm/tensor.c:839-1419).
 //
 // Warp roles and pipeline as in gemm_tc.cu; waits are bounded there and here.
@@ -24,7 +27,7 @@ using namespace plm_tc;
 
 namespace {
 
-constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
+constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2;
 // ring depth: two CTAs of any tile width fit one SM (2 x ~100 KB)
 __host__ __device__ constexpr int stages_of(int bn) { return bn <= 32 ? 5 : 4; }
 constexpr int MAX_SPLITS = 8;               // portable cluster size
@@ -44,17 +47,37 @@ __host__ __device__ constexpr size_t skinny_smem(int bn) {
     return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256;
 }
 
+// What the fused forms of the kernel need beside the product itself.
+//
+// An RMSNorm between two products is split over them.  The product before it (EPI_RESIDUAL) adds
+// its result to the fp32 residual stream `out` in place, writes xw = bf16(new row * norm weight) for
+// the product after it, and for every token the sum of squares of the new values that this CTA
+// wrote, one row of ss_out per (tile, cluster rank).  The product after it (SCALE) multiplies in xw and
+// scales token t's results by r[t] = 1 / sqrt(sum of those partial sums / size + eps): the
+// normalisation commutes with the product.  All sums run in a fixed order.
+struct Fuse {
+    const float* scale_parts;   // SCALE: [n_parts, 64]
+    int n_parts;
+    float inv_size, eps;
+    const bf16* norm_w;         // EPI_RESIDUAL: [F]
+    bf16* xw;                   // EPI_RESIDUAL: [T, ld_xw]
+    long ld_xw;
+    float* ss_out;              // EPI_RESIDUAL: [tiles * S, 64]
+};
+constexpr int SS_STRIDE = 64;   // tokens per row of the partial sums of squares (the most this kernel takes)
+
 // W: [F, K] (P operand, 128 rows per tile), X: [T, K] (Q operand, BN rows).  grid = (F tiles, 1, S),
 // cluster = (1, 1, S).  out row stride ldo.  For EPI_SWIGLU, F counts W's rows (gate and up together)
 // and out has F/2 columns.
-template <int BN, int EPI, typename OutT>
+template <int BN, int EPI, typename OutT, bool SCALE>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      OutT* __restrict__ out, int F, int T, int K, long ldo, int kb_per_split, int* __restrict__ status) {
+                      OutT* __restrict__ out, int F, int T, int K, long ldo, int kb_per_split, int* __restrict__ status,
+                      const Fuse fz) {
     constexpr int STAGES = stages_of(BN);
     constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    static_assert(BN * BM * 4 <= STAGES * (W_BYTES + X_BYTES), "the partial tile must fit the ring");
+    static_assert(2 * BN * BM * 4 <= STAGES * (W_BYTES + X_BYTES), "the partial tile and the squares must fit the ring");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -63,7 +86,9 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tmem_full = bars + 16 * STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 16 * STAGES + 8 - raw));
     float* part = reinterpret_cast<float*>(smem_raw + (base - raw));     // [BN][128] partial tile, after the main loop
+    float* squares = part + BN * BM;                                     // EPI_RESIDUAL: [BN][rows of this CTA's slice]
     __shared__ int s_abort;
+    __shared__ float s_scale[BN];
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,6 +164,16 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             tc_commit(tmem_full);
         }
     } else {
+        if (SCALE) {                                       // while the main loop runs: the rows' scale factors
+            pdl_wait();
+            const int t = threadIdx.x - 64;
+            if (t < BN) {
+                float ss = 0.f;
+                if (t < T)
+                    for (int p = 0; p < fz.n_parts; ++p) ss += fz.scale_parts[(size_t)p * SS_STRIDE + t];
+                s_scale[t] = 1.0f / sqrtf(ss * fz.inv_size + fz.eps);
+            }
+        }
         // park this CTA's partial tile in shared memory: part[token][feature row]
         const int quarter = warp & 3;
         const bool ready = mbar_wait(tmem_full, 0, status, 3);
@@ -184,6 +219,22 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const int c = it / slice, pr = it - c * slice;
         const int row = (int)rank * slice + pr;
         const int t = c;
+        if (EPI == EPI_RESIDUAL) {
+            const int f = p0 + row;
+            float sq = 0.f;
+            if (t < T && f < F) {
+                float v = 0.f;
+#pragma unroll
+                for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+                    if (r < S) v += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+                const float xn = to_f32(out[(size_t)t * ldo + f]) + v;
+                out[(size_t)t * ldo + f] = from_f32<OutT>(xn);
+                fz.xw[(size_t)t * fz.ld_xw + f] = __float2bfloat16_rn(xn * __bfloat162float(fz.norm_w[f]));
+                sq = xn * xn;
+            }
+            squares[it] = sq;                                      // [token][row of the slice]
+            continue;
+        }
         if (t >= T) continue;
         if (EPI == EPI_STORE) {
             const int f = p0 + row;
@@ -192,6 +243,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
             for (uint32_t r = 0; r < MAX_SPLITS; ++r)
                 if (r < S) v += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+            if (SCALE) v *= s_scale[c];
             out[(size_t)t * ldo + f] = from_f32<OutT>(v);
         } else {
             const int fo = p0 / 2 + row;
@@ -203,19 +255,25 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     g += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
                     u += ld_cluster(remote[r] + (uint32_t)(c * BM + BM / 2 + row) * 4u);
                 }
+            if (SCALE) { g *= s_scale[c]; u *= s_scale[c]; }
             out[(size_t)t * ldo + fo] = from_f32<OutT>(swiglu_bf16(g, u));
         }
     }
     __syncthreads();                                               // reconverge before the aligned barrier
+    if (EPI == EPI_RESIDUAL && threadIdx.x < BN && threadIdx.x < T) {
+        float ss = 0.f;
+        for (int pr = 0; pr < slice; ++pr) ss += squares[threadIdx.x * slice + pr];
+        fz.ss_out[((size_t)blockIdx.x * S + rank) * SS_STRIDE + threadIdx.x] = ss;
+    }
     cluster_sync_all();                                            // nobody reads this CTA's tile any more
 }
 
-template <int BN, int EPI, typename OutT>
+template <int BN, int EPI, typename OutT, bool SCALE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T, int K, long ldo, int S, int* status,
-           cudaStream_t stream) {
+           const Fuse& fz, cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = skinny_smem(BN);
-    auto kern = gemm_tc_skinny_kernel<BN, EPI, OutT>;
+    auto kern = gemm_tc_skinny_kernel<BN, EPI, OutT, SCALE>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -224,15 +282,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T
     const int n_kb = (K + BK - 1) / BK;
     const int per = (n_kb + S - 1) / S;
     return plm_status_of(launch_pdl_cluster(kern, dim3((F + BM - 1) / BM, 1, S), dim3(NUM_THREADS), dim3(1, 1, S), smem, stream,
-                                            mw, mx, out, F, T, K, ldo, per, status));
+                                            mw, mx, out, F, T, K, ldo, per, status, fz));
 }
 
-template <int EPI, typename OutT>
+template <int EPI, typename OutT, bool SCALE = false>
 int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T, int K, long ldo, int S,
-                int* status, cudaStream_t stream) {
-    if (bn == 16) return launch<16, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
-    if (bn == 32) return launch<32, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
-    return launch<64, EPI, OutT>(mw, mx, out, F, T, K, ldo, S, status, stream);
+                int* status, cudaStream_t stream, const Fuse& fz = Fuse{}) {
+    if (bn == 16) return launch<16, EPI, OutT, SCALE>(mw, mx, out, F, T, K, ldo, S, status, fz, stream);
+    if (bn == 32) return launch<32, EPI, OutT, SCALE>(mw, mx, out, F, T, K, ldo, S, status, fz, stream);
+    return launch<64, EPI, OutT, SCALE>(mw, mx, out, F, T, K, ldo, S, status, fz, stream);
 }
 
 }  // namespace
@@ -268,4 +326,60 @@ extern "C" int plm_gemm_tc_skinny(const void* x, const void* w, void* out, int o
     if (out_dtype == PLM_F32) return dispatch_bn<EPI_STORE, float>(bn, mw, mx, (float*)out, F, T, K, ldo, S, status, stream);
     if (out_dtype == PLM_BF16) return dispatch_bn<EPI_STORE, bf16>(bn, mw, mx, (bf16*)out, F, T, K, ldo, S, status, stream);
     return PLM_ERR_DTYPE;
+}
+
+// Rows of partial sums of squares that plm_gemm_tc_skinny_residual writes for (F, K): one per (tile,
+// cluster rank), each of 64 floats.
+extern "C" int plm_gemm_tc_skinny_residual_parts(int F, int K) {
+    return ((F + BM - 1) / BM) * plm_gemm_tc_skinny_splits(F, K);
+}
+
+// The product in front of an RMSNorm: resid[T, F] += x[T, K] * w[F, K]^T in place (fp32), xw[T, F] =
+// bf16(new resid * norm_w), ss_out[parts, 64] = partial sums of squares of the new rows (see Fuse).
+extern "C" int plm_gemm_tc_skinny_residual(const void* x, const void* w, float* resid, const void* norm_w, void* xw,
+                                           float* ss_out, int T, int F, int K, long ldx, long ldw, long ld_resid,
+                                           long ld_xw, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (T > 64) return PLM_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (!resid || !norm_w || !xw || !ss_out) return PLM_ERR_SHAPE;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    const int S = plm_gemm_tc_skinny_splits(F, K);
+    CUtensorMap mw, mx;
+    int rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, bn)) != PLM_OK) return rc;
+    Fuse fz = {};
+    fz.norm_w = (const bf16*)norm_w;
+    fz.xw = (bf16*)xw;
+    fz.ld_xw = ld_xw;
+    fz.ss_out = ss_out;
+    return dispatch_bn<EPI_RESIDUAL, float>(bn, mw, mx, resid, F, T, K, ld_resid, S, status, stream, fz);
+}
+
+// The product behind an RMSNorm whose weight is already in x (see Fuse): like plm_gemm_tc_skinny with
+// bfloat16 output, token t's results scaled by 1 / sqrt(sum_p scale_parts[p, t] / size + eps).
+extern "C" int plm_gemm_tc_skinny_scaled(const void* x, const void* w, void* out, int epilogue, int T, int F, int K,
+                                         long ldx, long ldw, long ldo, const float* scale_parts, int n_parts, int size,
+                                         float eps, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (T > 64) return PLM_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (epilogue == EPI_SWIGLU && F % 128) return PLM_ERR_SHAPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
+    if (!scale_parts || n_parts <= 0 || size <= 0) return PLM_ERR_SHAPE;
+    const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+    const int S = plm_gemm_tc_skinny_splits(F, K);
+    CUtensorMap mw, mx;
+    int rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, bn)) != PLM_OK) return rc;
+    Fuse fz = {};
+    fz.scale_parts = scale_parts;
+    fz.n_parts = n_parts;
+    fz.inv_size = 1.0f / (float)size;
+    fz.eps = eps;
+    if (epilogue == EPI_SWIGLU)
+        return dispatch_bn<EPI_SWIGLU, bf16, true>(bn, mw, mx, (bf16*)out, F, T, K, ldo, S, status, stream, fz);
+    return dispatch_bn<EPI_STORE, bf16, true>(bn, mw, mx, (bf16*)out, F, T, K, ldo, S, status, stream, fz);
 }

@@ -24,6 +24,10 @@ _SIGNATURES = {
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_skinny_residual_parts": [_i, _i],
+    "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _f, _vp, _vp],
+    "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
@@ -144,6 +148,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     T, d = x.shape
     if weight.shape != (d,):
         raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
+    if isinstance(delta, PendingLinear):
+        delta = delta.compute()
     if delta is not None:
         _dev(delta, "delta")
         if delta.dtype != torch.float32 or delta.shape != x.shape:
@@ -281,12 +287,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
-def gemm_tc_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The decode-shaped tensor-core product: a [M <= 64, K] @ w [N, K]^T with the weights on the MMA's 128
     rows and K split over a thread-block cluster whose CTAs add their partial tiles up through distributed
     shared memory.  With `swiglu`, w holds tiles of 64 gate rows followed by their 64 up rows (see
-    `interleave_gate_up`) and the result is silu(gate) * up, [M, N/2] in bfloat16."""
+    `interleave_gate_up`) and the result is silu(gate) * up, [M, N/2] in bfloat16.  `a` may be `ScaledRows`
+    (an RMSNorm whose scale is still due): the epilogue then scales each row of the result, in bfloat16."""
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.x
+        if out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc_skinny: rows with a scale that is still due give a bfloat16 result only")
     _dev(a, "a"), _dev(w, "w")
     M, K = a.shape
     N = w.shape[0]
@@ -299,10 +311,91 @@ def gemm_tc_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swi
     n_out = N // 2 if swiglu else N
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    if scaled is not None:
+        _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_scaled")(
+            _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
+            scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()), "gemm_tc_skinny_scaled")
+        return out
     _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
         _p(status_word(a.device)), _stream()), "gemm_tc_skinny")
     return out
+
+
+class PendingLinear:
+    """a [M, K] @ w [N, K]^T in float32 that has not run yet: the last product of a mixer or a
+    feed-forward, whose result is a delta for the residual stream.  The norm that follows may run it
+    with the residual add and its own weight in the epilogue (`linear_residual_norm`); anything else
+    calls `compute()`."""
+    __slots__ = ("a", "w")
+
+    def __init__(self, a: torch.Tensor, w: torch.Tensor):
+        self.a, self.w = a, w
+
+    @property
+    def shape(self):
+        return (self.a.shape[0], self.w.shape[0])
+
+    def compute(self) -> torch.Tensor:
+        return linear(self.a, self.w, torch.float32)
+
+
+class ScaledRows:
+    """An RMSNorm whose scale is still due: `x` [T, size] in bfloat16 holds row * norm weight, and
+    `parts` [n, 64] partial sums of squares of the rows (column t for row t), so that the normalised
+    row t is x[t] / sqrt(sum(parts[:, t]) / size + eps).  A product takes it as its left operand and
+    applies the scale to its result (`linear`, `linear_swiglu`); `materialize()` gives the rows."""
+    __slots__ = ("x", "parts", "size", "eps")
+
+    def __init__(self, x: torch.Tensor, parts: torch.Tensor, size: int, eps: float):
+        self.x, self.parts, self.size, self.eps = x, parts, size, eps
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty_like(self.x)
+        T, d = self.x.shape
+        _check(_fn("elementwise", "plm_scale_rows")(
+            _p(self.x), _p(self.parts), self.parts.shape[0], self.parts.shape[1], self.size, float(self.eps),
+            _p(out), T, d, _stream()), "scale_rows")
+        return out
+
+
+def residual_norm_supported(pending, x: torch.Tensor, norm_weight: torch.Tensor) -> bool:
+    """Whether `linear_residual_norm` takes this case: a pending product of at most 64 rows that the
+    cluster kernel takes, an fp32 stream of its shape and a bfloat16 norm weight."""
+    return (isinstance(pending, PendingLinear) and pending.a.shape[0] <= 64 and gemm_tc_supported(pending.a, pending.w)
+            and x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == tuple(pending.shape)
+            and norm_weight.dtype == torch.bfloat16 and norm_weight.shape == (x.shape[1],))
+
+
+def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> ScaledRows:
+    """x += pending (in place, the fp32 residual stream) and the RMSNorm of the new x as `ScaledRows`:
+    one tensor-core product whose epilogue does the add, applies the norm weight and leaves the rows'
+    sums of squares; the scale itself is applied by the product that takes the result."""
+    if not residual_norm_supported(pending, x, norm_weight):
+        raise KernelError("linear_residual_norm: not a case the fused kernel takes")
+    a, w = pending.a, pending.w
+    _dev(a, "a"), _dev(w, "w"), _dev(x, "x"), _dev(norm_weight, "norm_weight")
+    M, K = a.shape
+    N = w.shape[0]
+    n_parts = _fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual_parts")(N, K)
+    xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
+    _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual")(
+        _p(a), _p(w), _p(x), _p(norm_weight), _p(xw), _p(parts), M, N, K, K, K, N, N,
+        _p(status_word(x.device)), _stream()), "gemm_tc_skinny_residual")
+    return ScaledRows(xw, parts, N, eps)
 
 
 def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
@@ -341,11 +434,14 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
-    whose epilogue applies the activation; [M, F] in bfloat16."""
-    _dev(a, "a"), _dev(w_gate_up, "w_gate_up")
-    M, K = a.shape
+    whose epilogue applies the activation; [M, F] in bfloat16.  `a` may be `ScaledRows`."""
+    if isinstance(a, ScaledRows) and not (a.shape[0] <= 64 and gemm_tc_supported(a.x, w_gate_up)):
+        a = a.materialize()
+    x = a.x if isinstance(a, ScaledRows) else a
+    _dev(x, "a"), _dev(w_gate_up, "w_gate_up")
+    M, K = x.shape
     N = w_gate_up.shape[0]
-    if not gemm_tc_supported(a, w_gate_up) or N % 128:
+    if not gemm_tc_supported(x, w_gate_up) or N % 128:
         raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
     if M <= 64:
         return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
@@ -515,11 +611,20 @@ def sample(logits: torch.Tensor, rng_state: torch.Tensor, temperature: float, to
 
 
 # ---------------------------------------------------------------- dispatchers
-def linear(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):
     """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
     types and shape, never by the model: the tensor cores for bfloat16 operands
     that TMA can address (the cluster kernel for up to 64 rows, the wide kernel
-    beyond), the CUDA cores for everything else."""
+    beyond), the CUDA cores for everything else.
+
+    `a` may be `ScaledRows`.  With `defer` (a float32 delta for the residual stream) the product may
+    come back as a `PendingLinear` for the next norm to run; whoever cannot use that calls `compute()`."""
+    if isinstance(a, ScaledRows):
+        if a.shape[0] <= 64 and out_dtype == torch.bfloat16 and gemm_tc_supported(a.x, w):
+            return gemm_tc_skinny(a, w, out_dtype)
+        a = a.materialize()
+    if defer and out_dtype == torch.float32 and a.shape[0] <= 64 and gemm_tc_supported(a, w):
+        return PendingLinear(a, w)
     if gemm_tc_supported(a, w):
         if a.shape[0] <= 64:
             return gemm_tc_skinny(a, w, out_dtype)

@@ -27,7 +27,15 @@ class PreNormBlock(Part):
                 (s.feed_forward_norm.prefix, self.feed_forward_norm), (s.feed_forward.prefix, self.feed_forward)]
 
     def forward(self, stream, step, cache):
-        h = self.mixer_norm.forward(stream)
+        h = self._norm(self.mixer_norm, self.mixer, stream)
         stream.pending = self.mixer.forward(h, step, cache)
-        h = self.feed_forward_norm.forward(stream)
+        h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
         stream.pending = self.feed_forward.forward(h, step)
+
+    @staticmethod
+    def _norm(norm, consumer, stream):
+        """A norm may leave its scale to the products of the part that takes its result, when both
+        say that they can (`can_defer_scale`, `takes_scaled_rows`)."""
+        if getattr(norm, "can_defer_scale", False) and getattr(consumer, "takes_scaled_rows", False):
+            return norm.forward(stream, defer_scale=True)
+        return norm.forward(stream)

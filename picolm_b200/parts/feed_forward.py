@@ -47,9 +47,11 @@ class GatedMLP(Part):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
+    takes_scaled_rows = True          # h goes into a product and nowhere else
+
     def forward(self, h, step):
         if self.fused:
             act = ops.linear_swiglu(h, self.w_gate_up)
         else:
             act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype))
-        return ops.linear(act, self.w_down, torch.float32)
+        return ops.linear(act, self.w_down, torch.float32, defer=True)

@@ -75,10 +75,12 @@ class Attention(Part):
     def prepare(self, max_seq_tokens: int) -> None:
         self.position.prepare(max_seq_tokens)
 
+    takes_scaled_rows = True          # h goes into a product and nowhere else
+
     def forward(self, h, step, cache):
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, dt)
         q = torch.empty((h.shape[0], self.H, self.hd), dtype=dt, device=h.device)
         self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
         ctx = ops.attention(q, cache, step, self.G, self.scale)
-        return ops.linear(ctx, self.w_o, torch.float32)
+        return ops.linear(ctx, self.w_o, torch.float32, defer=True)

@@ -26,10 +26,21 @@ class RMSNorm(Part):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
-    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    can_defer_scale = True
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, defer_scale: bool = False):
         """Normalise `x + pending`.  Without `rows` the sum is written back to the
         stream and the delta is consumed; with `rows` only those rows are
-        normalised and the stream is left as it is."""
+        normalised and the stream is left as it is.
+
+        With `defer_scale` (the caller hands the result to products only) a pending product runs
+        with the add, this norm's weight and the sums of squares in its epilogue, and the result is
+        `ops.ScaledRows`: the product that takes it applies the scale."""
+        if (defer_scale and rows is None
+                and ops.residual_norm_supported(stream.pending, stream.x, self.weight)):
+            h = ops.linear_residual_norm(stream.pending, stream.x, self.weight, self.params["eps"])
+            stream.pending = None
+            return h
         h = ops.rmsnorm(stream.x, self.weight, self.params["eps"], self.runtime.dtype,
                         delta=stream.pending, rows=rows)
         if rows is None:

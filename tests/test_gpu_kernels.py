@@ -293,6 +293,49 @@ def test_sample_distribution():
     assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
 
 
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("T,F,K,N2", [(1, 128, 64, 256), (8, 2048, 512, 3072), (17, 200, 264, 384), (33, 136, 1024, 128),
+                                       (64, 328, 192, 640)])
+def test_norm_split_over_two_products(T, F, K, N2, swiglu):
+    """An RMSNorm between two products, done by their epilogues: the first adds its result to the
+    residual stream, applies the norm's weight and leaves the rows' sums of squares; the second scales
+    its results.  Against x + a w^T, its RMSNorm and the product of that, in float64."""
+    from picolm_b200 import ops
+    torch.manual_seed(T + F + K)
+    eps = 1e-5
+    a = (torch.randn(T, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(F, K) / K ** 0.25).to(torch.bfloat16)
+    x = torch.randn(T, F) * torch.linspace(0.2, 5.0, T)[:, None]          # rows of very different size
+    nw = (1.0 + 0.3 * torch.randn(F)).to(torch.bfloat16)
+    w2 = (torch.randn(N2, F) / F ** 0.5).to(torch.bfloat16)
+    xn = x.double() + a.double() @ w.double().t()
+    h = xn / torch.sqrt((xn * xn).mean(dim=1, keepdim=True) + eps) * nw.double()
+    y = h @ w2.double().t()
+    xd = x.to(DEV)
+    pending = ops.linear(a.to(DEV), w.to(DEV), torch.float32, defer=True)
+    assert isinstance(pending, ops.PendingLinear)
+    rows = ops.linear_residual_norm(pending, xd, nw.to(DEV), eps)
+    assert torch.allclose(xd.double().cpu(), xn, atol=2e-3, rtol=1e-4)      # the stream, updated in place
+    assert torch.allclose(rows.materialize().double().cpu(), h, atol=3e-2, rtol=2e-2)
+    if swiglu:
+        w2d = ops.interleave_gate_up(w2[: N2 // 2].contiguous().to(DEV), w2[N2 // 2:].contiguous().to(DEV))
+        got = ops.linear_swiglu(rows, w2d).double().cpu()
+        g, u = y[:, : N2 // 2], y[:, N2 // 2:]
+        ref = g / (1 + torch.exp(-g)) * u
+    else:
+        got = ops.linear(rows, w2.to(DEV), torch.bfloat16).double().cpu()
+        ref = y
+    ops.check_status(DEV)
+    assert torch.allclose(got, ref, atol=4e-2, rtol=3e-2)
+    # the same rows in another batch give the same values: the sums run in a fixed order
+    if T > 1:
+        x1 = x[-1:].contiguous().to(DEV)
+        rows1 = ops.linear_residual_norm(ops.linear(a[-1:].contiguous().to(DEV), w.to(DEV), torch.float32, defer=True),
+                                         x1, nw.to(DEV), eps)
+        assert torch.equal(x1[0], xd[-1])
+        assert torch.equal(rows1.materialize()[0], rows.materialize()[-1])
+
+
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [
     (1, 128, 64), (8, 3072, 2048), (16, 200, 264), (17, 256, 512), (33, 130, 1024), (64, 2048, 8192),
