@@ -98,7 +98,8 @@ def bench_attention_decode(args):
     splits = args.splits or ops.decode_splits(B, H, G, C)
 
     def run(i):
-        ops.attention_decode(q, caches[i][0], caches[i][1], pos, seq, table, G, 1.0 / math.sqrt(hd), splits)
+        ops.attention_decode(q, caches[i][0], caches[i][1], pos, seq, table, G, 1.0 / math.sqrt(hd), splits,
+                             scratch={"auto": None, "cluster": False, "scratch": True}[args.merge])
 
     sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     return {"kernel": "attention_decode", "batch": B, "ctx": C, "heads": H, "kv_heads": G, "head_dim": hd,
@@ -131,6 +132,8 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--out", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--merge", default="auto", choices=["auto", "cluster", "scratch"],
+                    help="attention_decode: merge the key ranges inside a cluster or through scratch memory")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)

@@ -537,12 +537,17 @@ DECODE_CLUSTER_SPLITS = 8       # up to this many ranges merge inside a thread-b
 
 
 def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """Into how many ranges the decode kernel cuts each sequence's keys: about
-    eight pages a range (measured best at batch 8 and 64), more ranges when that
-    leaves SMs without a CTA, never less than two pages a range."""
+    """Into how many ranges the decode kernel cuts each sequence's keys.  Where the whole grid runs at once
+    (three CTAs an SM), as many ranges as that allows, up to the eight that merge inside a cluster, each of
+    at least two pages.  Otherwise, and for long contexts (whose ranges would get too long for one wave
+    of CTAs), about eight pages a range, more when that leaves SMs without a CTA (measured at batch 1, 8
+    and 64 with 2,048 keys)."""
     row_groups = (num_heads // num_kv_heads + 15) // 16
     ctas = max(1, n_tokens * num_kv_heads * row_groups)
     pages = max(1, (max_kv_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
+    in_cluster = min(DECODE_CLUSTER_SPLITS, (3 * _SM_COUNT) // ctas, max(1, pages // 2))
+    if in_cluster >= 2 and pages <= (16 if ctas * in_cluster >= _SM_COUNT else 8) * in_cluster:
+        return in_cluster
     splits = (pages + 7) // 8
     if ctas * splits < _SM_COUNT:
         splits = max(splits, min(max(1, pages // 2), (_SM_COUNT + ctas - 1) // ctas))
