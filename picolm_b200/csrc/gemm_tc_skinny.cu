@@ -4,11 +4,12 @@
 // columns, and K is split over the CTAs of a thread-block cluster so that every
 // SM streams a share of W.
 //
-// The K splits' partial sums never go to global memory: each CTA of the cluster
-// parks its fp32 partial tile in its own shared memory, the cluster meets at a
-// barrier, and every CTA then sums a slice of the tile's rows over all CTAs'
-// shared memory (distributed shared memory, ascending rank: a fixed order) and
-// writes that slice of the result.  Epilogues:
+// The K splits' partial sums never go to global memory: every CTA of the cluster
+// owns a slice of the tile's rows, each CTA sends the rows of its fp32 partial
+// tile straight from tensor memory to their owners' shared memory (stores into
+// distributed shared memory), the cluster meets at a barrier, and every CTA sums
+// what it received (ascending rank: a fixed order) and writes its slice of the
+// result.  Epilogues:
 //   EPI_STORE   out = sum                                  (fp32 or bf16)
 //   EPI_SWIGLU  W's rows come in tiles of 64 gate rows followed by their 64 up rows;
 //               out[t, f] = silu(gate) * up, each rounded to bf16 first
@@ -28,23 +29,19 @@ using namespace plm_tc;
 namespace {
 
 constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2;
-// ring depth: two CTAs of any tile width fit one SM (2 x ~100 KB)
-__host__ __device__ constexpr int stages_of(int bn) { return bn <= 32 ? 5 : 4; }
+// ring depth: with the buffer that receives the partial sums (bn x 128 floats), two CTAs of any tile
+// width fit one SM (2 x ~105 KB)
+__host__ __device__ constexpr int stages_of(int bn) { return bn <= 16 ? 5 : (bn <= 32 ? 4 : 3); }
 constexpr int MAX_SPLITS = 8;               // portable cluster size
 
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
+__device__ __forceinline__ void st_cluster(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-__device__ __forceinline__ float ld_cluster(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-    return v;
-}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 __host__ __device__ constexpr size_t skinny_smem(int bn) {
-    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256;
+    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + (size_t)bn * BM * 4 + 1024 + 256;
 }
 
 // What the fused forms of the kernel need beside the product itself.
@@ -77,16 +74,20 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     constexpr int STAGES = stages_of(BN);
     constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    static_assert(2 * BN * BM * 4 <= STAGES * (W_BYTES + X_BYTES), "the partial tile and the squares must fit the ring");
+    static_assert(BN * BM * 4 <= STAGES * (W_BYTES + X_BYTES), "the squares must fit the ring");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t w_smem = base, x_smem = base + STAGES * W_BYTES;
-    const uint32_t bars = x_smem + STAGES * X_BYTES;
+    const uint32_t recv_smem = x_smem + STAGES * X_BYTES;              // what the cluster sends here: never the ring,
+    const uint32_t bars = recv_smem + BN * BM * 4;                     // which this CTA may still be reading
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tmem_full = bars + 16 * STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 16 * STAGES + 8 - raw));
-    float* part = reinterpret_cast<float*>(smem_raw + (base - raw));     // [BN][128] partial tile, after the main loop
-    float* squares = part + BN * BM;                                     // EPI_RESIDUAL: [BN][rows of this CTA's slice]
+    // recv[source rank][token][half][row of the slice]: the partial sums of this CTA's rows (half: the
+    // gate and the up row of an output column with EPI_SWIGLU)
+    const float* recv = reinterpret_cast<const float*>(smem_raw + (recv_smem - raw));
+    float* squares = reinterpret_cast<float*>(smem_raw + (base - raw));  // EPI_RESIDUAL, after the main loop:
+                                                                         // [BN][rows of this CTA's slice]
     __shared__ int s_abort;
     __shared__ float s_scale[BN];
 
@@ -117,14 +118,24 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Shared memory of another CTA may be written only once that CTA runs: a first meeting of the
+    // cluster, whose wait every warp does before its own work (warp 0 after it has asked for weights).
+    cluster_arrive();
+    constexpr int ROWS = EPI == EPI_SWIGLU ? BM / 2 : BM;          // rows that produce an output column
+    constexpr int HALVES = BM / ROWS;
+    const int slice = ROWS / (int)S;                               // output rows that a CTA of the cluster owns
 
     if (warp == 0) {
+        const int early = n_kb < STAGES ? n_kb : STAGES;
         if (lane == 0) {
-            const int early = n_kb < STAGES ? n_kb : STAGES;
             for (int i = 0; i < early; ++i) {                      // weights: nobody in this step writes them
                 mbar_expect_tx(full0 + 8 * i, W_BYTES + X_BYTES);
                 tma_load_2d(w_smem + i * W_BYTES, &map_w, full0 + 8 * i, (kb_begin + i) * BK, p0);
             }
+        }
+        __syncwarp();
+        cluster_wait();
+        if (lane == 0) {
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 tma_load_2d(x_smem + i * X_BYTES, &map_x, full0 + 8 * i, (kb_begin + i) * BK, 0);
@@ -145,6 +156,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
         }
     } else if (warp == 1) {
+        cluster_wait();
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(BN);
             for (int i = 0; i < n_kb; ++i) {
@@ -164,6 +176,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             tc_commit(tmem_full);
         }
     } else {
+        cluster_wait();
         if (SCALE) {                                       // while the main loop runs: the rows' scale factors
             pdl_wait();
             const int t = threadIdx.x - 64;
@@ -174,12 +187,17 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 s_scale[t] = 1.0f / sqrtf(ss * fz.inv_size + fz.eps);
             }
         }
-        // park this CTA's partial tile in shared memory: part[token][feature row]
+        // send this CTA's partial tile, row by row, to the CTAs that own the rows
         const int quarter = warp & 3;
         const bool ready = mbar_wait(tmem_full, 0, status, 3);
         if (!ready) s_abort = 1;
         tc_fence_after();
         const int row = quarter * 32 + lane;
+        const int orow = row % ROWS, half = row / ROWS;                // output row, and gate or up
+        const int owner = orow / slice, pr = orow - owner * slice;
+        const uint32_t dst = cluster_map(recv, (uint32_t)owner)
+                           + (uint32_t)((((int)rank * BN) * HALVES + half) * slice + pr) * 4u;
+        const uint32_t col_stride = (uint32_t)(HALVES * slice) * 4u;
         constexpr int CHUNK = BN >= 32 ? 32 : 16;
 #pragma unroll 1
         for (int c = 0; c < BN; c += CHUNK) {
@@ -193,7 +211,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 for (int j = 0; j < CHUNK; ++j) r[j] = 0u;              // a CTA without K blocks adds nothing
             }
 #pragma unroll
-            for (int j = 0; j < CHUNK; ++j) part[(c + j) * BM + row] = __uint_as_float(r[j]);
+            for (int j = 0; j < CHUNK; ++j) st_cluster(dst + (uint32_t)(c + j) * col_stride, __uint_as_float(r[j]));
         }
     }
     tc_fence_before();
@@ -204,17 +222,18 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-    cluster_sync_all();                                            // every CTA's partial tile is in place
+    cluster_sync_all();                                            // everything sent has arrived
 
-    // ---- each CTA sums its slice of the tile's rows over all CTAs and writes it
+    // ---- this CTA sums what it received for its slice of the tile's rows and writes it
     pdl_wait();
-    const uint32_t part_addr = smem_u32(part);
-    uint32_t remote[MAX_SPLITS];
-#pragma unroll
-    for (uint32_t r = 0; r < MAX_SPLITS; ++r) remote[r] = r < S ? map_to_rank(part_addr, r) : 0u;
-    constexpr int ROWS = EPI == EPI_SWIGLU ? BM / 2 : BM;          // rows that produce an output column
-    const int slice = ROWS / (int)S;
     const int items = slice * BN;
+    auto received = [&](int c, int half, int pr) {
+        float v = 0.f;
+#pragma unroll
+        for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+            if (r < S) v += recv[(((int)r * BN + c) * HALVES + half) * slice + pr];
+        return v;
+    };
     for (int it = threadIdx.x; it < items; it += NUM_THREADS) {
         const int c = it / slice, pr = it - c * slice;
         const int row = (int)rank * slice + pr;
@@ -223,10 +242,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int f = p0 + row;
             float sq = 0.f;
             if (t < T && f < F) {
-                float v = 0.f;
-#pragma unroll
-                for (uint32_t r = 0; r < MAX_SPLITS; ++r)
-                    if (r < S) v += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+                const float v = received(c, 0, pr);
                 const float xn = to_f32(out[(size_t)t * ldo + f]) + v;
                 out[(size_t)t * ldo + f] = from_f32<OutT>(xn);
                 fz.xw[(size_t)t * fz.ld_xw + f] = __float2bfloat16_rn(xn * __bfloat162float(fz.norm_w[f]));
@@ -239,22 +255,13 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (EPI == EPI_STORE) {
             const int f = p0 + row;
             if (f >= F) continue;
-            float v = 0.f;
-#pragma unroll
-            for (uint32_t r = 0; r < MAX_SPLITS; ++r)
-                if (r < S) v += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
+            float v = received(c, 0, pr);
             if (SCALE) v *= s_scale[c];
             out[(size_t)t * ldo + f] = from_f32<OutT>(v);
         } else {
             const int fo = p0 / 2 + row;
             if (fo >= F / 2) continue;
-            float g = 0.f, u = 0.f;
-#pragma unroll
-            for (uint32_t r = 0; r < MAX_SPLITS; ++r)
-                if (r < S) {
-                    g += ld_cluster(remote[r] + (uint32_t)(c * BM + row) * 4u);
-                    u += ld_cluster(remote[r] + (uint32_t)(c * BM + BM / 2 + row) * 4u);
-                }
+            float g = received(c, 0, pr), u = received(c, HALVES - 1, pr);
             if (SCALE) { g *= s_scale[c]; u *= s_scale[c]; }
             out[(size_t)t * ldo + fo] = from_f32<OutT>(swiglu_bf16(g, u));
         }
@@ -265,7 +272,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         for (int pr = 0; pr < slice; ++pr) ss += squares[threadIdx.x * slice + pr];
         fz.ss_out[((size_t)blockIdx.x * S + rank) * SS_STRIDE + threadIdx.x] = ss;
     }
-    cluster_sync_all();                                            // nobody reads this CTA's tile any more
+    // (no second meeting: after the first nobody touches another CTA's shared memory)
 }
 
 template <int BN, int EPI, typename OutT, bool SCALE>
