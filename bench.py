@@ -223,10 +223,15 @@ def main():
         sampler = ClockSampler() if sample_clocks else None
         if sampler:
             sampler.__enter__()
+        # The timed steps feed each sampled token to the next step on the device; the ids reach the
+        # host by a copy per step that nobody waits for until the end (as the generation loop does).
+        pinned = torch.empty((steps, batch), dtype=torch.int32).pin_memory()
+        tok_dev = torch.tensor(toks, dtype=torch.int32, device="cuda:0")
         torch.cuda.synchronize()
         a.record()
-        for _ in range(steps):
-            toks = ops.argmax(engine.step([(s, [t]) for s, t in zip(slots, toks)])).tolist()
+        for j in range(steps):
+            tok_dev = ops.argmax(engine.step_device_tokens(slots, tok_dev), out=engine.token_buffer(batch))
+            engine.fetch_later(tok_dev, pinned[j])
         b.record()
         torch.cuda.synchronize()
         if sampler:

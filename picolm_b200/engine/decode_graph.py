@@ -46,7 +46,9 @@ class DecodeGraph:
         dev = engine.runtime.device
         P = cache.pages_per_seq
         n_groups = len(cache.kv_groups)
-        # layout: tok_ids, tok_seq, tok_pos, seq_slot, seq_start, seq_kv_len, want_rows, block tables
+        # layout: tok_ids, tok_seq, tok_pos, seq_slot, seq_start, seq_kv_len, want_rows, block tables.
+        # On the device the token ids live in the engine's one token buffer instead (all graphs read
+        # it, and a sampler may write the next step's ids straight into it).
         self.sizes = [B, B, B, B, B + 1, B, B] + [B * P] * n_groups
         total = sum(self.sizes)
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
@@ -58,6 +60,7 @@ class DecodeGraph:
             self.h.append(self.host_np[o:o + n])
             self.d.append(self.dev[o:o + n])
             o += n
+        self.d[0] = engine.token_buffer(B)
         self.h[1][:] = np.arange(B)                       # tok_seq: one token per sequence
         self.h[4][:] = np.arange(B + 1)                   # seq_start
         self.h[6][:] = np.arange(B)                       # want_rows: every row
@@ -74,7 +77,8 @@ class DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
 
-    def _fill(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> None:
+    def _fill(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int],
+              device_tokens: Optional[torch.Tensor] = None) -> None:
         n, B = len(slots), self.batch
         cache = self.engine.cache
         h = self.h
@@ -91,6 +95,11 @@ class DecodeGraph:
             table[:n] = cache.block_table_rows(g, slots)
             table[n:] = 0                                 # the null page
         self.dev.copy_(self.host, non_blocking=True)
+        if device_tokens is None:
+            self.d[0].copy_(self.dev[:B])
+        elif device_tokens.data_ptr() != self.d[0].data_ptr():
+            # the token ids are on the device already; rows of padding keep whatever valid id they held
+            self.d[0][:n].copy_(device_tokens)
         self.copied.record()
 
     def capture(self) -> None:
@@ -118,11 +127,13 @@ class DecodeGraph:
         self.launches = ops.launch_count() - n0
         ops.count_launches(-self.launches)                # the capture itself ran nothing
 
-    def run(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> torch.Tensor:
+    def run(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int],
+            device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Replay for `len(slots)` real sequences; returns logits [len(slots), vocab],
-        valid until the next replay of this graph."""
+        valid until the next replay of this graph.  With `device_tokens` (int32 [len(slots)] on the
+        device) the token ids come from there instead of `tokens`."""
         from .. import ops
-        self._fill(slots, tokens, positions)
+        self._fill(slots, tokens, positions, device_tokens)
         self.graph.replay()
         ops.count_launches(self.launches)
         return self.logits[:len(slots)]

@@ -50,7 +50,13 @@ class Engine:
         safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks)
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
+        self._tokens = torch.zeros(256, dtype=torch.int32, device=self.runtime.device)
         self.reset_counters()
+
+    def token_buffer(self, n: int) -> torch.Tensor:
+        """The first `n` entries of the buffer from which captured decode steps read their token ids.  A
+        sampler that writes its result here (`out=`) saves `step_device_tokens` a copy."""
+        return self._tokens[:n]
 
     def reset_counters(self) -> None:
         """Bytes copied between host and device by the steps since the last reset."""
@@ -60,6 +66,12 @@ class Engine:
         """Sampled token ids as a host list (one device-to-host copy)."""
         self.counters["d2h_bytes"] += tokens.numel() * tokens.element_size()
         return tokens.tolist()
+
+    def fetch_later(self, tokens: torch.Tensor, pinned_row: torch.Tensor) -> None:
+        """Start copying sampled token ids into a row of pinned host memory without waiting for them;
+        `synchronize()` (or an event) says when they are there."""
+        pinned_row.copy_(tokens, non_blocking=True)
+        self.counters["d2h_bytes"] += tokens.numel() * tokens.element_size()
 
     # ----------------------------------------------------------- construction
     @staticmethod
@@ -112,30 +124,49 @@ class Engine:
             if lo < 0 or hi >= self.vocab_size:
                 raise ValueError(f"slot {slot}: token id {lo if lo < 0 else hi} is outside the vocabulary "
                                  f"[0, {self.vocab_size})")
+        return self._run(entries, wants, None)
+
+    def step_device_tokens(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One more token for each of the sequences in `slots`, the tokens taken from an int32 tensor
+        on the device (what the sampler wrote for the step before): the same step as
+        `step([(slot, [token]), ...])`, but the host need not know the tokens to launch it, so it can
+        prepare and launch steps while earlier ones still run.  The token ids must lie inside the
+        vocabulary (the sampling kernels' results do).  Returns the logits of every sequence."""
+        if not slots:
+            raise ValueError("no sequences")
+        if tokens.dtype != torch.int32 or not tokens.is_cuda or tokens.numel() != len(slots):
+            raise ValueError("tokens must be an int32 tensor on the device, one per sequence")
+        return self._run([(slot, [0]) for slot in slots], [[0]] * len(slots), tokens)
+
+    def _run(self, entries, wants, device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         self.cache.reserve([(slot, len(toks)) for slot, toks in entries])
         logits = None
+        graphed = False
         if self.use_graphs and all(len(toks) == 1 for _, toks in entries):
-            logits = self._decode_with_graph(entries, wants)
-        if logits is None:
+            logits, graphed = self._decode_with_graph(entries, wants, device_tokens)
+        if not graphed:
             batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
             self.counters["h2d_bytes"] += batch.h2d_bytes
+            if device_tokens is not None:
+                batch.tok_ids.copy_(device_tokens)
             logits = self.model.forward(batch, self.cache)
         self.counters["steps"] += 1
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))
         return logits
 
-    def _decode_with_graph(self, entries, wants) -> Optional[torch.Tensor]:
-        """One token for each sequence through the captured graph of the batch's size class.  Returns None
-        if this step cannot use one (batch too large, or places wanted that are not exactly [0])."""
+    def _decode_with_graph(self, entries, wants, device_tokens=None) -> Tuple[Optional[torch.Tensor], bool]:
+        """One token for each sequence through the captured graph of the batch's size class.  Returns the
+        logits (None if none are wanted) and whether a graph ran: it does not if the batch is too large
+        or places are wanted that are not exactly [0]."""
         from .decode_graph import DecodeGraph, bucket_for, length_class
         n = len(entries)
         bucket = bucket_for(n)
         if bucket is None:
-            return None
+            return None, False
         n_want = sum(len(w) for w in wants)
         if n_want not in (0, n) or any(list(w) not in ([], [0]) for w in wants):
-            return None
+            return None, False
         slots = [s for s, _ in entries]
         positions = [self.cache.length(s) for s in slots]
         key = (bucket, length_class(max(positions) + 1, self.cache.max_seq_tokens))
@@ -144,6 +175,6 @@ class Engine:
             g = DecodeGraph(self, key[0], key[1])
             g.capture()
             self._graphs[key] = g
-        logits = g.run(slots, [t[0] for _, t in entries], positions)
+        logits = g.run(slots, [t[0] for _, t in entries], positions, device_tokens)
         self.counters["h2d_bytes"] += g.step.h2d_bytes
-        return logits if n_want else None
+        return (logits if n_want else None), True

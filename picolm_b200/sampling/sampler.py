@@ -62,9 +62,9 @@ class Sampler:
         if self.rng is not None:
             self.rng = self.rng[torch.tensor(list(rows), dtype=torch.int64, device=self.device)].contiguous()
 
-    def sample(self, logits: torch.Tensor) -> torch.Tensor:
-        """logits fp32 [rows, vocab] -> int32 [rows]."""
+    def sample(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """logits fp32 [rows, vocab] -> int32 [rows] (into `out` if given)."""
         p = self.params
         if p.greedy:
-            return ops.argmax(logits)
-        return ops.sample(logits, self.rng, p.temperature, p.top_k, p.top_p, p.min_p)
+            return ops.argmax(logits, out=out)
+        return ops.sample(logits, self.rng, p.temperature, p.top_k, p.top_p, p.min_p, out=out)

@@ -6,7 +6,7 @@ from types import SimpleNamespace
 import pytest
 
 from picolm_b200.cache import CacheSpec, SequenceCache
-from picolm_b200.engine.generate import Request, finish_reason, generate, plan_batch, tokens_reserved
+from picolm_b200.engine.generate import Request, finish_reason, generate, plan_batch, steps_ahead, tokens_reserved
 from picolm_b200.sampling import SamplingParams, stream_seed
 
 
@@ -124,3 +124,50 @@ def test_zero_new_tokens_and_empty_prompt():
     assert outs == [[]] and stats.steps == 0
     with pytest.raises(ValueError, match="empty"):
         generate(eng, [[]], max_tokens=1, sampler_factory=FakeSampler)
+
+
+def test_steps_ahead():
+    # two sequences with 1 and 3 new tokens so far of at most 10 and 5: the second ends in 2 steps
+    assert steps_ahead(8, [1, 3], [10, 5], [20, 30], 100) == 2
+    assert steps_ahead(8, [1], [100], [20], 100) == 8
+    assert steps_ahead(8, [1], [100], [97], 100) == 3      # the context: 97 cached, 3 more can be fed
+    assert steps_ahead(8, [4], [5], [99], 100) == 1
+
+
+class StretchEngine(FakeEngine):
+    """A fake engine that can take a step's tokens from 'the device' (a tensor)."""
+
+    def step_device_tokens(self, slots, tokens):
+        import torch
+        return torch.tensor(self.step([(s, [int(t)]) for s, t in zip(slots, tokens.tolist())]), dtype=torch.int32)
+
+    def fetch_later(self, tokens, row):
+        row.copy_(tokens)
+
+
+class TensorSampler(FakeSampler):
+    def sample(self, logits):
+        import torch
+        assert len(logits) == len(self.rows)
+        return torch.as_tensor(logits, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("most", [2, 3, 8])
+def test_stretches_give_the_same_output(most):
+    """The host looking in only every few steps changes nothing but the work done: stop tokens met in
+    between cut the output where they stand, limits are met exactly, slots come back."""
+    prompts = [[10, 11, 12], [45], [20] * 40, [30, 31], [48, 49], [44], [90] * 95]
+    want, _ = generate(FakeEngine(), prompts, max_tokens=7, sampling=SamplingParams(temperature=0.0),
+                       sampler_factory=FakeSampler, steps_per_sync=1)
+    eng = StretchEngine()
+    outs, stats = generate(eng, prompts, max_tokens=7, sampling=SamplingParams(temperature=0.0),
+                           sampler_factory=TensorSampler, steps_per_sync=most)
+    assert outs == want
+    assert outs[1] == [46, 47, 48, 49, 50] and outs[4] == [50] and outs[6] == [91, 92, 93, 94, 95, 96]
+    assert stats.generated_tokens == sum(len(o) for o in outs)
+    # nothing is fed past a sequence's limits: no sequence grew beyond the context
+    for step in eng.steps:
+        for slot, toks in step:
+            assert len(toks) >= 1
+    eng.cache.check()
+    assert eng.cache.slots.used == 0 and eng.cache.kv_groups[0].pool.used == 0

@@ -32,6 +32,10 @@ def test_greedy_generation_matches_the_plain_implementation(model_dirs, name):
     eng.cache.check()
     # alone or in a batch: the same tokens
     assert generate(eng, [prompts[1]], max_tokens=10, temperature=0.0, stop_ids=[stop]) == [want[1]]
+    # the host looking at the tokens after every step, or only every few steps: the same tokens
+    for every in (1, 3):
+        assert generate(eng, prompts, max_tokens=10, temperature=0.0, stop_ids=[stop], steps_per_sync=every) == want
+    eng.cache.check()
 
 
 def test_bfloat16_greedy_follows_the_plain_bfloat16_twin(model_dirs):
@@ -65,6 +69,10 @@ def test_sampling_is_seeded_per_request(model_dirs):
     one_by_one = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[],
                           max_batch=1)
     assert one_by_one == a
+    every_step = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[a[1][3]],
+                          steps_per_sync=1)
+    stretches = generate(eng, prompts, max_tokens=16, temperature=0.9, top_k=20, top_p=0.95, seed=7, stop_ids=[a[1][3]])
+    assert every_step == stretches and len(stretches[1]) <= 4
 
 
 def test_command_line(model_dirs):
