@@ -28,12 +28,13 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}     # an earlier measurement on this pool
 
 
-def bench_config():
-    """The sizes of BASELINE.json's configs[2], read from its text."""
+def bench_config(index=2):
+    """The sizes of BASELINE.json's configs[index] (2, the Llama-3.2-1B shape, unless asked otherwise),
+    read from its text."""
     text = ""
     try:
         with open(os.path.join(ROOT, "BASELINE.json")) as f:
-            text = json.load(f)["configs"][2]
+            text = json.load(f)["configs"][index]
     except (OSError, KeyError, IndexError, ValueError):
         pass
 
@@ -51,13 +52,17 @@ def bench_config():
                          "low_freq_factor": float(num(r"low_freq (\d+)", 1)),
                          "high_freq_factor": float(num(r"high_freq (\d+)", 4)),
                          "original_max_position_embeddings": num(r"original (\d+)", 8192)},
-        "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": "tied" in text or not text,
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": "untied" not in text,
         "hidden_act": "silu", "bos_token_id": 128000, "eos_token_id": 128001,
     }
     m = re.search(r"rms_norm_eps ([0-9.e-]+)", text)
     if m:
         cfg["rms_norm_eps"] = float(m.group(1).rstrip("."))
-    return cfg, num(r"context (\d+)", 4096), num(r"prefill at ([\d,]+) tokens", 2048), num(r"seed (\d+)", 2)
+    if "no rope scaling" in text:
+        cfg["rope_scaling"] = None
+    name = text.split(",")[0].strip() or "Llama-3.2-1B shape"
+    prompt = num(r"prefill at ([\d,]+) tokens", 0) or num(r"([\d,]+)-token random-id prompts", 2048)
+    return cfg, num(r"context (\d+)", 4096), prompt, num(r"seed (\d+)", 2), name
 
 
 def peaks():
@@ -143,6 +148,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
+                    help="which of BASELINE.json's configs gives the layer sizes (default 2, the headline)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 decode points")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
@@ -161,14 +168,14 @@ def main():
     from picolm_b200.engine import Engine
     from picolm_b200.weights import write_random_model
 
-    cfg_dict, context, prefill_tokens, seed = bench_config()
+    cfg_dict, context, prompt_len, seed, model_name = bench_config(args.config)
+    prefill_tokens = min(2048, context)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
     cfg = config_from_dict(cfg_dict)
     pk, pk_src = peaks()
     torch.cuda.set_device(0)
-    prompt_len = prefill_tokens
     B = args.batch
     points_b = [] if args.skip_points else [1, 64]
     max_b = max([B] + points_b)
@@ -182,8 +189,8 @@ def main():
     g = torch.Generator().manual_seed(seed)
     vocab = cfg.vocab_size
 
-    def prompts(n):
-        return [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(n)]
+    def prompts(n, length=None):
+        return [torch.randint(0, vocab, (length or prompt_len,), generator=g).tolist() for _ in range(n)]
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
@@ -192,7 +199,7 @@ def main():
     reps = 5
     times = []
     for i in range(args.warmup + reps):
-        p = prompts(1)[0]
+        p = prompts(1, prefill_tokens)[0]
         s = engine.new_sequence()
         a, b = ev(), ev()
         torch.cuda.synchronize()
@@ -269,16 +276,16 @@ def main():
            "prefill_tokens_per_s": round(stats.prefill_tokens / stats.prefill_seconds, 1)}
 
     out = {
-        "metric": "decode tokens/s (Llama-3.2-1B shape, bf16, batch 8, 1 B200)", "value": round(value, 1),
+        "metric": f"decode tokens/s ({model_name}, bf16, batch {B}, 1 B200)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random token ids, random-init weights N(0, 0.02)", "impl": "ours",
-        "config": {"model": "Llama-3.2-1B shape", "layers": cfg.num_hidden_layers, "layers_in_config": full_layers,
+        "config": {"model": model_name, "layers": cfg.num_hidden_layers, "layers_in_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "tied": cfg.tie_word_embeddings, "global_batch": B, "seq_len": context, "prompt_len": prompt_len,
                    "prefill_tokens": prefill_tokens, "parallelism": "none (1 GPU)",
-                   "l2": "every step reads all weights (2.5 GB > 126 MB L2); no flush"},
+                   "l2": f"every step reads all weights ({w_bytes / 1e9:.1f} GB > 126 MB L2); no flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
         "points": points,
     }
