@@ -44,24 +44,7 @@ __host__ __device__ constexpr size_t skinny_smem(int bn) {
     return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + (size_t)bn * BM * 4 + 1024 + 256;
 }
 
-// What the fused forms of the kernel need beside the product itself.
-//
-// An RMSNorm between two products is split over them.  The product before it (EPI_RESIDUAL) adds
-// its result to the fp32 residual stream `out` in place, writes xw = bf16(new row * norm weight) for
-// the product after it, and for every token the sum of squares of the new values that this CTA
-// wrote, one row of ss_out per (tile, cluster rank).  The product after it (SCALE) multiplies in xw and
-// scales token t's results by r[t] = 1 / sqrt(sum of those partial sums / size + eps): the
-// normalisation commutes with the product.  All sums run in a fixed order.
-struct Fuse {
-    const float* scale_parts;   // SCALE: [n_parts, 64]
-    int n_parts;
-    float inv_size, eps;
-    const bf16* norm_w;         // EPI_RESIDUAL: [F]
-    bf16* xw;                   // EPI_RESIDUAL: [T, ld_xw]
-    long ld_xw;
-    float* ss_out;              // EPI_RESIDUAL: [tiles * S, 64]
-};
-constexpr int SS_STRIDE = 64;   // tokens per row of the partial sums of squares (the most this kernel takes)
+constexpr int SS_STRIDE = 64;   // tokens per row of the partial sums of squares that this kernel writes (the most it takes)
 
 // W: [F, K] (P operand, 128 rows per tile), X: [T, K] (Q operand, BN rows).  grid = (F tiles, 1, S),
 // cluster = (1, 1, S).  out row stride ldo.  For EPI_SWIGLU, F counts W's rows (gate and up together)
@@ -183,7 +166,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (t < BN) {
                 float ss = 0.f;
                 if (t < T)
-                    for (int p = 0; p < fz.n_parts; ++p) ss += fz.scale_parts[(size_t)p * SS_STRIDE + t];
+                    for (int p = 0; p < fz.n_parts; ++p) ss += fz.scale_parts[(size_t)p * fz.ld_parts + t];
                 s_scale[t] = 1.0f / sqrtf(ss * fz.inv_size + fz.eps);
             }
         }
@@ -367,14 +350,14 @@ extern "C" int plm_gemm_tc_skinny_residual(const void* x, const void* w, float* 
 // The product behind an RMSNorm whose weight is already in x (see Fuse): like plm_gemm_tc_skinny with
 // bfloat16 output, token t's results scaled by 1 / sqrt(sum_p scale_parts[p, t] / size + eps).
 extern "C" int plm_gemm_tc_skinny_scaled(const void* x, const void* w, void* out, int epilogue, int T, int F, int K,
-                                         long ldx, long ldw, long ldo, const float* scale_parts, int n_parts, int size,
-                                         float eps, int* status, cudaStream_t stream) {
+                                         long ldx, long ldw, long ldo, const float* scale_parts, int n_parts,
+                                         int ld_parts, int size, float eps, int* status, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return PLM_OK;
     if (T > 64) return PLM_ERR_UNSUPPORTED;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU && F % 128) return PLM_ERR_SHAPE;
     if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
-    if (!scale_parts || n_parts <= 0 || size <= 0) return PLM_ERR_SHAPE;
+    if (!scale_parts || n_parts <= 0 || size <= 0 || ld_parts < T) return PLM_ERR_SHAPE;
     const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
     const int S = plm_gemm_tc_skinny_splits(F, K);
     CUtensorMap mw, mx;
@@ -384,6 +367,7 @@ extern "C" int plm_gemm_tc_skinny_scaled(const void* x, const void* w, void* out
     Fuse fz = {};
     fz.scale_parts = scale_parts;
     fz.n_parts = n_parts;
+    fz.ld_parts = ld_parts;
     fz.inv_size = 1.0f / (float)size;
     fz.eps = eps;
     if (epilogue == EPI_SWIGLU)

@@ -146,4 +146,22 @@ static inline int make_map(CUtensorMap* map, const void* ptr, long rows, long K,
 }
 
 
+// What the fused forms of the product kernels need beside the product itself.
+//
+// An RMSNorm between two products is split over them.  The product before it (EPI_RESIDUAL) adds
+// its result to the fp32 residual stream `out` in place, writes xw = bf16(new row * norm weight) for
+// the product after it, and for every token the sum of squares of the new values that this CTA
+// wrote, one row of ss_out per CTA that wrote part of the row.  The product after it (SCALE) multiplies in xw and
+// scales token t's results by r[t] = 1 / sqrt(sum of those partial sums / size + eps): the
+// normalisation commutes with the product.  All sums run in a fixed order.
+struct Fuse {
+    const float* scale_parts;   // SCALE: [n_parts, ld_parts], column t for token t
+    int n_parts, ld_parts;
+    float inv_size, eps;
+    const bf16* norm_w;         // EPI_RESIDUAL: [F]
+    bf16* xw;                   // EPI_RESIDUAL: [T, ld_xw]
+    long ld_xw;
+    float* ss_out;              // EPI_RESIDUAL: [rows as the kernel says, its own row length]
+};
+
 }  // namespace plm_tc

@@ -26,7 +26,7 @@ _SIGNATURES = {
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_skinny_residual_parts": [_i, _i],
-    "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _f, _vp, _vp],
+    "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _i, _f, _vp, _vp],
     "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
@@ -314,7 +314,8 @@ def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = Fa
     if scaled is not None:
         _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_scaled")(
             _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
-            scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()), "gemm_tc_skinny_scaled")
+            scaled.parts.shape[1], scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()),
+            "gemm_tc_skinny_scaled")
         return out
     _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
@@ -342,7 +343,7 @@ class PendingLinear:
 
 class ScaledRows:
     """An RMSNorm whose scale is still due: `x` [T, size] in bfloat16 holds row * norm weight, and
-    `parts` [n, 64] partial sums of squares of the rows (column t for row t), so that the normalised
+    `parts` [n, >= T] partial sums of squares of the rows (column t for row t), so that the normalised
     row t is x[t] / sqrt(sum(parts[:, t]) / size + eps).  A product takes it as its left operand and
     applies the scale to its result (`linear`, `linear_swiglu`); `materialize()` gives the rows."""
     __slots__ = ("x", "parts", "size", "eps")
@@ -373,7 +374,9 @@ class ScaledRows:
 
 def residual_norm_supported(pending, x: torch.Tensor, norm_weight: torch.Tensor) -> bool:
     """Whether `linear_residual_norm` takes this case: a pending product of at most 64 rows that the
-    cluster kernel takes, an fp32 stream of its shape and a bfloat16 norm weight."""
+    cluster kernel takes, an fp32 stream of its shape and a bfloat16 norm weight.  (For more rows the
+    fused epilogue was measured slower than a norm kernel of its own: there a thread of the epilogue
+    holds a row of the tile, and its read-modify-write of the stream does not coalesce.)"""
     return (isinstance(pending, PendingLinear) and pending.a.shape[0] <= 64 and gemm_tc_supported(pending.a, pending.w)
             and x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == tuple(pending.shape)
             and norm_weight.dtype == torch.bfloat16 and norm_weight.shape == (x.shape[1],))
@@ -389,8 +392,8 @@ def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: t
     _dev(a, "a"), _dev(w, "w"), _dev(x, "x"), _dev(norm_weight, "norm_weight")
     M, K = a.shape
     N = w.shape[0]
-    n_parts = _fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual_parts")(N, K)
     xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    n_parts = _fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual_parts")(N, K)
     parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
     _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual")(
         _p(a), _p(w), _p(x), _p(norm_weight), _p(xw), _p(parts), M, N, K, K, K, N, N,

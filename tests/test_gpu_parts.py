@@ -100,14 +100,18 @@ def test_attention_part_with_rope_options(dtype, pairing):
     torch.manual_seed(4)
     w = {n: (torch.randn(s.shape) * 0.15).to(DT[dtype]) for n, s in specs.items()}
     mixer.load({n: t.to(DEV) for n, t in w.items()})
-    lens = [70, 9]
+    lens = [40, 9]                                       # few enough rows for the last product to come back unrun
     cache, step = _step_and_cache(rt, [mixer.cache_spec()], lens)
     mixer.prepare(cache.max_seq_tokens)
     from picolm_b200.cache import KVLayerCache
     g = cache.kv_groups[0]
     view = KVLayerCache(g.k[0], g.v[0], step.block_tables[0], None, True)
     h = torch.randn(sum(lens), d).to(DT[dtype])
-    out = mixer.forward(h.to(DEV), step, view).cpu()
+    out = mixer.forward(h.to(DEV), step, view)
+    if dtype == "bfloat16":                              # a delta that the next norm may run (or anyone, by compute())
+        assert isinstance(out, ops.PendingLinear)
+        out = out.compute()
+    out = out.cpu()
     rnd = (lambda t: t.to(DT[dtype]).float())
     cos, sin = P.rope_table(max(lens), rot, 777.0, scaling)
     cos, sin = cos.float(), sin.float()
