@@ -119,11 +119,16 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __shared__ int s_abort;
 
     pdl_launch_dependents();
-    const int b = blockIdx.z, h = blockIdx.y;
+    // Blocks start in the order of their index (x fastest): the longest query tiles (those at the end of
+    // a sequence, which see the most keys) of all heads first, the short ones fill the end.  Heads of
+    // one KV head are neighbours, so they stream the same keys at about the same time.
+    const int b = blockIdx.z;
+    const int lin = blockIdx.y * gridDim.x + blockIdx.x;
+    const int h = lin % H, rank_of_tile = lin / H;
     const int t0 = seq_start[b], n_new = seq_start[b + 1] - t0;          // inputs written before the step began
     const int n_tiles = (n_new + BQ - 1) / BQ;
-    if ((int)blockIdx.x >= n_tiles) return;
-    const int tile = n_tiles - 1 - blockIdx.x;                          // the longest tiles first
+    if (rank_of_tile >= n_tiles) return;
+    const int tile = n_tiles - 1 - rank_of_tile;
     const int kv_len = seq_kv_len[b];
     const int pos0 = kv_len - n_new + tile * BQ;                         // position of the tile's first row
     const int rows = min(BQ, n_new - tile * BQ);
