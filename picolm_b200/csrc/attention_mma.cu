@@ -303,7 +303,9 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     float* merge = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES);      // reused after the last tile
     float* result = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES + DC_MERGE_BYTES);
     pdl_launch_dependents();
-    pdl_wait();
+    // What describes the step (positions, page tables) was written before the step began, and pages
+    // before a sequence's last one hold keys of earlier steps: all of that may be read before the
+    // kernel in front of this one (which writes this step's key and the queries) has finished.
     const int n_splits = gridDim.x, split = blockIdx.x;
     const int g = blockIdx.y / row_groups, rg = blockIdx.y - g * row_groups;
     const int t = blockIdx.z;
@@ -321,6 +323,21 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
 
+    auto issue = [&](int i) {
+        const size_t base = ((size_t)pages[p_begin + i] * G + g) * PLM_PAGE * HD;
+        const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
+        load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
+        load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
+    };
+    const int n_first = min(n_pages, DC_STAGES - 1);                    // pages asked for before the loop
+    const bool early = n_first <= 0 || p_begin + n_first - 1 < page_last;  // none of them is written in this step
+    if (!early) pdl_wait();
+#pragma unroll
+    for (int i = 0; i < DC_STAGES - 1; ++i) {
+        if (i < n_pages) issue(i);
+        cp_commit();
+    }
+    if (early) pdl_wait();
     if (!CLUSTER && n_pages <= 0) {                     // an empty split: weight zero in the merge
         for (int r = threadIdx.x; r < n_rows; r += NT) {
             float* ml = ws_ml + (((size_t)t * H + h0 + r) * n_splits + split) * 2;
@@ -329,24 +346,13 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
         return;
     }
     if (n_pages > 0) {                                  // (in a cluster an empty split still meets the others)
-        constexpr int CPR = HD / 8;
+        constexpr int CPR = HD / 8;                     // the queries: plain loads, visible after the loop's first barrier
         for (int c = threadIdx.x; c < 16 * CPR; c += NT) {
             const int r = c / CPR, col = c - r * CPR;
-            bf16* dst = q_s + r * LDS + col * 8;
-            if (r < n_rows) cp_async16(smem_u32(dst), q + ((size_t)t * H + h0 + r) * HD + col * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * H + h0 + r) * HD + col * 8);
+            *reinterpret_cast<uint4*>(q_s + r * LDS + col * 8) = v;
         }
-    }
-    auto issue = [&](int i) {
-        const size_t base = ((size_t)pages[p_begin + i] * G + g) * PLM_PAGE * HD;
-        const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
-        load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
-        load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
-    };
-#pragma unroll
-    for (int i = 0; i < DC_STAGES - 1; ++i) {
-        if (i < n_pages) issue(i);
-        cp_commit();
     }
     float o[HD / 8][4];
 #pragma unroll
