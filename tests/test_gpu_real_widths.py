@@ -67,3 +67,34 @@ def test_graph_and_plain_launches_agree(real):
         assert bool(eng._graphs) == graphs
         del eng
     assert_close(outs[0], outs[1], "bfloat16", "graph against plain launches")
+
+
+# A narrow model with the head size of the larger Llamas: 128-wide heads go through the other
+# instantiation of every attention kernel (tcgen05 prefill, mma.sync decode in and outside a cluster).
+CONFIG_HD128 = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 640,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 1792,
+    "vocab_size": 2000, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-6, "max_position_embeddings": 4096, "tie_word_embeddings": False, "hidden_act": "silu",
+    "bos_token_id": 1, "eos_token_id": 2,
+}
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_head_size_128_in_every_cut(tmp_path_factory, dtype):
+    from picolm_b200.engine import Engine
+    d = make_model_dir(str(tmp_path_factory.mktemp("hd128") / "m"), CONFIG_HD128, 5, sharpen=4.0)
+    cfg, w = P.load_model(d)
+    toks = {n: random_tokens(n, CONFIG_HD128["vocab_size"], 500 + n) for n in (300, 130, 40)}
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    ref = {n: P.forward(cfg, w, t, act_dtype=act) for n, t in toks.items()}
+    eng = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 24, max_seqs=4)
+    assert_close(run_whole(eng, toks[300]), ref[300], dtype, f"hd128 {dtype} whole")
+    assert_close(run_tail(eng, toks[130], tail=32), ref[130], dtype, f"hd128 {dtype} tail")
+    outs = run_batch(eng, [toks[300], toks[40], toks[130]], [200, 25, 100])
+    for n, got in zip((300, 40, 130), outs):
+        assert_close(got, ref[n], dtype, f"hd128 {dtype} batch {n}")
+    eng.cache.check()
+    if dtype == "bfloat16":
+        from picolm_b200 import ops
+        ops.check_status()
