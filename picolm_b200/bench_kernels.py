@@ -4,6 +4,8 @@ against the bytes it has to move or the flops it has to do.
     python -m picolm_b200.bench_kernels gemm --m 8 --n 16384 --k 2048
     python -m picolm_b200.bench_kernels attention_decode --batch 8 --ctx 2048 --heads 32 --kv-heads 8 --head-dim 64
     python -m picolm_b200.bench_kernels attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
+    python -m picolm_b200.bench_kernels sample --batch 8 --vocab 128256 --temperature 0.8 --top-k 40 --top-p 0.9
+    python -m picolm_b200.bench_kernels gemm --m 8 --n 2048 --k 8192 --residual      (the product with the norm's half)
 
 Operands rotate through copies that together exceed the L2 cache, so every
 timed launch reads its weights or its cache from HBM.  `--iters` launches are
@@ -62,8 +64,14 @@ def bench_gemm(args):
     a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     out_dtype = torch.float32 if args.out == "float32" else torch.bfloat16
 
+    if args.residual:                                        # EPI_RESIDUAL: stream += product, norm weight, sums of squares
+        x = torch.randn(M, N, device="cuda")
+        nw = torch.ones(N, device="cuda", dtype=torch.bfloat16)
+
     def run(i):
-        if args.swiglu:
+        if args.residual:
+            ops.linear_residual_norm(ops.PendingLinear(a, ws[i]), x, nw, 1e-5)
+        elif args.swiglu:
             ops.linear_swiglu(a, ws[i])
         else:
             ops.linear(a, ws[i], out_dtype)
@@ -125,9 +133,29 @@ def bench_attention_prefill(args):
             "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 2)}
 
 
+def bench_sample(args):
+    from . import ops
+    B, V = args.batch, args.vocab
+    copies = max(2, math.ceil(2 * L2_BYTES / (B * V * 4)))
+    copies = min(copies, 64)
+    logits = [torch.randn(B, V, device="cuda") * 3 for _ in range(copies)]
+    rng = torch.arange(1, B + 1, dtype=torch.int64, device="cuda") * 7919
+
+    def run(i):
+        if args.temperature <= 0:
+            ops.argmax(logits[i])
+        else:
+            ops.sample(logits[i], rng, args.temperature, args.top_k, args.top_p, args.min_p)
+
+    sec = _time(run, len(logits), 1 if args.once else args.iters, 0 if args.once else args.warmup)
+    return {"kernel": "argmax" if args.temperature <= 0 else "sample", "batch": B, "vocab": V,
+            "temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p, "min_p": args.min_p,
+            "us": round(sec * 1e6, 2), "GB/s": round(B * V * 4 / sec / 1e9, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m picolm_b200.bench_kernels", description=__doc__.split("\n\n")[0])
-    ap.add_argument("kernel", choices=["gemm", "attention_decode", "attention_prefill"])
+    ap.add_argument("kernel", choices=["gemm", "attention_decode", "attention_prefill", "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -142,6 +170,13 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--swiglu", action="store_true", help="gemm: the product with the SwiGLU epilogue (n counts gate and up rows)")
+    ap.add_argument("--residual", action="store_true",
+                    help="gemm (m <= 64): the product in front of an RMSNorm (adds to the stream, norm weight, sums of squares)")
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--temperature", type=float, default=0.8, help="sample: 0 times the argmax kernel")
+    ap.add_argument("--top-k", type=int, default=40)
+    ap.add_argument("--top-p", type=float, default=0.9)
+    ap.add_argument("--min-p", type=float, default=0.05)
     ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
     ap.add_argument("--copies", type=int, default=0,
                     help="gemm: weight copies to rotate through (default: enough to exceed L2; 1 keeps them in L2)")
@@ -153,7 +188,7 @@ def main(argv=None):
     global USE_GRAPH
     USE_GRAPH = args.graph and not args.once
     fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
-          "attention_prefill": bench_attention_prefill}[args.kernel]
+          "attention_prefill": bench_attention_prefill, "sample": bench_sample}[args.kernel]
     print(json.dumps(fn(args)))
     return 0
 
