@@ -183,7 +183,10 @@ def main():
     with tempfile.TemporaryDirectory() as tmp:
         t0 = time.time()
         write_random_model(cfg, seed, tmp, norm_std=0.0)
-        engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * context, max_seqs=max_b,
+        # the cache holds what the largest run needs (its prompts, warm-up and timed steps), not
+        # max_b full contexts: at the 13B shape those would not fit the GPU
+        per_seq = min(context, (max(prompt_len, prefill_tokens) + 2 * args.warmup + 2 * args.steps + 16 + 63) // 64 * 64)
+        engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * per_seq, max_seqs=max_b,
                                     max_seq_tokens=context, use_graphs=False if args.no_graphs else None)
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr)
     g = torch.Generator().manual_seed(seed)
