@@ -86,12 +86,13 @@ def find_nvcc() -> str:
 def _writable_dir(path: str) -> bool:
     try:
         os.makedirs(path, exist_ok=True)
-        probe = os.path.join(path, f".probe-{os.getpid()}")
+        probe = os.path.join(path, f"probe-{os.getpid()}.tmp")
         with open(probe, "w"):
             pass
         os.remove(probe)
         return True
-    except OSError:
+    except OSError as e:
+        print(f"[picolm_b200] {path} cannot be written ({e}); trying the next folder", file=sys.stderr, flush=True)
         return False
 
 
