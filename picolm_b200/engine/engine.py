@@ -45,9 +45,9 @@ class Engine:
                                    max_seq_tokens=longest)
         model.prepare(self.cache.max_seq_tokens)
         self.vocab_size = spec.vocab_size
-        # Decode steps replay a CUDA graph when every mixer says that its forward only launches
-        # work that depends on the step through device buffers (`graph_safe`).
-        safe = all(getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        # Decode steps replay a CUDA graph when every part of every block says that its forward only
+        # launches work that depends on the step through device buffers (`graph_safe`).
+        safe = all(getattr(part, "graph_safe", False) for b in model.blocks for _, part in b.parts())
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
         self._tokens = torch.zeros(256, dtype=torch.int32, device=self.runtime.device)

@@ -49,6 +49,11 @@ class Part:
 
     family: str = ""
     kind: str = ""
+    # True says: forward() only launches work whose dependence on the step goes through device buffers
+    # (no host read of a device value, no shape that depends on the tokens), so that a decode step
+    # through this part may be captured in a CUDA graph.  The engine uses graphs only if every part of
+    # every block says so.
+    graph_safe: bool = False
 
     def __init__(self, params: Mapping[str, Any], runtime: Optional[Runtime]):
         self.params = dict(params)

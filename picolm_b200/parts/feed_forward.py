@@ -48,6 +48,7 @@ class GatedMLP(Part):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     takes_scaled_rows = True          # h goes into a product and nowhere else
+    graph_safe = True
 
     def forward(self, h, step):
         if self.fused:

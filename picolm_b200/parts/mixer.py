@@ -36,9 +36,11 @@ class Attention(Part):
     1/sqrt(head_dim)), window (None: all keys), position (a PartSpec of the
     position family), q_name/k_name/v_name/o_name (relative tensor names)."""
 
-    # forward() launches kernels whose dependence on the step goes through device buffers only
-    # (apart from sizes fixed per batch size), so a decode step may be captured in a CUDA graph
-    graph_safe = True
+    @property
+    def graph_safe(self) -> bool:
+        """forward() launches kernels whose dependence on the step goes through device buffers only (apart
+        from sizes fixed per batch size); the position encoding has to say the same of itself."""
+        return bool(getattr(self.position, "graph_safe", False))
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)

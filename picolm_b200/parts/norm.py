@@ -27,6 +27,7 @@ class RMSNorm(Part):
         return self.weight.numel() * self.weight.element_size()
 
     can_defer_scale = True
+    graph_safe = True
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, defer_scale: bool = False):
         """Normalise `x + pending`.  Without `rows` the sum is written back to the

@@ -56,6 +56,8 @@ class RotaryEncoding(Part):
     """params: head_dim, rotary_dim, theta, scaling (dict or None), pairing
     ("half" or "adjacent"), max_positions."""
 
+    graph_safe = True
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         if self.params["pairing"] not in ("half", "adjacent"):
@@ -91,6 +93,8 @@ class RotaryEncoding(Part):
 @register_part("position", "none")
 class NoPositionEncoding(Part):
     """Queries and keys go through unrotated."""
+
+    graph_safe = True
 
     def prepare(self, n_positions: int) -> None:
         pass
