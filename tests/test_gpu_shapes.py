@@ -21,6 +21,7 @@ SHAPES = {
     "hd256":         (1, 128, 2,  1, 256, 256, 128, 10000.0, 1e-5, True),
     "mqa_20_heads":  (1, 320, 20, 1,  16, 320, 264, 10000.0, 1e-5, False),      # 20 query heads on one KV head
     "odd_widths":    (2, 72,  3,  3,  24, 100, 97,  10000.0, 1e-5, False),      # F = 100: not a multiple of 8
+    "hd40":          (1, 80,  2,  1,  40, 160, 130, 10000.0, 1e-5, False),      # no multiple of 16: CUDA-core attention
 }
 
 
@@ -54,3 +55,17 @@ def test_shape_in_every_cut(tmp_path, name, dtype):
     if dtype == "bfloat16":
         from picolm_b200 import ops
         ops.check_status()
+
+
+def test_head_size_beyond_the_kernels_is_refused(tmp_path):
+    """A head of 272 is more than any attention kernel takes: a clear error at the first step, no result."""
+    from picolm_b200.engine import Engine
+    from picolm_b200.ops import KernelError
+    cfg_dict = _config((1, 64, 1, 1, 272, 64, 50, 10000.0, 1e-5, False))
+    d = make_model_dir(str(tmp_path / "hd272"), cfg_dict, 3)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(d, dtype=dtype, max_tokens=128, max_seqs=1)
+        s = eng.new_sequence()
+        with pytest.raises(KernelError, match="head_dim 272 exceeds 256"):
+            eng.step([(s, [1, 2, 3])])
+        eng.end_sequence(s)
