@@ -290,12 +290,44 @@ constexpr int DC_MAX_CLUSTER = 8;                                               
 // partial result in its own shared memory and the cluster merges them through distributed shared
 // memory, in split order.  Without it (more splits than a cluster holds) ws_o [tokens*H, splits, HD]
 // and ws_ml [tokens*H, splits, 2] receive the partial results for attn_merge_kernel.
-template <bool CLUSTER>
+//
+// With ROPE the kernel does the rotary encoding and the cache write of the step itself
+// (picolm/tensor.c:3216-3304 and picolm/model_core.c:1943-1955 folded in): q is then the output of
+// the QKV projection, [tokens, (H + 2G) * HD], the whole head is rotated with half-split pairs by the
+// tables rot.cos / rot.sin [positions, HD/2], and the CTAs whose range holds the sequence's last page
+// put the step's rotated key and its value into their copy of that page; those of the first row
+// group also write them to the cache.  No other kernel of the step then writes this cache, so every
+// page may be requested before the kernel in front has finished.
+struct Rotary {
+    const float* cos;
+    const float* sin;
+    bf16* kc_w;          // the cache, writable
+    bf16* vc_w;
+};
+
+// x[j..j+8) and x[HD/2+j..HD/2+j+8) of one head, rotated by the angles of `pos` (fp32, rounded once)
+__device__ __forceinline__ void rotate16(uint4& lo, uint4& hi, const float* __restrict__ cos_t,
+                                         const float* __restrict__ sin_t, int pos, int j) {
+    const float* cp = cos_t + (size_t)pos * (HD / 2) + j;
+    const float* sp = sin_t + (size_t)pos * (HD / 2) + j;
+    __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float a0 = __low2float(l2[k]), a1 = __high2float(l2[k]);
+        const float b0 = __low2float(h2[k]), b1 = __high2float(h2[k]);
+        const float c0 = cp[2 * k], c1 = cp[2 * k + 1], s0 = sp[2 * k], s1 = sp[2 * k + 1];
+        l2[k] = __floats2bfloat162_rn(rope_first(a0, b0, c0, s0), rope_first(a1, b1, c1, s1));
+        h2[k] = __floats2bfloat162_rn(rope_second(a0, b0, c0, s0), rope_second(a1, b1, c1, s1));
+    }
+}
+
+template <bool CLUSTER, bool ROPE>
 __global__ void __launch_bounds__(NT)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table,
-                   int max_pages, int H, int G, float scale_log2, int window, int row_groups) {
+                   int max_pages, int H, int G, float scale_log2, int window, int row_groups, const Rotary rot) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw + DC_Q_BYTES);
@@ -330,7 +362,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
         load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
     };
     const int n_first = min(n_pages, DC_STAGES - 1);                    // pages asked for before the loop
-    const bool early = n_first <= 0 || p_begin + n_first - 1 < page_last;  // none of them is written in this step
+    const bool early = ROPE || n_first <= 0 || p_begin + n_first - 1 < page_last;  // none of them is written in this step
     if (!early) pdl_wait();
 #pragma unroll
     for (int i = 0; i < DC_STAGES - 1; ++i) {
@@ -345,13 +377,28 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
         }
         return;
     }
-    if (n_pages > 0) {                                  // (in a cluster an empty split still meets the others)
+    if (n_pages > 0 && !ROPE) {                         // (in a cluster an empty split still meets the others)
         constexpr int CPR = HD / 8;                     // the queries: plain loads, visible after the loop's first barrier
         for (int c = threadIdx.x; c < 16 * CPR; c += NT) {
             const int r = c / CPR, col = c - r * CPR;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * H + h0 + r) * HD + col * 8);
             *reinterpret_cast<uint4*>(q_s + r * LDS + col * 8) = v;
+        }
+    }
+    const bf16* qkv_row = q + (size_t)t * (H + 2 * G) * HD;              // ROPE: this token's projections
+    if (n_pages > 0 && ROPE) {
+        constexpr int GRP = HD / 16;                    // groups of 8 pairs per head
+        for (int c = threadIdx.x; c < 16 * GRP; c += NT) {
+            const int r = c / GRP, j = (c - r * GRP) * 8;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (r < n_rows) {
+                lo = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(h0 + r) * HD + j);
+                hi = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(h0 + r) * HD + HD / 2 + j);
+                rotate16(lo, hi, rot.cos, rot.sin, pos, j);
+            }
+            *reinterpret_cast<uint4*>(q_s + r * LDS + j) = lo;
+            *reinterpret_cast<uint4*>(q_s + r * LDS + HD / 2 + j) = hi;
         }
     }
     float o[HD / 8][4];
@@ -366,6 +413,34 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
         __syncthreads();
         const bf16* kt = k_s + (i % DC_STAGES) * TILE_ELEMS;
         const bf16* vt = v_s + (i % DC_STAGES) * TILE_ELEMS;
+        if (ROPE && p_begin + i == page_last) {
+            // the step's own key (rotated) and value: into this CTA's copy of the page, and from the
+            // first row group into the cache as well
+            constexpr int GRP = HD / 16;
+            const int in_page = pos - page_last * PLM_PAGE;
+            bf16* k_row = k_s + (i % DC_STAGES) * TILE_ELEMS + in_page * LDS;
+            bf16* v_row = v_s + (i % DC_STAGES) * TILE_ELEMS + in_page * LDS;
+            const size_t cache_row = (((size_t)pages[page_last] * G + g) * PLM_PAGE + in_page) * HD;
+            const bool to_cache = rg == 0 && pages[page_last] > 0;       // page 0 is the null page of padding rows
+            if (threadIdx.x < GRP) {
+                const int j = threadIdx.x * 8;
+                uint4 lo = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + g) * HD + j);
+                uint4 hi = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + g) * HD + HD / 2 + j);
+                rotate16(lo, hi, rot.cos, rot.sin, pos, j);
+                *reinterpret_cast<uint4*>(k_row + j) = lo;
+                *reinterpret_cast<uint4*>(k_row + HD / 2 + j) = hi;
+                if (to_cache) {
+                    *reinterpret_cast<uint4*>(rot.kc_w + cache_row + j) = lo;
+                    *reinterpret_cast<uint4*>(rot.kc_w + cache_row + HD / 2 + j) = hi;
+                }
+            } else if (threadIdx.x >= 32 && threadIdx.x < 32 + HD / 8) {
+                const int j = (threadIdx.x - 32) * 8;
+                const uint4 v = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + G + g) * HD + j);
+                *reinterpret_cast<uint4*>(v_row + j) = v;
+                if (to_cache) *reinterpret_cast<uint4*>(rot.vc_w + cache_row + j) = v;
+            }
+            __syncthreads();
+        }
         const int key_base = (p_begin + i) * PLM_PAGE + warp * 16;       // this warp's 16 keys of the page
         if (key_base <= pos) {
             float s[2][4];
@@ -535,8 +610,8 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
     if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535) return PLM_ERR_SHAPE;
     static bool configured = false;
     if (!configured) {
-        int rc = set_smem(attn_decode_kernel<false>, DC_SMEM);
-        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true>, DC_SMEM);
+        int rc = set_smem(attn_decode_kernel<false, false>, DC_SMEM);
+        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, false>, DC_SMEM);
         if (rc != PLM_OK) return rc;
         configured = true;
     }
@@ -545,16 +620,53 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
     dim3 grid(n_splits, G * row_groups, n_tokens);
     if (n_splits > 1 && !workspace) {                       // the splits merge inside their cluster
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
-        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
                                                 stream, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q,
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}));
+    if (rc != PLM_OK || n_splits == 1) return rc;
+    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
+                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
+}
+
+// Decode with the rotary encoding and the cache write folded in (see struct Rotary): qkv [T, (H + 2G) * HD]
+// is the QKV projection's output, cos_t / sin_t [positions, HD/2] fp32; the step's keys and values are
+// written to kc / vc at tok_pos.  Otherwise as plm_attn_decode.
+extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* out, float* workspace,
+                                    const float* cos_t, const float* sin_t, const int* tok_pos, const int* tok_seq,
+                                    const int* block_table, int max_pages, int n_tokens, int H, int G, float scale,
+                                    int window, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535 || !cos_t || !sin_t) return PLM_ERR_SHAPE;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(attn_decode_kernel<false, true>, DC_SMEM);
+        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, true>, DC_SMEM);
+        if (rc != PLM_OK) return rc;
+        configured = true;
+    }
+    const int R = H / G, row_groups = (R + 15) / 16;
+    if (G * row_groups > 65535) return PLM_ERR_SHAPE;
+    const Rotary rot = {cos_t, sin_t, (bf16*)kc, (bf16*)vc};
+    dim3 grid(n_splits, G * row_groups, n_tokens);
+    if (n_splits > 1 && !workspace) {
+        if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
+                                                stream, (const bf16*)qkv, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
+                                                (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot));
+    }
+    float* ws_o = workspace;
+    float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)qkv,
+                                      (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));

@@ -59,6 +59,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// One rotary pair (picolm/tensor.c:3216-3304: x0' = x0 c - x1 s, x1' = x0 s + x1 c) with the roundings spelt
+// out (each product rounded, then the sum: what a plain implementation does), so that every kernel that
+// rotates gives the same bits whatever the compiler would fuse.
+__device__ __forceinline__ float rope_first(float a, float b, float c, float s) { return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)); }
+__device__ __forceinline__ float rope_second(float a, float b, float c, float s) { return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)); }
+
 // Programmatic dependent launch.  A kernel launched through launch_pdl may begin while the kernel
 // before it on the stream is still running; pdl_wait() blocks until that kernel (and with it every
 // earlier one) has finished and its writes are visible.  So: before pdl_wait() a kernel may only

@@ -264,7 +264,7 @@ __global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q
         if (head < H) {
             if (rotate) {
                 const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
-                const float ra = a * c - b * s, rb = a * s + b * c;
+                const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
                 a = ra; b = rb;
             }
             Ta* o = q_out + ((size_t)t * H + head) * hd;
@@ -274,7 +274,7 @@ __global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q
             if (!store || !have_page) continue;
             if (rotate) {
                 const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
-                const float ra = a * c - b * s, rb = a * s + b * c;
+                const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
                 a = ra; b = rb;
             }
             const int g = head - H;
@@ -338,8 +338,8 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
             for (int k = 0; k < 4; ++k) {
                 const float a0 = __low2float(l2[k]), a1 = __high2float(l2[k]);
                 const float b0 = __low2float(h2[k]), b1 = __high2float(h2[k]);
-                l2[k] = __floats2bfloat162_rn(a0 * c[2 * k] - b0 * sn[2 * k], a1 * c[2 * k + 1] - b1 * sn[2 * k + 1]);
-                h2[k] = __floats2bfloat162_rn(a0 * sn[2 * k] + b0 * c[2 * k], a1 * sn[2 * k + 1] + b1 * c[2 * k + 1]);
+                l2[k] = __floats2bfloat162_rn(rope_first(a0, b0, c[2 * k], sn[2 * k]), rope_first(a1, b1, c[2 * k + 1], sn[2 * k + 1]));
+                h2[k] = __floats2bfloat162_rn(rope_second(a0, b0, c[2 * k], sn[2 * k]), rope_second(a1, b1, c[2 * k + 1], sn[2 * k + 1]));
             }
         }
         *reinterpret_cast<uint4*>(dst + j) = lo;

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
 }
@@ -581,6 +582,53 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
         "attention_decode", kernels=2 if scratch else 1)
+    return out
+
+
+class Rotation:
+    """A rotary encoding as the kernels take it: cos / sin tables [positions, rotary_dim / 2] in float32,
+    how many leading components of a head are rotated, and how they pair up ("half" or "adjacent")."""
+    __slots__ = ("cos", "sin", "rotary_dim", "pairing")
+
+    def __init__(self, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int, pairing: str):
+        self.cos, self.sin, self.rotary_dim, self.pairing = cos, sin, rotary_dim, pairing
+
+
+def attention_decode_rope_supported(qkv: torch.Tensor, kv, rotation: Optional[Rotation], head_dim: int) -> bool:
+    """Whether the decode kernel can do this rotation and the cache write itself: bfloat16, a head size it
+    takes, the whole head rotated in half-split pairs, a cache that this layer writes."""
+    return (rotation is not None and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and rotation.rotary_dim == head_dim and rotation.pairing == "half" and kv.writable
+            and kv.k.dtype == torch.bfloat16 and rotation.cos is not None)
+
+
+def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_heads: int, head_dim: int,
+                          scale: float, rotation: Rotation, scratch: Optional[bool] = None) -> torch.Tensor:
+    """A decode step's attention with the rotary encoding and the cache write folded in: `qkv`
+    [T, (H + 2G) * hd] is the output of the QKV projection; queries and the new keys are rotated inside
+    the kernel, the new keys and values are written to the cache at the tokens' positions, and the
+    queries attend to everything up to and including them.  Returns [T, H * hd]."""
+    _dev(qkv, "qkv"), _dev(kv.k, "k_cache"), _dev(kv.v, "v_cache")
+    T = qkv.shape[0]
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    if not attention_decode_rope_supported(qkv, kv, rotation, hd):
+        raise KernelError("attention_decode_rope: not a case the fused kernel takes")
+    if qkv.shape[1] != (H + 2 * G) * hd or kv.k.shape[1:] != (G, PAGE_TOKENS, hd) or kv.v.shape != kv.k.shape:
+        raise KernelError("attention_decode_rope: qkv or the cache does not have the shape the heads imply")
+    if step.max_position >= rotation.cos.shape[0]:
+        raise KernelError(f"position {step.max_position} lies beyond the rotary table")
+    n_splits = decode_splits(T, H, G, step.max_position + 1)
+    ctas = T * G * ((H // G + 15) // 16) * n_splits
+    if scratch is None:
+        scratch = ctas > 3 * _SM_COUNT
+    scratch = n_splits > 1 and (scratch or n_splits > DECODE_CLUSTER_SPLITS)
+    out = torch.empty((T, H * hd), dtype=qkv.dtype, device=qkv.device)
+    ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=qkv.device) if scratch else None
+    lib, flags = attention_variant(hd)
+    _check(_fn(lib, "plm_attn_decode_rope", flags)(
+        _p(qkv), _p(kv.k), _p(kv.v), _p(out), _p(ws), _p(rotation.cos), _p(rotation.sin), _p(step.tok_pos),
+        _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, float(scale), int(kv.window or 0),
+        int(n_splits), _stream()), "attention_decode_rope", kernels=2 if scratch else 1)
     return out
 
 

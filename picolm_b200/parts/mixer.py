@@ -82,7 +82,13 @@ class Attention(Part):
     def forward(self, h, step, cache):
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, dt)
-        q = torch.empty((h.shape[0], self.H, self.hd), dtype=dt, device=h.device)
-        self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
-        ctx = ops.attention(q, cache, step, self.G, self.scale)
+        # a position encoding that can describe itself as a rotation (`rotation()`) may be applied, and the
+        # cache written, by the decode attention kernel itself
+        rotation = self.position.rotation() if step.is_decode and hasattr(self.position, "rotation") else None
+        if rotation is not None and ops.attention_decode_rope_supported(qkv, cache, rotation, self.hd):
+            ctx = ops.attention_decode_rope(qkv, cache, step, self.H, self.G, self.hd, self.scale, rotation)
+        else:
+            q = torch.empty((h.shape[0], self.H, self.hd), dtype=dt, device=h.device)
+            self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
+            ctx = ops.attention(q, cache, step, self.G, self.scale)
         return ops.linear(ctx, self.w_o, torch.float32, defer=True)

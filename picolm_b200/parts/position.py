@@ -80,6 +80,10 @@ class RotaryEncoding(Part):
         self.cos = ang.cos().to(torch.float32).to(self.runtime.device).contiguous()
         self.sin = ang.sin().to(torch.float32).to(self.runtime.device).contiguous()
 
+    def rotation(self):
+        """The encoding as data (`ops.Rotation`), for a kernel that applies it itself."""
+        return ops.Rotation(self.cos, self.sin, self.params["rotary_dim"], self.params["pairing"])
+
     def apply(self, qkv, q_out, kv, step, num_heads, num_kv_heads, head_dim) -> None:
         if self.cos is None or step.max_position >= self.cos.shape[0]:
             raise RuntimeError(

@@ -293,6 +293,48 @@ def test_sample_distribution():
     assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
 
 
+@pytest.mark.parametrize("scratch", [False, True])
+@pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (40, 2, 16), (6, 3, 128), (4, 4, 48)])
+def test_attention_decode_with_the_rotation_folded_in(H, G, hd, scratch):
+    """The decode kernel that rotates queries and the new keys and writes the cache itself, against the
+    two kernels it replaces (RoPE + cache write, then attention): the same output bit for bit, the same
+    cache.  Positions at the first and the last place of a page, a sequence of one token, 20 query heads
+    on a KV head (two row groups: one of them writes the cache)."""
+    from types import SimpleNamespace
+    from picolm_b200 import ops
+    torch.manual_seed(H + hd)
+    lens = [129, 1, 64, 700, 65, 320]                    # lengths after the step: the new token sits at len - 1
+    B = len(lens)
+    ks = [torch.randn(n, G, hd) * 0.5 for n in lens]
+    vs = [torch.randn(n, G, hd) for n in lens]
+    kc, vc, table = _paged(ks, vs, lens, 40, torch.bfloat16, 5)
+    qkv = (torch.randn(B, (H + 2 * G) * hd) * 0.7).to(torch.bfloat16).to(DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    ang = torch.arange(1024, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    step = SimpleNamespace(tok_pos=pos, tok_seq=seq, max_position=max(lens) - 1)
+    # the two kernels
+    k1, v1 = kc.clone().to(DEV), vc.clone().to(DEV)
+    q = torch.empty((B, H, hd), dtype=torch.bfloat16, device=DEV)
+    ops.rope_store(qkv, q, k1, v1, cos, sin, pos, seq, table.to(DEV), H, G, hd, hd, "half")
+    n_splits = ops.decode_splits(B, H, G, max(lens))
+    want = ops.attention_decode(q, k1, v1, pos, seq, table.to(DEV), G, scale, n_splits, scratch=scratch)
+    # the one kernel
+    k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
+    kv = SimpleNamespace(k=k2, v=v2, block_table=table.to(DEV), window=None, writable=True)
+    rot = ops.Rotation(cos, sin, hd, "half")
+    assert ops.attention_decode_rope_supported(qkv, kv, rot, hd)
+    got = ops.attention_decode_rope(qkv, kv, step, H, G, hd, scale, rot, scratch=scratch)
+    assert torch.isfinite(got).all()
+    assert torch.equal(got, want)
+    # the cache: the same values wherever the first way wrote some (unused places hold NaN in both)
+    assert torch.equal(torch.nan_to_num(k2.float(), nan=7.0), torch.nan_to_num(k1.float(), nan=7.0))
+    assert torch.equal(torch.nan_to_num(v2.float(), nan=7.0), torch.nan_to_num(v1.float(), nan=7.0))
+
+
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("T,F,K,N2", [(1, 128, 64, 256), (8, 2048, 512, 3072), (17, 200, 264, 384), (33, 136, 1024, 128),
                                        (64, 328, 192, 640)])
