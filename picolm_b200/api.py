@@ -43,11 +43,11 @@ def model_free(engine: Engine) -> None:
 def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.8,
              top_p: float = 0.9, top_k: int = 40, min_p: float = 0.05, seed: int = 42,
              stop_ids: Optional[Sequence[int]] = None, max_batch: Optional[int] = None,
-             return_stats: bool = False, steps_per_sync: int = 8):
+             return_stats: bool = False, steps_per_sync: int = 3):
     """Generate for every prompt (a list of token ids); returns the new tokens
     of each.  `temperature` 0 is greedy.  Prompts are batched as the cache
-    allows, batches run one after another.  `steps_per_sync`: after how many decode
-    steps at the latest the host looks at the new tokens (1: after every step)."""
+    allows, batches run one after another.  `steps_per_sync`: how many decode steps may
+    be in flight before the host looks at the first one's tokens (1: it waits for every step)."""
     params = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p, seed=seed)
     outputs, stats = _generate(engine, prompts, max_tokens=max_tokens, sampling=params, stop_ids=stop_ids,
                                max_batch=max_batch, steps_per_sync=steps_per_sync)

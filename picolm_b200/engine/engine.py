@@ -67,6 +67,24 @@ class Engine:
         self.counters["d2h_bytes"] += tokens.numel() * tokens.element_size()
         return tokens.tolist()
 
+    def pinned_tokens(self, rows: int, cols: int) -> torch.Tensor:
+        """A [rows, cols] int32 view of pinned host memory for `fetch_later` (allocated once and kept:
+        pinning memory is slow)."""
+        need = rows * cols
+        buf = getattr(self, "_pinned", None)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need, 64 * 64), dtype=torch.int32)
+            if self.runtime.device.type == "cuda":
+                buf = buf.pin_memory()
+            self._pinned = buf
+        return buf[:need].view(rows, cols)
+
+    def mark(self) -> torch.cuda.Event:
+        """An event after everything launched so far on the current stream."""
+        e = torch.cuda.Event()
+        e.record()
+        return e
+
     def fetch_later(self, tokens: torch.Tensor, pinned_row: torch.Tensor) -> None:
         """Start copying sampled token ids into a row of pinned host memory without waiting for them;
         `synchronize()` (or an event) says when they are there."""

@@ -84,77 +84,81 @@ def finish_reason(token: int, n_generated: int, max_new: int, stop_ids, length_a
     return None
 
 
-def steps_ahead(most: int, generated: Sequence[int], max_new: Sequence[int], lengths: Sequence[int],
-                max_seq_tokens: int) -> int:
-    """How many steps a batch may run before the host has to look at it for another reason than a stop
-    token: until the first of its sequences produces its last allowed token or fills the context.
-    `generated[i]` new tokens exist of sequence i (the last one not fed yet), `lengths[i]` tokens of it
-    are in the cache; every sequence is one that goes on (`finish_reason` said None)."""
-    k = most
-    for n, limit, length in zip(generated, max_new, lengths):
-        k = min(k, limit - n, max_seq_tokens - length)
-    return max(k, 1)
-
-
 def _to_host(engine, tokens):
     fetch = getattr(engine, "to_host", None)
     return fetch(tokens) if fetch is not None else tokens.tolist()
 
 
-def _decode_in_stretches(engine, sampler, batch, slots, live, first_tokens, stop, on_token, stats, most) -> None:
-    """The decode loop of one batch with the host looking in every `most` steps at the latest (see
-    `generate`).  `first_tokens`: what the prompts' step sampled, on the host."""
+def _decode_ahead(engine, sampler, batch, slots, live, first_tokens, stop, on_token, stats, depth) -> None:
+    """The decode loop of one batch with up to `depth` steps in flight: a step's sampled ids feed the next
+    step on the device, the host looks at them `depth - 1` steps late (see `generate`).  `live`: indices
+    into `batch` of the sequences that run; `first_tokens`: what the prompts' step sampled, on the host."""
+    import collections
     import torch
     cache = engine.cache
     device = engine.runtime.device
-    pinned = torch.empty((most, len(live)), dtype=torch.int32)
-    if torch.device(device).type == "cuda":
-        pinned = pinned.pin_memory()
     buffer = getattr(engine, "token_buffer", None)       # where the engine's captured steps read their ids
-    rows = [[int(t) for t in first_tokens]]              # stretches of token rows still to be judged
-    base = [engine.length(slots[i]) for i in live]       # cache length when rows[0] was sampled
-    tok_dev = None
+    mark = getattr(engine, "mark", None)                 # an event after what was launched so far
+    n0 = len(live)
+    pinned = engine.pinned_tokens(depth + 1, n0) if hasattr(engine, "pinned_tokens") else \
+        torch.empty((depth + 1, n0), dtype=torch.int32)
+
+    def judge(members, tokens, lengths_after_feed):
+        """Append a step's tokens to the sequences that are still undecided; returns those that go on."""
+        for i, tok, length in zip(members, tokens, lengths_after_feed):
+            r = batch[i]
+            if r.finish_reason is not None:              # ended by an earlier token: this one is surplus
+                continue
+            r.output.append(tok)
+            stats.generated_tokens += 1
+            if on_token is not None:
+                on_token(r.index, tok)
+            r.finish_reason = finish_reason(tok, len(r.output), r.max_new, stop, length, cache.max_seq_tokens)
+
+    judge(live, [int(t) for t in first_tokens], [engine.length(slots[i]) + 1 for i in live])
+    # what the host knows to be launched: per sequence the number of tokens sampled or being sampled
+    launched = {i: len(batch[i].output) for i in live}
+    cur = [i for i in live if batch[i].finish_reason is None]       # the sequences of the next step
+    rows_of = list(live)                                             # whose ids the rows of tok_dev hold
+    tok_dev = torch.tensor([int(t) for t in first_tokens], dtype=torch.int32, device=device)
+    inflight = collections.deque()
+    step_no = 0
     while True:
-        still = list(range(len(live)))
-        for j, row_tokens in enumerate(rows):
-            nxt = []
-            for row in still:
-                r, tok = batch[live[row]], row_tokens[row]
-                r.output.append(tok)
-                stats.generated_tokens += 1
-                if on_token is not None:
-                    on_token(r.index, tok)
-                r.finish_reason = finish_reason(tok, len(r.output), r.max_new, stop, base[row] + j + 1,
-                                                cache.max_seq_tokens)
-                if r.finish_reason is None:
-                    nxt.append(row)
-            still = nxt
-        if not still:
-            return
-        last = rows[-1]
-        if len(still) != len(live) or tok_dev is None:
-            sampler.keep(still)
-            tok_dev = torch.tensor([last[row] for row in still], dtype=torch.int32, device=device)
-            live = [live[row] for row in still]
-        cur = [slots[i] for i in live]
-        base = [engine.length(s) for s in cur]
-        k = steps_ahead(most, [len(batch[i].output) for i in live], [batch[i].max_new for i in live], base,
-                        cache.max_seq_tokens)
-        for j in range(k):
-            logits = engine.step_device_tokens(cur, tok_dev)
+        while len(inflight) < depth:
+            # a sequence runs another step unless a token ended it or its limits are reached by what is
+            # already launched (those are known without looking at any token)
+            cur = [i for i in cur if batch[i].finish_reason is None and launched[i] < batch[i].max_new
+                   and engine.length(slots[i]) < cache.max_seq_tokens]
+            if not cur:
+                break
+            if cur != rows_of:                           # some left: keep the others' rows, on the device
+                keep = [rows_of.index(i) for i in cur]
+                sampler.keep(keep)
+                tok_dev = tok_dev[torch.tensor(keep, dtype=torch.int64, device=device)].contiguous()
+                rows_of = list(cur)
+            cur_slots = [slots[i] for i in cur]
+            logits = engine.step_device_tokens(cur_slots, tok_dev)
             tok_dev = sampler.sample(logits, out=buffer(len(cur))) if buffer else sampler.sample(logits)
-            engine.fetch_later(tok_dev, pinned[j, :len(live)])
+            row = pinned[step_no % (depth + 1), :len(cur)]
+            engine.fetch_later(tok_dev, row)
+            inflight.append((list(cur), row, [engine.length(s) + 1 for s in cur_slots], mark() if mark else None))
+            for i in cur:
+                launched[i] += 1
             stats.steps += 1
-        engine.synchronize()
-        rows = pinned[:k, :len(live)].tolist()
-        base = [b + 1 for b in base]                     # rows[j] was sampled with base + j + 1 tokens cached
+            step_no += 1
+        if not inflight:
+            return
+        members, row, lengths, event = inflight.popleft()
+        if event is not None:
+            event.synchronize()
+        judge(members, row.tolist(), lengths)
 
 
 def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_ids: Optional[Sequence[int]] = None,
              max_batch: Optional[int] = None,
              on_token: Optional[Callable[[int, int], None]] = None,
-             sampler_factory=None, steps_per_sync: int = 8) -> Tuple[List[List[int]], GenerationStats]:
+             sampler_factory=None, steps_per_sync: int = 3) -> Tuple[List[List[int]], GenerationStats]:
     """Generate up to `max_tokens` new tokens for every prompt (lists of token
     ids).  Returns the new tokens of each prompt, in the prompts' order, and
     timing counters.  `stop_ids` defaults to the model's own end-of-sequence ids;
@@ -162,11 +166,12 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
     `sampler_factory(params, request indices, device)` replaces the device
     sampler (tests of the loop's decisions use it).
 
-    With `steps_per_sync` > 1 (and an engine that can take a step's tokens from the device) the host
-    looks at the new tokens only every so many steps: the sampled ids feed the next step on the device
-    and reach the host by copies that nobody waits for, so the host prepares and launches steps while
-    earlier ones run.  A sequence that meets a stop token in between runs on to the end of that
-    stretch; its surplus tokens are dropped, so the output is the same."""
+    With `steps_per_sync` > 1 (and an engine that can take a step's tokens from the device) that many
+    decode steps may be in flight: the sampled ids feed the next step on the device and reach the host
+    by copies that nobody waits for, and the host looks at a step's ids only when later steps are
+    already launched, so the device never waits for it.  A sequence that meets a stop token runs on for
+    the steps already launched; its surplus tokens are dropped, so the output is the same.  Ends by
+    `max_tokens` or by the context are known in advance and cost nothing."""
     sampling = sampling or SamplingParams()
     stop = frozenset(engine.model.spec.stop_token_ids if stop_ids is None else stop_ids)
     cache = engine.cache
@@ -203,8 +208,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
             stats.steps += 1
             t0 = time.perf_counter()
             if steps_per_sync > 1 and hasattr(engine, "step_device_tokens"):
-                _decode_in_stretches(engine, sampler, batch, slots, live, tokens, stop, on_token, stats,
-                                     steps_per_sync)
+                _decode_ahead(engine, sampler, batch, slots, live, tokens, stop, on_token, stats, steps_per_sync)
                 stats.generation_seconds += time.perf_counter() - t0
                 continue
             while True:
