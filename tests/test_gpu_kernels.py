@@ -293,9 +293,10 @@ def test_sample_distribution():
     assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
 
 
+@pytest.mark.parametrize("window", [None, 90])
 @pytest.mark.parametrize("scratch", [False, True])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (40, 2, 16), (6, 3, 128), (4, 4, 48)])
-def test_attention_decode_with_the_rotation_folded_in(H, G, hd, scratch):
+def test_attention_decode_with_the_rotation_folded_in(H, G, hd, scratch, window):
     """The decode kernel that rotates queries and the new keys and writes the cache itself, against the
     two kernels it replaces (RoPE + cache write, then attention): the same output bit for bit, the same
     cache.  Positions at the first and the last place of a page, a sequence of one token, 20 query heads
@@ -321,10 +322,10 @@ def test_attention_decode_with_the_rotation_folded_in(H, G, hd, scratch):
     q = torch.empty((B, H, hd), dtype=torch.bfloat16, device=DEV)
     ops.rope_store(qkv, q, k1, v1, cos, sin, pos, seq, table.to(DEV), H, G, hd, hd, "half")
     n_splits = ops.decode_splits(B, H, G, max(lens))
-    want = ops.attention_decode(q, k1, v1, pos, seq, table.to(DEV), G, scale, n_splits, scratch=scratch)
+    want = ops.attention_decode(q, k1, v1, pos, seq, table.to(DEV), G, scale, n_splits, window=window, scratch=scratch)
     # the one kernel
     k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
-    kv = SimpleNamespace(k=k2, v=v2, block_table=table.to(DEV), window=None, writable=True)
+    kv = SimpleNamespace(k=k2, v=v2, block_table=table.to(DEV), window=window, writable=True)
     rot = ops.Rotation(cos, sin, hd, "half")
     assert ops.attention_decode_rope_supported(qkv, kv, rot, hd)
     got = ops.attention_decode_rope(qkv, kv, step, H, G, hd, scale, rot, scratch=scratch)
