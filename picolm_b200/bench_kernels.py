@@ -71,6 +71,8 @@ def bench_gemm(args):
     def run(i):
         if args.residual:
             ops.linear_residual_norm(ops.PendingLinear(a, ws[i]), x, nw, 1e-5)
+        elif args.pair:
+            ops.gemm_tc_wide(a, ws[i], out_dtype, swiglu=args.swiglu, pair=True)
         elif args.swiglu:
             ops.linear_swiglu(a, ws[i])
         else:
@@ -170,6 +172,7 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--swiglu", action="store_true", help="gemm: the product with the SwiGLU epilogue (n counts gate and up rows)")
+    ap.add_argument("--pair", action="store_true", help="gemm (m > 64): the kernel of CTA pairs (tcgen05.mma.cta_group::2)")
     ap.add_argument("--residual", action="store_true",
                     help="gemm (m <= 64): the product in front of an RMSNorm (adds to the stream, norm weight, sums of squares)")
     ap.add_argument("--vocab", type=int, default=128256)

@@ -89,7 +89,10 @@ def _writable_dir(path: str) -> bool:
         probe = os.path.join(path, f"probe-{os.getpid()}.tmp")
         with open(probe, "w"):
             pass
-        os.remove(probe)
+        try:
+            os.remove(probe)
+        except OSError:
+            pass                                             # it could be created: that is what counts
         return True
     except OSError as e:
         print(f"[picolm_b200] {path} cannot be written ({e}); trying the next folder", file=sys.stderr, flush=True)

@@ -15,6 +15,16 @@
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
 // epilogue.  Waits on mbarriers are bounded; a wait that runs out records where in `status`
 // and the CTA drains and leaves.
+//
+// PAIR: two CTAs of a cluster (two SMs) work on one tile of 256 tokens x 256 features with
+// tcgen05.mma.cta_group::2.  Each CTA loads its 128 token rows and HALF of the weight tile (128
+// features), the tensor cores of both SMs read both halves, and each CTA's tensor memory receives
+// its own 128 rows of the result.  A 128 x 256 tile is bound by what an SM has to bring in from L2
+// per MMA cycle (48 KB per K block of 64); the pair brings in 32 KB each for the same work.  The
+// CTA of rank 0 issues all MMAs: both CTAs' loads signal ITS "full" barriers (expect-tx set there),
+// its commits arrive at the "empty" and "accumulator full" barriers of both CTAs (commit with
+// multicast), and both CTAs' epilogues arrive at ITS "accumulator empty" barriers.  No TMA load
+// uses multicast.
 #include "tc_common.cuh"
 
 using namespace plm_tc;
@@ -30,14 +40,43 @@ __host__ __device__ constexpr size_t wide_smem(int bn) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// --- the forms for a pair of CTAs (cta_group::2); `bar` of the first three is a shared::cluster address
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {           // arrives at `bar` in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D fp32, A and B bf16, both K-major, M = 256 over the pair, N = n
+__host__ __device__ constexpr uint32_t instr_desc_bf16_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+__host__ __device__ constexpr int pair_stages() { return 6; }
+__host__ __device__ constexpr size_t pair_smem() { return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256; }
 
-template <int BN, int EPI, typename OutT>
+template <int BN, int EPI, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
                     int* __restrict__ status) {
-    constexpr int STAGES = stages_of(BN);
-    constexpr uint32_t X_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2;
+    static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
+    constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
+    constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
+    constexpr uint32_t X_BYTES = BM * BK * 2, W_BYTES = W_ROWS * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN;                               // two accumulators
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -52,21 +91,31 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (K + BK - 1) / BK;
-    const int n_tiles_total = m_tiles * n_tiles;
+    const int n_tiles_total = m_tiles * n_tiles;                         // PAIR: tiles of 256 tokens
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
+    const int first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x, tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, PAIR ? 256 : 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {                                                      // by the same warp of both CTAs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                        // both CTAs' barriers exist before either is signalled
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -76,30 +125,39 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             bool waited = false;
             int it = 0;                                                  // K blocks issued so far, over all tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * BM, f0 = (tile / m_tiles) * BN;
+            for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step) {
+                const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN + (int)rank * W_ROWS;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
                     if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; ok = false; break; }
-                    mbar_expect_tx(full0 + 8 * s, X_BYTES + W_BYTES);
-                    // weights are written by no kernel of the step: they may be requested at once
-                    tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, kb * BK, f0);
-                    if (!waited) { pdl_wait(); waited = true; }         // activations come from the kernel before
-                    tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, kb * BK, m0);
+                    if (PAIR) {
+                        // both CTAs' tiles count at the "full" barrier of rank 0, which expects them all
+                        const uint32_t full = cluster_map_addr(full0 + 8 * s, 0);
+                        if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * (X_BYTES + W_BYTES));
+                        tma_load_2d_pair(w_smem + s * W_BYTES, &map_w, full, kb * BK, f0);
+                        if (!waited) { pdl_wait(); waited = true; }
+                        tma_load_2d_pair(x_smem + s * X_BYTES, &map_x, full, kb * BK, m0);
+                    } else {
+                        mbar_expect_tx(full0 + 8 * s, X_BYTES + W_BYTES);
+                        // weights are written by no kernel of the step: they may be requested at once
+                        tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, kb * BK, f0);
+                        if (!waited) { pdl_wait(); waited = true; }     // activations come from the kernel before
+                        tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, kb * BK, m0);
+                    }
                 }
             }
-            if (*(volatile int*)&s_abort)
+            if (*(volatile int*)&s_abort && (!PAIR || rank == 0))
                 for (int i = max(0, it - STAGES); i < it; ++i)
                     mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc_bf16(BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = PAIR ? instr_desc_bf16_pair(BN) : instr_desc_bf16(BN);
             int it = 0, j = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++j) {
+            for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step, ++j) {
                 const int acc = j & 1;
                 // the epilogue must have read this accumulator's previous tile out
                 if (!mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, status, 2)) { s_abort = 1; ok = false; break; }
@@ -112,12 +170,17 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     const uint64_t xd = smem_desc_sw128(x_smem + s * X_BYTES);
                     const uint64_t wd = smem_desc_sw128(w_smem + s * W_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_bf16(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                    wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(empty0 + 8 * s);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        if (PAIR)
+                            tc_mma_bf16_pair(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
+                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else
+                            tc_mma_bf16(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
+                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    if (PAIR) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
-                tc_commit(acc_full0 + 8 * acc);
+                if (PAIR) tc_commit_pair(acc_full0 + 8 * acc); else tc_commit(acc_full0 + 8 * acc);
             }
         }
     } else {
@@ -127,9 +190,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         pdl_wait();                                                      // the output may still be in use by an earlier kernel
         int j = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++j) {
+        for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step, ++j) {
             const int acc = j & 1;
-            const int m0 = (tile % m_tiles) * BM, f0 = (tile / m_tiles) * BN;
+            const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN;
             if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, status, 3)) { s_abort = 1; ok = false; break; }
             tc_fence_after();
             const int t = m0 + quarter * 32 + lane;                      // the token row held by this thread
@@ -180,15 +243,20 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
             tc_fence_before();
-            mbar_arrive(acc_empty0 + 8 * acc);                           // this accumulator may be overwritten
+            // this accumulator may be overwritten (a pair: says so to rank 0, which issues the MMAs)
+            if (PAIR) mbar_arrive_cluster(cluster_map_addr(acc_empty0 + 8 * acc, 0)); else mbar_arrive(acc_empty0 + 8 * acc);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // the other CTA's MMAs read this CTA's tiles and write its tensor memory
     if (warp == 1) {
         tc_fence_after();
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -202,12 +270,30 @@ int sm_count() {
     return n;
 }
 
+template <int EPI, typename OutT>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
+                cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = pair_smem();
+    auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int m_tiles = (T + 2 * BM - 1) / (2 * BM), n_tiles = (F + 255) / 256;
+    int pairs = sm_count() / 2;
+    if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
+    return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
+                                            out, T, F, K, ldo, m_tiles, n_tiles, status));
+}
+
 template <int BN, int EPI, typename OutT>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
            cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = wide_smem(BN);
-    auto kern = gemm_tc_wide_kernel<BN, EPI, OutT>;
+    auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -248,5 +334,23 @@ extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out
         if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
         return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     }
+    return PLM_ERR_DTYPE;
+}
+
+// The same product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 tokens x 256 features; see
+// PAIR at the top).  For prompts of at least 256 tokens and at least 256 features.
+extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
+    CUtensorMap mx, mw;
+    int rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, 128)) != PLM_OK) return rc;
+    if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+    if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
+    if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     return PLM_ERR_DTYPE;
 }

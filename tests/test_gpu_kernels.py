@@ -293,6 +293,42 @@ def test_sample_distribution():
     assert chi2 < 40.0                                       # 11 degrees of freedom: 40 is beyond p = 1e-4
 
 
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (2048, 512, 256), (300, 640, 200), (1000, 1152, 2048), (129, 128, 72)])
+def test_gemm_tc_pair(out_dtype, M, N, K, swiglu):
+    """The product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 x 256) against float64: whole
+    and ragged tiles in both directions (a pair whose second CTA has no rows or no features left), K
+    tails, more tiles than pairs, both epilogues."""
+    from picolm_b200 import ops
+    if swiglu and out_dtype == "float32":
+        pytest.skip("the SwiGLU epilogue writes bfloat16")
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    y = a.double() @ w.double().t()
+    if swiglu:
+        wd = ops.interleave_gate_up(w[: N // 2].contiguous().to(DEV), w[N // 2:].contiguous().to(DEV))
+        got = ops.gemm_tc_wide(a.to(DEV), wd, torch.bfloat16, swiglu=True, pair=True)
+        g, u = y[:, : N // 2].bfloat16().double(), y[:, N // 2:].bfloat16().double()
+        ref = g / (1 + torch.exp(-g)) * u
+        assert got.shape == (M, N // 2)
+    else:
+        got = ops.gemm_tc_wide(a.to(DEV), w.to(DEV), DT[out_dtype], pair=True)
+        ref = y
+        assert got.shape == (M, N)
+    ops.check_status(DEV)
+    if out_dtype == "float32":
+        assert torch.allclose(got.double().cpu(), ref, atol=2e-3, rtol=1e-4)
+    else:
+        assert torch.allclose(got.double().cpu(), ref, atol=3e-2, rtol=2e-2)
+    # the single-CTA kernel accumulates in the same order: the same bits
+    if not swiglu:
+        assert torch.equal(got, ops.gemm_tc_wide(a.to(DEV), w.to(DEV), DT[out_dtype]))
+
+
 @pytest.mark.parametrize("window", [None, 90])
 @pytest.mark.parametrize("scratch", [False, True])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (40, 2, 16), (6, 3, 128), (4, 4, 48)])
