@@ -105,7 +105,9 @@ class DecodeGraph:
     def capture(self) -> None:
         from .. import ops
         eng = self.engine
-        self._fill([], [], [])
+        # (the token buffer is shared with the steps around this capture and may hold the ids that the next
+        # replay is to read: it is left as it is; whatever valid ids it holds serve the warm-up run)
+        self._fill([], [], [], device_tokens=self.d[0])
         # once outside the capture: first-call set-up of every kernel, allocator warm-up
         eng.model.forward(self.step, eng.cache)
         torch.cuda.synchronize()

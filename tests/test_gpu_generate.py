@@ -56,6 +56,27 @@ def test_bfloat16_greedy_follows_the_plain_bfloat16_twin(model_dirs):
             seq.append(tok)
 
 
+def test_generation_across_a_new_graph(tmp_path):
+    """Greedy generation that crosses the length at which decode steps get another CUDA graph (every
+    512 positions), while the sampled ids stay on the device: the capture in the middle must not touch
+    them.  Against the plain implementation, token for token, in float32; bfloat16 must agree with itself
+    whether the host looks at every token or not."""
+    from picolm_b200.api import generate, model_load
+    from util import make_model_dir
+    cfg_dict = dict(TINY["A"]["config"], max_position_embeddings=1024)
+    d = make_model_dir(str(tmp_path / "long"), cfg_dict, 7, sharpen=3.0)
+    cfg, w = P.load_model(d)
+    prompts = [random_tokens(500, 256, 91), random_tokens(470, 256, 92)]
+    want = [P.greedy(cfg, w, p, 40) for p in prompts]
+    eng = model_load(d, dtype="float32", max_batch=2)
+    assert generate(eng, prompts, max_tokens=40, temperature=0.0, stop_ids=[]) == want
+    assert len(eng._graphs) >= 2                              # the two length classes each have a graph
+    eng16 = model_load(d, dtype="bfloat16", max_batch=2)
+    a = generate(eng16, prompts, max_tokens=40, temperature=0.0, stop_ids=[])
+    b = generate(eng16, prompts, max_tokens=40, temperature=0.0, stop_ids=[], steps_per_sync=1)
+    assert a == b
+
+
 def test_sampling_is_seeded_per_request(model_dirs):
     """The same seed gives the same tokens; a request's tokens do not depend on
     its batch (its stream is seeded by its index among the prompts)."""
