@@ -1,0 +1,151 @@
+"""The plumbing under the kernels' Python faces: the C signatures, loading a library's entry point,
+error codes, the launch counter, argument helpers and the device status word of the bounded waits."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_library
+
+PAGE_TOKENS = 64            # tokens per cache page; PLM_PAGE in csrc/common.cuh
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+_SIGNATURES = {
+    "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_skinny_residual_parts": [_i, _i],
+    "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _i, _f, _vp, _vp],
+    "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
+    "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_pair": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
+    "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
+    "plm_gemm_tc_plan": [_i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long)],
+    "plm_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _l, _l],
+    "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
+    "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
+}
+_fn_cache = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", -4: "unsupported option",
+          -5: "the device wait ran out (see the status word)"}
+
+
+def _fn(library: str, name: str, extra_flags=()):
+    key = (library, name, tuple(extra_flags))
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = load_library(library, extra_flags)
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = ctypes.c_int
+        _fn_cache[key] = f
+    return f
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (one per successful call of
+    an entry point that launches one kernel)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for kernels that ran (or did not run) outside `_check`: the replays of a CUDA graph."""
+    global _launches
+    _launches += n
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
+    if code == 0:
+        _launches += kernels
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused ({_CODES.get(code, code)})")
+    raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        return torch.cuda.cudart().cudaGetErrorString(code)  # type: ignore[attr-defined]
+    except Exception:
+        return "see cudaError_t"
+
+
+def _dev(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; picolm_b200 kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DT:
+        raise KernelError(f"{name} has dtype {t.dtype}; float32 and bfloat16 are supported")
+    return _DT[t.dtype]
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _dev(t, name)
+    if t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+
+
+SM_COUNT = 148              # SMs of a B200: what grids are sized for
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device int that kernels with bounded waits write to when a wait runs
+    out (0: all well).  One per device."""
+    key = torch.device(device)
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=key)
+        _status[key] = t
+    return t
+
+
+def check_status(device="cuda:0") -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (this
+    synchronises with the device)."""
+    t = _status.get(torch.device(device))
+    if t is None:
+        return
+    code = int(t.item())
+    if code:
+        t.zero_()
+        where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
+        raise KernelError(f"a tensor-core kernel gave up waiting on an mbarrier ({where}); its output is not valid")
+

@@ -1,0 +1,251 @@
+"""Matrix products: the CUDA-core kernel, the tcgen05 kernels for decode-shaped and prompt-shaped
+problems, the pieces of an RMSNorm that two products share, and the dispatcher `linear`."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ._lib import SM_COUNT, KernelError, _check, _dev, _dt, _fn, _p, _stream, status_word
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, fp32 accumulation."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: a is [{M}, {K}] but w is [{N}, {K2}]")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _check(_fn("gemm_simt", "plm_gemm_simt")(
+        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, K, K, N, _stream()), "gemm_simt")
+    return out
+
+
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes a @ w^T: both bfloat16, K a multiple of
+    8 (rows start on 16-byte boundaries, as TMA needs) and at least one K block."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    (M, K), (N, K2) = a.shape, w.shape
+    if K != K2 or K < 64:
+        return False
+    return bool(_fn("gemm_tc", "plm_gemm_tc_supported")(_p(a), _p(w), M, N, K, K, K))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bf16 in, fp32
+    accumulate).  With M <= 64 the weights take the 128-row side of the MMA and K
+    is split; the fp32 partial sums pass through a scratch buffer."""
+    _dev(a, "a"), _dev(w, "w")
+    if not gemm_tc_supported(a, w):
+        raise KernelError(f"gemm_tc: a {tuple(a.shape)} {a.dtype} @ w {tuple(w.shape)} {w.dtype} is not supported "
+                          f"(bfloat16, K a multiple of 8 and >= 64, 16-byte aligned)")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    splits, ws_elems = ctypes.c_int(0), ctypes.c_long(0)
+    _fn("gemm_tc", "plm_gemm_tc_plan")(M, N, K, ctypes.byref(splits), ctypes.byref(ws_elems))
+    ws = torch.empty((ws_elems.value,), dtype=torch.float32, device=a.device) if ws_elems.value else None
+    _check(_fn("gemm_tc", "plm_gemm_tc")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), M, N, K, K, K, N, _p(ws), _p(status_word(a.device)), _stream()),
+        "gemm_tc", kernels=2 if ws is not None else 1)
+    return out
+
+
+def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The decode-shaped tensor-core product: a [M <= 64, K] @ w [N, K]^T with the weights on the MMA's 128
+    rows and K split over a thread-block cluster whose CTAs add their partial tiles up through distributed
+    shared memory.  With `swiglu`, w holds tiles of 64 gate rows followed by their 64 up rows (see
+    `interleave_gate_up`) and the result is silu(gate) * up, [M, N/2] in bfloat16.  `a` may be `ScaledRows`
+    (an RMSNorm whose scale is still due): the epilogue then scales each row of the result, in bfloat16."""
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.x
+        if out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc_skinny: rows with a scale that is still due give a bfloat16 result only")
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if M > 64 or not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc_skinny: needs a supported bfloat16 problem with at most 64 rows")
+    if swiglu:
+        if N % 128:
+            raise KernelError("gemm_tc_skinny: the interleaved gate/up matrix must have a multiple of 128 rows")
+        out_dtype = torch.bfloat16
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    if scaled is not None:
+        _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_scaled")(
+            _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
+            scaled.parts.shape[1], scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()),
+            "gemm_tc_skinny_scaled")
+        return out
+    _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
+        _p(status_word(a.device)), _stream()), "gemm_tc_skinny")
+    return out
+
+
+class PendingLinear:
+    """a [M, K] @ w [N, K]^T in float32 that has not run yet: the last product of a mixer or a
+    feed-forward, whose result is a delta for the residual stream.  The norm that follows may run it
+    with the residual add and its own weight in the epilogue (`linear_residual_norm`); anything else
+    calls `compute()`."""
+    __slots__ = ("a", "w")
+
+    def __init__(self, a: torch.Tensor, w: torch.Tensor):
+        self.a, self.w = a, w
+
+    @property
+    def shape(self):
+        return (self.a.shape[0], self.w.shape[0])
+
+    def compute(self) -> torch.Tensor:
+        return linear(self.a, self.w, torch.float32)
+
+
+class ScaledRows:
+    """An RMSNorm whose scale is still due: `x` [T, size] in bfloat16 holds row * norm weight, and
+    `parts` [n, >= T] partial sums of squares of the rows (column t for row t), so that the normalised
+    row t is x[t] / sqrt(sum(parts[:, t]) / size + eps).  A product takes it as its left operand and
+    applies the scale to its result (`linear`, `linear_swiglu`); `materialize()` gives the rows."""
+    __slots__ = ("x", "parts", "size", "eps")
+
+    def __init__(self, x: torch.Tensor, parts: torch.Tensor, size: int, eps: float):
+        self.x, self.parts, self.size, self.eps = x, parts, size, eps
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty_like(self.x)
+        T, d = self.x.shape
+        _check(_fn("elementwise", "plm_scale_rows")(
+            _p(self.x), _p(self.parts), self.parts.shape[0], self.parts.shape[1], self.size, float(self.eps),
+            _p(out), T, d, _stream()), "scale_rows")
+        return out
+
+
+def residual_norm_supported(pending, x: torch.Tensor, norm_weight: torch.Tensor) -> bool:
+    """Whether `linear_residual_norm` takes this case: a pending product of at most 64 rows that the
+    cluster kernel takes, an fp32 stream of its shape and a bfloat16 norm weight.  (For more rows the
+    fused epilogue was measured slower than a norm kernel of its own: there a thread of the epilogue
+    holds a row of the tile, and its read-modify-write of the stream does not coalesce.)"""
+    return (isinstance(pending, PendingLinear) and pending.a.shape[0] <= 64 and gemm_tc_supported(pending.a, pending.w)
+            and x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == tuple(pending.shape)
+            and norm_weight.dtype == torch.bfloat16 and norm_weight.shape == (x.shape[1],))
+
+
+def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> ScaledRows:
+    """x += pending (in place, the fp32 residual stream) and the RMSNorm of the new x as `ScaledRows`:
+    one tensor-core product whose epilogue does the add, applies the norm weight and leaves the rows'
+    sums of squares; the scale itself is applied by the product that takes the result."""
+    if not residual_norm_supported(pending, x, norm_weight):
+        raise KernelError("linear_residual_norm: not a case the fused kernel takes")
+    a, w = pending.a, pending.w
+    _dev(a, "a"), _dev(w, "w"), _dev(x, "x"), _dev(norm_weight, "norm_weight")
+    M, K = a.shape
+    N = w.shape[0]
+    xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    n_parts = _fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual_parts")(N, K)
+    parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
+    _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual")(
+        _p(a), _p(w), _p(x), _p(norm_weight), _p(xw), _p(parts), M, N, K, K, K, N, N,
+        _p(status_word(x.device)), _stream()), "gemm_tc_skinny_residual")
+    return ScaledRows(xw, parts, N, eps)
+
+
+def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+                 out: Optional[torch.Tensor] = None, pair: bool = False) -> torch.Tensor:
+    """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
+    (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
+    tile's main loop).  With `swiglu`, w comes from `interleave_gate_up` and the result is
+    silu(gate) * up, [M, N/2] in bfloat16.  `pair`: the same by pairs of CTAs on tiles of 256 x 256
+    (`tcgen05.mma.cta_group::2`: each CTA of a pair loads half of the weight tile)."""
+    _dev(a, "a"), _dev(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc_wide: needs bfloat16 operands that TMA can address")
+    if swiglu:
+        if N % 128:
+            raise KernelError("gemm_tc_wide: the interleaved gate/up matrix must have a multiple of 128 rows")
+        out_dtype = torch.bfloat16
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair" if pair else "plm_gemm_tc_wide")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
+        _p(status_word(a.device)), _stream()), "gemm_tc_pair" if pair else "gemm_tc_wide")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[gate | up] as one matrix whose rows come in tiles of 64 gate rows followed by the 64 up rows of
+    the same features, so that a 128-row MMA tile holds both branches of 64 outputs and the product's
+    epilogue can apply SwiGLU.  Needs a number of features that is a multiple of 64."""
+    F, K = gate.shape
+    if up.shape != gate.shape or F % 64:
+        raise KernelError("interleave_gate_up: gate and up must have the same shape with a multiple of 64 rows")
+    return torch.stack([gate.view(F // 64, 64, K), up.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def pair_pays(m: int, n: int) -> bool:
+    """Whether the prompt-shaped product runs as pairs of CTAs on tiles of 256 x 256: measured 3..5 % faster
+    than single CTAs on tiles of 128 x 256 where there are at least two rounds of tiles for the 74 pairs,
+    and no faster or slower (a ragged last round of larger tiles) below that."""
+    return m >= 256 and n >= 256 and ((m + 255) // 256) * ((n + 255) // 256) >= SM_COUNT
+
+
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
+    whose epilogue applies the activation; [M, F] in bfloat16.  `a` may be `ScaledRows`."""
+    if isinstance(a, ScaledRows) and not (a.shape[0] <= 64 and gemm_tc_supported(a.x, w_gate_up)):
+        a = a.materialize()
+    x = a.x if isinstance(a, ScaledRows) else a
+    _dev(x, "a"), _dev(w_gate_up, "w_gate_up")
+    M, K = x.shape
+    N = w_gate_up.shape[0]
+    if not gemm_tc_supported(x, w_gate_up) or N % 128:
+        raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
+    if M <= 64:
+        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
+    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N))
+
+
+def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):
+    """a [M, K] times w [N, K]^T -> [M, N].  The kernel is chosen by element
+    types and shape, never by the model: the tensor cores for bfloat16 operands
+    that TMA can address (the cluster kernel for up to 64 rows, the wide kernel
+    beyond), the CUDA cores for everything else.
+
+    `a` may be `ScaledRows`.  With `defer` (a float32 delta for the residual stream) the product may
+    come back as a `PendingLinear` for the next norm to run; whoever cannot use that calls `compute()`."""
+    if isinstance(a, ScaledRows):
+        if a.shape[0] <= 64 and out_dtype == torch.bfloat16 and gemm_tc_supported(a.x, w):
+            return gemm_tc_skinny(a, w, out_dtype)
+        a = a.materialize()
+    if defer and out_dtype == torch.float32 and a.shape[0] <= 64 and gemm_tc_supported(a, w):
+        return PendingLinear(a, w)
+    if gemm_tc_supported(a, w):
+        if a.shape[0] <= 64:
+            return gemm_tc_skinny(a, w, out_dtype)
+        return gemm_tc_wide(a, w, out_dtype, pair=pair_pays(a.shape[0], w.shape[0]))
+    return gemm_simt(a, w, out_dtype)
