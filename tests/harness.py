@@ -54,3 +54,18 @@ def run_batch(engine, requests, prompt_lens):
     finally:
         for s in slots:
             engine.end_sequence(s)
+
+
+def run_chunks(engine, tokens, sizes):
+    """One request fed in pieces of `sizes` tokens (several tokens at a time after a cached prefix: the
+    prompt kernels with a start position).  Returns logits [T, vocab] like run_whole."""
+    assert sum(sizes) == len(tokens)
+    s = engine.new_sequence()
+    try:
+        out, o = [], 0
+        for n in sizes:
+            out.append(engine.step([(s, tokens[o:o + n])], [list(range(n))]).float().cpu())
+            o += n
+        return torch.cat(out, dim=0)
+    finally:
+        engine.end_sequence(s)

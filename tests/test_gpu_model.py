@@ -3,7 +3,7 @@ for every way of cutting requests into steps."""
 import pytest
 import torch
 
-from harness import run_batch, run_tail, run_whole
+from harness import run_batch, run_chunks, run_tail, run_whole
 from plain import llama_plain as P
 from util import TINY, assert_close, random_tokens
 
@@ -110,6 +110,19 @@ def test_long_decoding_and_first_tokens(engines, plain, name, dtype):
     ref = plain(name, toks, dtype)
     assert_close(got[:4], ref[:4], dtype, f"{name} {dtype} first tokens")
     assert_close(got, ref, dtype, f"{name} {dtype} long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
+def test_prompt_in_pieces(engines, plain, name, dtype):
+    """A prompt fed in pieces of several tokens: every piece after the first attends to a cached prefix
+    and to itself (pieces that end inside a page, a piece of one token in between)."""
+    eng = engines(name, dtype)
+    n = min(_ctx(name), 128)
+    toks = random_tokens(n, _vocab(name), 77)
+    sizes = [40, 30, 1, 17, n - 88]
+    assert_close(run_chunks(eng, toks, sizes), plain(name, toks, dtype), dtype, f"{name} {dtype} pieces")
+    eng.cache.check()
 
 
 def test_float32_results_do_not_depend_on_the_cut(engines):

@@ -4,7 +4,7 @@ the shapes that serving uses, against the plain implementation on the CPU."""
 import pytest
 import torch
 
-from harness import run_batch, run_tail, run_whole
+from harness import run_batch, run_chunks, run_tail, run_whole
 from plain import llama_plain as P
 from util import assert_close, make_model_dir, random_tokens
 
@@ -45,6 +45,7 @@ def test_real_widths_in_every_cut(real, dtype):
     for n in (200, 33):
         assert_close(run_whole(eng, toks[n]), plain(n, dtype), dtype, f"real widths {dtype} whole {n}")
     assert_close(run_tail(eng, toks[70], tail=32), plain(70, dtype), dtype, f"real widths {dtype} tail")
+    assert_close(run_chunks(eng, toks[200], [90, 70, 40]), plain(200, dtype), dtype, f"real widths {dtype} pieces")
     outs = run_batch(eng, [toks[200], toks[33], toks[70]], [150, 20, 64])
     for n, got in zip((200, 33, 70), outs):
         assert_close(got, plain(n, dtype), dtype, f"real widths {dtype} batch {n}")
@@ -91,6 +92,7 @@ def test_head_size_128_in_every_cut(tmp_path_factory, dtype):
     eng = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 24, max_seqs=4)
     assert_close(run_whole(eng, toks[300]), ref[300], dtype, f"hd128 {dtype} whole")
     assert_close(run_tail(eng, toks[130], tail=32), ref[130], dtype, f"hd128 {dtype} tail")
+    assert_close(run_chunks(eng, toks[300], [130, 100, 70]), ref[300], dtype, f"hd128 {dtype} pieces")
     outs = run_batch(eng, [toks[300], toks[40], toks[130]], [200, 25, 100])
     for n, got in zip((300, 40, 130), outs):
         assert_close(got, ref[n], dtype, f"hd128 {dtype} batch {n}")
