@@ -125,6 +125,30 @@ def test_prompt_in_pieces(engines, plain, name, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_token_and_a_prompt_in_one_step(engines, plain, dtype):
+    """The step function takes any mixture: a sequence that goes on by one token beside one that brings a
+    whole prompt, then both go on with pieces of unequal lengths."""
+    name = "A_sharp"
+    eng = engines(name, dtype)
+    a, b = random_tokens(60, _vocab(name), 81), random_tokens(45, _vocab(name), 82)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    try:
+        got_a = [eng.step([(sa, a[:20])], [list(range(20))]).float().cpu()]
+        out = eng.step([(sa, a[20:21]), (sb, b[:30])], [[0], list(range(30))]).float().cpu()
+        got_a.append(out[:1])
+        got_b = [out[1:]]
+        out = eng.step([(sb, b[30:45]), (sa, a[21:60])], [list(range(15)), list(range(39))]).float().cpu()
+        got_b.append(out[:15])
+        got_a.append(out[15:])
+    finally:
+        eng.end_sequence(sa)
+        eng.end_sequence(sb)
+    assert_close(torch.cat(got_a), plain(name, a, dtype), dtype, f"{dtype} mixed step, first sequence")
+    assert_close(torch.cat(got_b), plain(name, b, dtype), dtype, f"{dtype} mixed step, second sequence")
+    eng.cache.check()
+
+
 def test_float32_results_do_not_depend_on_the_cut(engines):
     """In float32 every kernel accumulates in an order fixed by the row itself,
     so the three ways of cutting agree to the last bit."""
