@@ -185,7 +185,7 @@ def main():
         write_random_model(cfg, seed, tmp, norm_std=0.0)
         # the cache holds what the largest run needs (its prompts, warm-up and timed steps), not
         # max_b full contexts: at the 13B shape those would not fit the GPU
-        per_seq = min(context, (max(prompt_len, prefill_tokens) + 2 * args.warmup + 2 * args.steps + 16 + 63) // 64 * 64)
+        per_seq = min(context, (max(prompt_len, prefill_tokens) + 2 * args.warmup + 3 * args.steps + 16 + 63) // 64 * 64)
         engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * per_seq, max_seqs=max_b,
                                     max_seq_tokens=context, use_graphs=False if args.no_graphs else None)
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr)
@@ -266,7 +266,7 @@ def main():
         points[f"decode_b{pb}"] = round(pb / pms * 1e3, 1)
 
     # ------------------------------------------- end to end, host ids in and out
-    gen_new = args.warmup + args.steps
+    gen_new = args.warmup + 2 * args.steps            # long enough to outlast the clock dip after the prompts' step
     ps = prompts(B)
     generate(engine, ps, max_tokens=4, temperature=0.0, stop_ids=[], max_batch=B)            # warm-up
     engine.reset_counters()

@@ -104,7 +104,7 @@ def _decode_ahead(engine, sampler, batch, slots, live, first_tokens, stop, on_to
         torch.empty((depth + 1, n0), dtype=torch.int32)
 
     def judge(members, tokens, lengths_after_feed):
-        """Append a step's tokens to the sequences that are still undecided; returns those that go on."""
+        """Append a step's tokens to the sequences that no earlier token has ended, and decide whether they end."""
         for i, tok, length in zip(members, tokens, lengths_after_feed):
             r = batch[i]
             if r.finish_reason is not None:              # ended by an earlier token: this one is surplus
