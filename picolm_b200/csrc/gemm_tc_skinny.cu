@@ -217,7 +217,58 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (r < S) v += recv[(((int)r * BN + c) * HALVES + half) * slice + pr];
         return v;
     };
-    for (int it = threadIdx.x; it < items; it += NUM_THREADS) {
+    // The residual epilogue four features at a time where everything is aligned for it (the usual case):
+    // 16-byte loads of the partial sums and of the stream, 8-byte loads and stores of the bf16 sides.
+    bool residual_done = false;
+    if constexpr (EPI == EPI_RESIDUAL) {
+        if (slice % 4 == 0 && ldo % 4 == 0 && fz.ld_xw % 4 == 0 && ((uintptr_t)out & 15) == 0 &&
+            ((uintptr_t)fz.xw & 7) == 0 && ((uintptr_t)fz.norm_w & 7) == 0) {
+            residual_done = true;
+            const int quads = slice / 4;
+            for (int it = threadIdx.x; it < quads * BN; it += NUM_THREADS) {
+                const int c = it / quads, pr = (it - c * quads) * 4;
+                const int t = c, f = p0 + (int)rank * slice + pr;
+                float sq[4] = {0.f, 0.f, 0.f, 0.f};
+                if (t < T && f < F) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+                        if (r < S) {
+                            const float4 p = *reinterpret_cast<const float4*>(&recv[((int)r * BN + c) * slice + pr]);
+                            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+                        }
+                    float* xp = reinterpret_cast<float*>(out) + (size_t)t * ldo + f;
+                    bf16* wp = fz.xw + (size_t)t * fz.ld_xw + f;
+                    if (f + 3 < F) {
+                        const float4 x = *reinterpret_cast<const float4*>(xp);
+                        const float xn[4] = {x.x + v.x, x.y + v.y, x.z + v.z, x.w + v.w};
+                        *reinterpret_cast<float4*>(xp) = make_float4(xn[0], xn[1], xn[2], xn[3]);
+                        const uint2 nw = *reinterpret_cast<const uint2*>(fz.norm_w + f);
+                        const __nv_bfloat162 n01 = *reinterpret_cast<const __nv_bfloat162*>(&nw.x);
+                        const __nv_bfloat162 n23 = *reinterpret_cast<const __nv_bfloat162*>(&nw.y);
+                        __nv_bfloat162 o01 = __floats2bfloat162_rn(xn[0] * __low2float(n01), xn[1] * __high2float(n01));
+                        __nv_bfloat162 o23 = __floats2bfloat162_rn(xn[2] * __low2float(n23), xn[3] * __high2float(n23));
+                        uint2 o;
+                        o.x = *reinterpret_cast<uint32_t*>(&o01);
+                        o.y = *reinterpret_cast<uint32_t*>(&o23);
+                        *reinterpret_cast<uint2*>(wp) = o;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sq[e] = xn[e] * xn[e];
+                    } else {
+                        const float vv[4] = {v.x, v.y, v.z, v.w};
+                        for (int e = 0; e < 4 && f + e < F; ++e) {
+                            const float xn = xp[e] + vv[e];
+                            xp[e] = xn;
+                            wp[e] = __float2bfloat16_rn(xn * __bfloat162float(fz.norm_w[f + e]));
+                            sq[e] = xn * xn;
+                        }
+                    }
+                }
+                *reinterpret_cast<float4*>(&squares[c * slice + pr]) = make_float4(sq[0], sq[1], sq[2], sq[3]);
+            }
+        }
+    }
+    for (int it = threadIdx.x; it < items && !residual_done; it += NUM_THREADS) {
         const int c = it / slice, pr = it - c * slice;
         const int row = (int)rank * slice + pr;
         const int t = c;
