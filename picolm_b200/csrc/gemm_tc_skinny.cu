@@ -219,7 +219,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     };
     // The residual epilogue four features at a time where everything is aligned for it (the usual case):
     // 16-byte loads of the partial sums and of the stream, 8-byte loads and stores of the bf16 sides.
-    bool residual_done = false;
+    bool residual_done = false;                                    // (any of the wide forms below ran)
     if constexpr (EPI == EPI_RESIDUAL) {
         if (slice % 4 == 0 && ldo % 4 == 0 && fz.ld_xw % 4 == 0 && ((uintptr_t)out & 15) == 0 &&
             ((uintptr_t)fz.xw & 7) == 0 && ((uintptr_t)fz.norm_w & 7) == 0) {
@@ -265,6 +265,47 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     }
                 }
                 *reinterpret_cast<float4*>(&squares[c * slice + pr]) = make_float4(sq[0], sq[1], sq[2], sq[3]);
+            }
+        }
+    }
+    // The same for the store and SwiGLU epilogues with bf16 output: four results, one 8-byte store.
+    if constexpr (EPI != EPI_RESIDUAL && sizeof(OutT) == 2) {
+        const int n_out = EPI == EPI_SWIGLU ? F / 2 : F;
+        const int o0 = (EPI == EPI_SWIGLU ? p0 / 2 : p0) + (int)rank * slice;       // first output column of this CTA
+        if (slice % 4 == 0 && ldo % 4 == 0 && n_out % 4 == 0 && ((uintptr_t)out & 7) == 0) {
+            residual_done = true;
+            const int quads = slice / 4;
+            for (int it = threadIdx.x; it < quads * BN; it += NUM_THREADS) {
+                const int c = it / quads, pr = (it - c * quads) * 4;
+                const int t = c, fo = o0 + pr;
+                if (t >= T || fo >= n_out) continue;                                  // n_out % 4 == 0: whole quads only
+                float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll
+                for (uint32_t r = 0; r < MAX_SPLITS; ++r)
+                    if (r < S) {
+                        const float4 p = *reinterpret_cast<const float4*>(&recv[(((int)r * BN + c) * HALVES) * slice + pr]);
+                        g.x += p.x; g.y += p.y; g.z += p.z; g.w += p.w;
+                        if (EPI == EPI_SWIGLU) {
+                            const float4 q = *reinterpret_cast<const float4*>(&recv[(((int)r * BN + c) * HALVES + 1) * slice + pr]);
+                            u.x += q.x; u.y += q.y; u.z += q.z; u.w += q.w;
+                        }
+                    }
+                float v[4] = {g.x, g.y, g.z, g.w};
+                if (SCALE) {
+                    const float sc = s_scale[c];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] *= sc;
+                    u.x *= sc; u.y *= sc; u.z *= sc; u.w *= sc;
+                }
+                if (EPI == EPI_SWIGLU) {
+                    v[0] = swiglu_bf16(v[0], u.x); v[1] = swiglu_bf16(v[1], u.y);
+                    v[2] = swiglu_bf16(v[2], u.z); v[3] = swiglu_bf16(v[3], u.w);
+                }
+                __nv_bfloat162 o01 = __floats2bfloat162_rn(v[0], v[1]), o23 = __floats2bfloat162_rn(v[2], v[3]);
+                uint2 o;
+                o.x = *reinterpret_cast<uint32_t*>(&o01);
+                o.y = *reinterpret_cast<uint32_t*>(&o23);
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + (size_t)t * ldo + fo) = o;
             }
         }
     }
