@@ -105,7 +105,7 @@ def bench_attention_decode(args):
     q = torch.randn(B, H, hd, device="cuda").to(torch.bfloat16)
     pos = torch.full((B,), C - 1, dtype=torch.int32, device="cuda")
     seq = torch.arange(B, dtype=torch.int32, device="cuda")
-    splits = args.splits or ops.decode_splits(B, H, G, C)
+    splits = args.splits or ops.decode_splits(B, H, G, C, hd)
 
     def run(i):
         ops.attention_decode(q, caches[i][0], caches[i][1], pos, seq, table, G, 1.0 / math.sqrt(hd), splits,

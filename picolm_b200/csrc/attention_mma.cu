@@ -76,13 +76,15 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, int valid)
 }
 
 // S[16 x 8*NKT] += Q[16 x HD] . K^T for keys [key0, key0 + 8*NKT) of a tile; q_rows points at the
-// warp's 16 query rows in shared memory.
+// warp's query rows in shared memory, of which this lane addresses row `arow` (lane % 16 where all 16
+// rows are there; the decode kernel keeps fewer and points the others at a row of zeros).
 template <int NKT>
-__device__ __forceinline__ void qk_tile(float (&s)[NKT][4], const bf16* q_rows, const bf16* k_tile, int key0, int lane) {
+__device__ __forceinline__ void qk_tile(float (&s)[NKT][4], const bf16* q_rows, const bf16* k_tile, int key0, int lane,
+                                        int arow) {
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
         uint32_t a[4];
-        ldsm_x4(a, smem_u32(q_rows + (lane & 15) * LDS + ks * 16 + (lane >> 4) * 8));
+        ldsm_x4(a, smem_u32(q_rows + arow * LDS + ks * 16 + (lane >> 4) * 8));
 #pragma unroll
         for (int j = 0; j < NKT; j += 2) {
             uint32_t b[4];
@@ -253,7 +255,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
             float s[8][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-            qk_tile<8>(s, q_s + warp * 16 * LDS, kt, 0, lane);
+            qk_tile<8>(s, q_s + warp * 16 * LDS, kt, 0, lane, lane & 15);
             softmax_block<8>(s, o, m, l, scale_log2, key_base, pos_lo, pos_hi, lo_lo, lo_hi, lane);
             pv_tile<8>(o, s, vt, 0, lane);
         }
@@ -278,11 +280,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
 // -------------------------------------------------------------------- decode
 constexpr int DC_STAGES = 3;
 constexpr size_t DC_TILES_BYTES = (size_t)(2 * DC_STAGES) * TILE_ELEMS * sizeof(bf16);
-constexpr size_t DC_Q_BYTES = (size_t)16 * LDS * sizeof(bf16);
+// Query rows kept in shared memory: all 16 of the MMA's rows, or, for up to 8 query heads per KV head,
+// those 8 and one row of zeros that stands for the rest: with head size 64 that lets four CTAs share an SM
+// instead of three (57,088 bytes each at most), and a third more bytes are in flight.
+constexpr size_t dc_q_bytes(int q_rows) { return (size_t)q_rows * LDS * sizeof(bf16); }
 constexpr size_t DC_MERGE_BYTES = (size_t)4 * 16 * (HD + 2) * sizeof(float);
 constexpr size_t DC_RESULT_BYTES = (size_t)16 * (HD + 2) * sizeof(float);          // what a CTA shows to its cluster
 constexpr size_t DC_AFTER_BYTES = DC_MERGE_BYTES + DC_RESULT_BYTES;
-constexpr size_t DC_SMEM = DC_Q_BYTES + (DC_TILES_BYTES > DC_AFTER_BYTES ? DC_TILES_BYTES : DC_AFTER_BYTES);
+constexpr size_t dc_smem(int q_rows) { return dc_q_bytes(q_rows) + (DC_TILES_BYTES > DC_AFTER_BYTES ? DC_TILES_BYTES : DC_AFTER_BYTES); }
+constexpr size_t DC_SMEM = dc_smem(16);
 constexpr int DC_MAX_CLUSTER = 8;                                                   // portable cluster size
 
 // grid = (splits, G * row_groups, tokens).  With one split the output is written directly.  With
@@ -327,13 +333,15 @@ __global__ void __launch_bounds__(NT)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table,
-                   int max_pages, int H, int G, float scale_log2, int window, int row_groups, const Rotary rot) {
+                   int max_pages, int H, int G, float scale_log2, int window, int row_groups, const Rotary rot,
+                   int q_rows) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    const size_t q_bytes = (size_t)q_rows * LDS * sizeof(bf16);          // q_rows: 16, or 9 (8 heads and a row of zeros)
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
-    bf16* k_s = reinterpret_cast<bf16*>(smem_raw + DC_Q_BYTES);
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw + q_bytes);
     bf16* v_s = k_s + DC_STAGES * TILE_ELEMS;
-    float* merge = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES);      // reused after the last tile
-    float* result = reinterpret_cast<float*>(smem_raw + DC_Q_BYTES + DC_MERGE_BYTES);
+    float* merge = reinterpret_cast<float*>(smem_raw + q_bytes);         // reused after the last tile
+    float* result = reinterpret_cast<float*>(smem_raw + q_bytes + DC_MERGE_BYTES);
     pdl_launch_dependents();
     // What describes the step (positions, page tables) was written before the step began, and pages
     // before a sequence's last one hold keys of earlier steps: all of that may be read before the
@@ -379,7 +387,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     }
     if (n_pages > 0 && !ROPE) {                         // (in a cluster an empty split still meets the others)
         constexpr int CPR = HD / 8;                     // the queries: plain loads, visible after the loop's first barrier
-        for (int c = threadIdx.x; c < 16 * CPR; c += NT) {
+        for (int c = threadIdx.x; c < q_rows * CPR; c += NT) {
             const int r = c / CPR, col = c - r * CPR;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * H + h0 + r) * HD + col * 8);
@@ -389,7 +397,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const bf16* qkv_row = q + (size_t)t * (H + 2 * G) * HD;              // ROPE: this token's projections
     if (n_pages > 0 && ROPE) {
         constexpr int GRP = HD / 16;                    // groups of 8 pairs per head
-        for (int c = threadIdx.x; c < 16 * GRP; c += NT) {
+        for (int c = threadIdx.x; c < q_rows * GRP; c += NT) {
             const int r = c / GRP, j = (c - r * GRP) * 8;
             uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
             if (r < n_rows) {
@@ -446,7 +454,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
             float s[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-            qk_tile<2>(s, q_s, kt, warp * 16, lane);
+            qk_tile<2>(s, q_s, kt, warp * 16, lane, min(lane & 15, q_rows - 1));
             softmax_block<2>(s, o, m, l, scale_log2, key_base, pos, pos, lo, lo, lane);
             pv_tile<2>(o, s, vt, warp * 16, lane);
         }
@@ -563,6 +571,11 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
     }
 }
 
+// 9 query rows (8 heads and a row of zeros) make room for a fourth CTA on an SM.  That pays where the grid
+// is several waves long (large batches: a third more bytes in flight); a grid of one wave runs better with
+// three, which leave room for the CTAs of the kernel behind it to ask for their weights meanwhile.
+int decode_q_rows(int heads_per_kv_head, long ctas) { return heads_per_kv_head <= 8 && ctas > 3 * 148 ? 9 : 16; }
+
 template <typename K>
 int set_smem(K kern, size_t bytes) {
     if (bytes <= 48 * 1024) return PLM_OK;
@@ -617,19 +630,21 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
     }
     const int R = H / G, row_groups = (R + 15) / 16;
     if (G * row_groups > 65535) return PLM_ERR_SHAPE;
+    const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
+    const size_t smem = dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
     if (n_splits > 1 && !workspace) {                       // the splits merge inside their cluster
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
-        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)q,
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false>, grid, dim3(NT), smem, stream, (const bf16*)q,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
@@ -654,19 +669,21 @@ extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* o
     const int R = H / G, row_groups = (R + 15) / 16;
     if (G * row_groups > 65535) return PLM_ERR_SHAPE;
     const Rotary rot = {cos_t, sin_t, (bf16*)kc, (bf16*)vc};
+    const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
+    const size_t smem = dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
     if (n_splits > 1 && !workspace) {
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
-        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true>, grid, dim3(NT), dim3(n_splits, 1, 1), DC_SMEM,
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)qkv, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true>, grid, dim3(NT), DC_SMEM, stream, (const bf16*)qkv,
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true>, grid, dim3(NT), smem, stream, (const bf16*)qkv,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));

@@ -94,16 +94,27 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 DECODE_CLUSTER_SPLITS = 8       # up to this many ranges merge inside a thread-block cluster, without scratch
 
 
-def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
+def decode_ctas_per_sm(head_dim: int, heads_per_kv_head: int) -> int:
+    """How many CTAs of the decode kernel share an SM: its shared memory (three stages of a key and a value
+    tile of 64 padded rows, and 9 or 16 query rows; csrc/attention_mma.cu) against the SM's 227 KB."""
+    row = (head_dim + 8) * 2
+    smem = (9 if heads_per_kv_head <= 8 else 16) * row + 6 * 64 * row
+    return max(1, min(6, (227 * 1024) // (smem + 1024)))         # (registers allow six)
+
+
+def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 64) -> int:
     """Into how many ranges the decode kernel cuts each sequence's keys.  Where the whole grid runs at once
-    (three CTAs an SM), as many ranges as that allows, up to the eight that merge inside a cluster, each of
-    at least two pages.  Otherwise, and for long contexts (whose ranges would get too long for one wave
-    of CTAs), about eight pages a range, more when that leaves SMs without a CTA (measured at batch 1, 8
-    and 64 with 2,048 keys)."""
+    (up to three CTAs an SM), as many ranges as that allows, up to the eight that merge inside a
+    cluster, each of at least two pages.  Otherwise, and for long contexts (whose ranges would get too long
+    for one wave of CTAs), about eight pages a range, more when that leaves SMs without a CTA (measured at
+    batch 1, 8, 16 and 64 with 2,048 keys)."""
     row_groups = (num_heads // num_kv_heads + 15) // 16
     ctas = max(1, n_tokens * num_kv_heads * row_groups)
     pages = max(1, (max_kv_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
-    in_cluster = min(DECODE_CLUSTER_SPLITS, (3 * SM_COUNT) // ctas, max(1, pages // 2))
+    # (at most three CTAs an SM are counted on: a grid that fills the SMs to the brim keeps the next kernel's
+    # CTAs, which would already be asking for their weights, off them; measured at batch 8)
+    wave = min(3, decode_ctas_per_sm(head_dim, num_heads // num_kv_heads)) * SM_COUNT
+    in_cluster = min(DECODE_CLUSTER_SPLITS, wave // ctas, max(1, pages // 2))
     if in_cluster >= 2 and pages <= (16 if ctas * in_cluster >= SM_COUNT else 8) * in_cluster:
         return in_cluster
     splits = (pages + 7) // 8
@@ -128,7 +139,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     # Clusters are scheduled as a whole: past one wave of CTAs that costs more than the second kernel saves.
     ctas = T * num_kv_heads * ((H // num_kv_heads + 15) // 16) * n_splits
     if scratch is None:
-        scratch = ctas > 3 * SM_COUNT
+        scratch = ctas > min(3, decode_ctas_per_sm(hd, H // num_kv_heads)) * SM_COUNT
     scratch = n_splits > 1 and (scratch or n_splits > DECODE_CLUSTER_SPLITS)
     ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=q.device) if scratch else None
     lib, flags = attention_variant(hd)
@@ -171,10 +182,10 @@ def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_he
         raise KernelError("attention_decode_rope: qkv or the cache does not have the shape the heads imply")
     if step.max_position >= rotation.cos.shape[0]:
         raise KernelError(f"position {step.max_position} lies beyond the rotary table")
-    n_splits = decode_splits(T, H, G, step.max_position + 1)
+    n_splits = decode_splits(T, H, G, step.max_position + 1, hd)
     ctas = T * G * ((H // G + 15) // 16) * n_splits
     if scratch is None:
-        scratch = ctas > 3 * SM_COUNT
+        scratch = ctas > min(3, decode_ctas_per_sm(hd, H // G)) * SM_COUNT
     scratch = n_splits > 1 and (scratch or n_splits > DECODE_CLUSTER_SPLITS)
     out = torch.empty((T, H * hd), dtype=qkv.dtype, device=qkv.device)
     ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=qkv.device) if scratch else None
@@ -191,7 +202,7 @@ def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> tor
     and values (`kv` is a `KVLayerCache`)."""
     if attention_mma_supported(q):
         if step.is_decode:
-            splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1)
+            splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1, q.shape[2])
             return attention_decode(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                                     splits, window=kv.window)
         prefill = attention_prefill_tc if attention_tc_supported(q) else attention_prefill
