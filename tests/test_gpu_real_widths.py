@@ -100,3 +100,45 @@ def test_head_size_128_in_every_cut(tmp_path_factory, dtype):
     if dtype == "bfloat16":
         from picolm_b200 import ops
         ops.check_status()
+
+
+# A long sequence: dozens of pages, so that the prompt kernel walks many of them per query tile and the
+# decode kernel cuts the keys into more ranges than a cluster holds (scratch memory and a merge kernel).
+CONFIG_LONG = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 512,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 1024,
+    "vocab_size": 1500, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 1024},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 8192, "tie_word_embeddings": True, "hidden_act": "silu",
+    "bos_token_id": 1, "eos_token_id": 2,
+}
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_a_long_sequence(tmp_path_factory, dtype):
+    from picolm_b200 import ops
+    from picolm_b200.engine import Engine
+    d = make_model_dir(str(tmp_path_factory.mktemp("long") / "m"), CONFIG_LONG, 9, sharpen=4.0)
+    cfg, w = P.load_model(d)
+    n = 4500
+    toks = random_tokens(n, CONFIG_LONG["vocab_size"], 77)
+    ref = P.forward(cfg, w, toks, act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
+    eng = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 72, max_seqs=2)
+    if dtype == "bfloat16":
+        assert ops.decode_splits(1, 8, 2, n, 64) > 8            # the decode steps below go through scratch memory
+    s = eng.new_sequence()
+    try:
+        head = n - 12
+        rows = [0, 63, 64, 1000, 2047, 2048, 4000, head - 1]
+        got = [eng.step([(s, toks[:head])], [rows]).float().cpu()]
+        want = [ref[rows]]
+        for t in range(head, n):
+            got.append(eng.step([(s, [toks[t]])], [[0]]).float().cpu())
+            want.append(ref[t:t + 1])
+    finally:
+        eng.end_sequence(s)
+    assert_close(torch.cat(got), torch.cat(want), dtype, f"long sequence {dtype}")
+    eng.cache.check()
+    if dtype == "bfloat16":
+        ops.check_status()
