@@ -47,6 +47,10 @@ def build_parser() -> argparse.ArgumentParser:
     e.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                    help="bfloat16 (serving kernels) or float32 (everything in true 32-bit)")
     e.add_argument("--max-batch", type=int, default=8, help="most sequences generated together (default: 8)")
+    b = ap.add_argument_group("Benchmark options")
+    b.add_argument("--benchmark-ctx", action="store_true",
+                   help="benchmark prefill+gen speed at growing context sizes: the prompt (-p) is prefilled again and "
+                        "again behind what is already cached, -n tokens are generated after each, up to the context (-c)")
     i = ap.add_argument_group("Info options")
     i.add_argument("--list-tensors", action="store_true", help="list all tensors (name, shape, type) and exit")
     r = ap.add_argument_group("Random weights")
@@ -54,6 +58,38 @@ def build_parser() -> argparse.ArgumentParser:
                    help="write a model folder with random weights for this config.json and exit")
     r.add_argument("--out", help="folder to write with --random-weights")
     return ap
+
+
+def benchmark_context_scaling(args, base: List[int]) -> int:
+    """The reference's `--benchmark-ctx` (picolm/picolm.c:416-553): one sequence whose cache keeps growing;
+    every round prefills the base prompt behind what is cached, then generates `-n` tokens greedily, and
+    prints `ctx_size,prefill_tok/s,gen_tok/s` (the cached length before the round) to standard error."""
+    import time
+
+    from . import ops
+    from .api import model_load
+    engine = model_load(args.model, dtype=args.dtype, context=args.context or None, max_batch=1)
+    limit = engine.cache.max_seq_tokens
+    n_base, chunk = len(base), max(1, args.max_tokens)
+    print(f"Base prompt: {n_base} tokens", file=sys.stderr)
+    print("ctx_size,prefill_tok/s,gen_tok/s", file=sys.stderr)
+    slot = engine.new_sequence()
+    try:
+        while engine.length(slot) + n_base + chunk <= limit:
+            cached = engine.length(slot)
+            engine.synchronize()
+            t0 = time.perf_counter()
+            tok = ops.argmax(engine.step([(slot, base)]))
+            engine.synchronize()
+            t1 = time.perf_counter()
+            for _ in range(chunk):
+                tok = ops.argmax(engine.step_device_tokens([slot], tok), out=engine.token_buffer(1))
+            engine.synchronize()
+            t2 = time.perf_counter()
+            print(f"{cached},{n_base / (t1 - t0):.1f},{chunk / (t2 - t1):.1f}", file=sys.stderr)
+    finally:
+        engine.end_sequence(slot)
+    return 0
 
 
 def main(argv=None) -> int:
@@ -91,6 +127,9 @@ def main(argv=None) -> int:
     if not prompts:
         print("no prompt given (-p \"1,2,3\" or token ids on stdin)", file=sys.stderr)
         return 1
+
+    if args.benchmark_ctx:
+        return benchmark_context_scaling(args, prompts[0])
 
     from .api import generate, model_load
     engine = model_load(args.model, dtype=args.dtype, context=args.context or None,

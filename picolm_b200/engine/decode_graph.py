@@ -28,14 +28,19 @@ def bucket_for(n: int) -> Optional[int]:
     return None
 
 
-LENGTH_QUANTUM = 512          # sequence lengths are rounded up to this for the sizes a graph bakes in
+LENGTH_QUANTUM = 512          # sequence lengths are rounded up for the sizes a graph bakes in: to this ...
 
 
 def length_class(max_len: int, longest: int) -> int:
     """The length a graph is captured for: kernels that size their grids by the longest sequence
     (how many ranges the decode attention cuts the keys into) get this instead of the true length,
-    so that a graph serves all steps until the batch's longest sequence grows past it."""
-    return min(longest, (max_len + LENGTH_QUANTUM - 1) // LENGTH_QUANTUM * LENGTH_QUANTUM)
+    so that a graph serves all steps until the batch's longest sequence grows past it.  Steps of 512
+    up to 2,048, then of a quarter of the next power of two (1,024 up to 4,096, 2,048 up to 8,192, ...):
+    at most 25 % above the true length, and a few dozen classes for any context."""
+    q = LENGTH_QUANTUM
+    while q * 4 < max_len:
+        q *= 2
+    return min(longest, (max_len + q - 1) // q * q)
 
 
 class DecodeGraph:

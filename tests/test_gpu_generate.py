@@ -1,5 +1,6 @@
 """Greedy and sampled generation through the Python entry point and the command line."""
 import os
+import re
 import subprocess
 import sys
 
@@ -109,3 +110,11 @@ def test_command_line(model_dirs):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
                         "--list-tensors"], capture_output=True, text=True, timeout=60)
     assert "model.layers.1.mlp.down_proj.weight\t[64, 172]\tBF16" in r.stdout
+    # the reference's --benchmark-ctx: one CSV line per round, the cached length growing by prompt + -n
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
+                        "-p", "5,6,7,8,9,10", "-n", "10", "-c", "70", "--benchmark-ctx"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    rows = [ln.split(",") for ln in r.stderr.splitlines() if re.fullmatch(r"\d+,[0-9.]+,[0-9.]+", ln)]
+    assert "ctx_size,prefill_tok/s,gen_tok/s" in r.stderr
+    assert [int(x[0]) for x in rows] == [0, 16, 32, 48] and all(float(x[1]) > 0 and float(x[2]) > 0 for x in rows)
