@@ -33,7 +33,9 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     (M, K), (N, K2) = a.shape, w.shape
     if K != K2 or K < 64:
         return False
-    return bool(_fn("gemm_tc", "plm_gemm_tc_supported")(_p(a), _p(w), M, N, K, K, K))
+    # TMA's rule (the kernels check it again): rows start on 16-byte boundaries
+    return (M > 0 and N > 0 and K % 8 == 0 and a.is_contiguous() and w.is_contiguous()
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
