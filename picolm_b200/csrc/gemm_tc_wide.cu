@@ -16,6 +16,11 @@
 // epilogue.  Waits on mbarriers are bounded; a wait that runs out records where in `status`
 // and the CTA drains and leaves.
 //
+// K splits (single CTAs, store epilogue): where a problem has fewer tiles than SMs (prompts of a few
+// hundred tokens), every tile's K range is cut into `k_splits` parts that are units of work of their own;
+// each writes its fp32 partial tile to its own slice of a scratch buffer, and a second kernel adds the
+// slices up in order and converts.
+//
 // PAIR: two CTAs of a cluster (two SMs) work on one tile of 256 tokens x 256 features with
 // tcgen05.mma.cta_group::2.  Each CTA loads its 128 token rows and HALF of the weight tile (128
 // features), the tensor cores of both SMs read both halves, and each CTA's tensor memory receives
@@ -72,7 +77,7 @@ template <int BN, int EPI, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
-                    int* __restrict__ status) {
+                    int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride) {
     static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
     constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
@@ -91,7 +96,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (K + BK - 1) / BK;
-    const int n_tiles_total = m_tiles * n_tiles;                         // PAIR: tiles of 256 tokens
+    const int n_tiles_mn = m_tiles * n_tiles;                            // PAIR: tiles of 256 tokens
+    const int n_tiles_total = n_tiles_mn * k_splits;                     // units of work: (tile, part of K)
     const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
     const int first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x, tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
     constexpr int TILE_M = PAIR ? 2 * BM : BM;
@@ -125,9 +131,11 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             bool waited = false;
             int it = 0;                                                  // K blocks issued so far, over all tiles
             bool ok = true;
-            for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step) {
+            for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step) {
+                const int tile = unit % n_tiles_mn, ks = unit / n_tiles_mn;
+                const int kb_begin = ks * kb_per_split, kb_end = min(n_kb, kb_begin + kb_per_split);
                 const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN + (int)rank * W_ROWS;
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
                     if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; ok = false; break; }
@@ -157,12 +165,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             constexpr uint32_t idesc = PAIR ? instr_desc_bf16_pair(BN) : instr_desc_bf16(BN);
             int it = 0, j = 0;
             bool ok = true;
-            for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step, ++j) {
+            for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step, ++j) {
                 const int acc = j & 1;
+                const int ks = unit / n_tiles_mn;
+                const int kb_begin = ks * kb_per_split, kb_end = min(n_kb, kb_begin + kb_per_split);
                 // the epilogue must have read this accumulator's previous tile out
                 if (!mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, status, 2)) { s_abort = 1; ok = false; break; }
                 tc_fence_after();
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
                     if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 2)) { s_abort = 1; ok = false; break; }
@@ -173,10 +183,10 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         if (PAIR)
                             tc_mma_bf16_pair(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                         else
                             tc_mma_bf16(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     if (PAIR) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
@@ -190,8 +200,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         pdl_wait();                                                      // the output may still be in use by an earlier kernel
         int j = 0;
         bool ok = true;
-        for (int tile = first_tile; tile < n_tiles_total && ok; tile += tile_step, ++j) {
+        for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step, ++j) {
             const int acc = j & 1;
+            const int tile = unit % n_tiles_mn, ks = unit / n_tiles_mn;
             const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN;
             if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, status, 3)) { s_abort = 1; ok = false; break; }
             tc_fence_after();
@@ -230,8 +241,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     tc_ld32(tacc + c, r);
                     tc_wait_ld();
                     if (t < T) {
-                        OutT* rowp = out + (size_t)t * ldo + f0 + c;
-                        const bool vec = (f0 + c + 32 <= F) && ((((size_t)t * ldo + f0 + c) * sizeof(OutT)) % 16 == 0);
+                        OutT* rowp = out + (size_t)ks * split_stride + (size_t)t * ldo + f0 + c;
+                        const bool vec = (f0 + c + 32 <= F) && ((((size_t)ks * split_stride + (size_t)t * ldo + f0 + c) * sizeof(OutT)) % 16 == 0);
                         if (vec) {
 #pragma unroll
                             for (int i = 0; i < 32; i += 8) store_vec8<OutT>(rowp + i, r + i);
@@ -285,12 +296,12 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
-                                            out, T, F, K, ldo, m_tiles, n_tiles, status));
+                                            out, T, F, K, ldo, m_tiles, n_tiles, status, 1, (K + BK - 1) / BK, (size_t)0));
 }
 
 template <int BN, int EPI, typename OutT>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0) {
     static bool configured = false;
     constexpr size_t smem = wide_smem(BN);
     auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
@@ -300,19 +311,79 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
         configured = true;
     }
     const int m_tiles = (T + BM - 1) / BM, n_tiles = (F + BN - 1) / BN;
-    const int ctas = m_tiles * n_tiles < sm_count() ? m_tiles * n_tiles : sm_count();
+    const int units = m_tiles * n_tiles * k_splits;
+    const int ctas = units < sm_count() ? units : sm_count();
+    if (kb_per_split <= 0) kb_per_split = (K + BK - 1) / BK;
     return plm_status_of(launch_pdl(kern, dim3(ctas), dim3(NUM_THREADS), smem, stream, mx, mw, out, T, F, K, ldo, m_tiles,
-                                    n_tiles, status));
+                                    n_tiles, status, k_splits, kb_per_split, split_stride));
+}
+
+// out[i] = sum over the K splits of scratch[s * stride + i], in order; four at a time.
+template <typename OutT>
+__global__ void reduce_splits_kernel(const float* __restrict__ scratch, OutT* __restrict__ out, int k_splits, size_t n4,
+                                     size_t stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = *reinterpret_cast<const float4*>(scratch + 4 * i);
+        for (int s = 1; s < k_splits; ++s) {
+            const float4 b = *reinterpret_cast<const float4*>(scratch + (size_t)s * stride + 4 * i);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (sizeof(OutT) == 4) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + 4 * i) = a;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + 4 * i) = o;
+        }
+    }
+}
+
+// Tile width and K splits of the single-CTA form for (T, F, K); see plm_gemm_tc_wide.
+void wide_plan(int T, int F, int K, int* bn_out, int* k_splits_out, int* kb_per_out) {
+    int bn = 128;
+    const long m_tiles = (T + BM - 1) / BM, sms = sm_count();
+    if (F >= 2048 && T >= 256) {
+        const long wide = (m_tiles * ((F + 255) / 256) + sms - 1) / sms, narrow = (m_tiles * ((F + 127) / 128) + sms - 1) / sms;
+        bn = 0.8 * (double)narrow < (double)wide ? 128 : 256;
+    }
+    // K splits where the tiles leave at least half of the SMs without work and K is long enough to cut
+    const long tiles = m_tiles * ((F + bn - 1) / bn);
+    const int n_kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (tiles * 2 <= sms && F % 4 == 0) {
+        splits = (int)(sms / tiles);
+        if (splits > 8) splits = 8;
+        if (splits > n_kb / 4) splits = n_kb / 4;
+        if (splits < 1) splits = 1;
+    }
+    const int per = (n_kb + splits - 1) / splits;
+    *bn_out = bn;
+    *kb_per_out = per;
+    *k_splits_out = (n_kb + per - 1) / per;                                // no part of K is empty
 }
 
 }  // namespace
 
+// Into how many parts plm_gemm_tc_wide cuts K for (T, F, K) with the store epilogue: it needs that many
+// slices of T * F floats of scratch memory if the answer is more than 1.
+extern "C" int plm_gemm_tc_wide_splits(int T, int F, int K) {
+    int bn, splits, per;
+    wide_plan(T, F, K, &bn, &splits, &per);
+    return splits;
+}
+
 // out[T, F'] = epilogue(x[T, K] * w[F, K]^T), T > 64, bf16 operands that TMA can address (K and the
 // leading dimensions multiples of 8, pointers 16-byte aligned).  epilogue 0: F' = F, out float32
 // (out_dtype 0) or bfloat16 (1).  epilogue 1 (SwiGLU): w holds tiles of 64 gate rows followed by their
-// 64 up rows (F a multiple of 128), F' = F / 2, out bfloat16.
-extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
-                                int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+// 64 up rows (F a multiple of 128), F' = F / 2, out bfloat16.  `scratch`: plm_gemm_tc_wide_splits(T, F, K) slices
+// of T * F floats where that is more than 1 (else unused; without it K is not cut).
+extern "C" int plm_gemm_tc_wide_scratch(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                        int K, long ldx, long ldw, long ldo, float* scratch, int* status,
+                                        cudaStream_t stream) {
     if (T <= 0 || F <= 0) return PLM_OK;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
@@ -320,12 +391,8 @@ extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out
     // Tile width: 256 columns feed the tensor cores best (a 128-column tile takes 0.8 of a 256-column tile's
     // time for half the work), but the CTAs walk whole tiles: where the narrow tiles need no more rounds over
     // the SMs than the wide ones (prompts of a few hundred tokens), they finish earlier.
-    int bn = 128;
-    if (F >= 2048 && T >= 256) {
-        const long m_tiles = (T + BM - 1) / BM, sms = sm_count();
-        const long wide = (m_tiles * ((F + 255) / 256) + sms - 1) / sms, narrow = (m_tiles * ((F + 127) / 128) + sms - 1) / sms;
-        bn = 0.8 * (double)narrow < (double)wide ? 128 : 256;
-    }
+    int bn, k_splits, kb_per;
+    wide_plan(T, F, K, &bn, &k_splits, &kb_per);
     CUtensorMap mx, mw;
     int rc;
     if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
@@ -334,15 +401,33 @@ extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out
         if (bn == 256) return launch<256, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
         return launch<128, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     }
+    if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    if (k_splits > 1 && scratch && ldo == F && (((uintptr_t)scratch | (uintptr_t)out) & 15) == 0) {
+        // the parts of K as units of work of their own, each into its slice of the scratch; then the sum
+        const size_t stride = (size_t)T * F;
+        rc = bn == 256 ? launch<256, EPI_STORE, float>(mx, mw, scratch, T, F, K, F, status, stream, k_splits, kb_per, stride)
+                       : launch<128, EPI_STORE, float>(mx, mw, scratch, T, F, K, F, status, stream, k_splits, kb_per, stride);
+        if (rc != PLM_OK) return rc;
+        const size_t n4 = stride / 4;
+        const int blocks = (int)((n4 + 255) / 256 < (size_t)(8 * sm_count()) ? (n4 + 255) / 256 : (size_t)(8 * sm_count()));
+        if (out_dtype == PLM_F32)
+            return plm_status_of(launch_pdl(reduce_splits_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                                            (const float*)scratch, (float*)out, k_splits, n4, stride));
+        return plm_status_of(launch_pdl(reduce_splits_kernel<bf16>, dim3(blocks), dim3(256), 0, stream,
+                                        (const float*)scratch, (bf16*)out, k_splits, n4, stride));
+    }
     if (out_dtype == PLM_F32) {
         if (bn == 256) return launch<256, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
         return launch<128, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
     }
-    if (out_dtype == PLM_BF16) {
-        if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
-        return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
-    }
-    return PLM_ERR_DTYPE;
+    if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+    return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+}
+
+// The same without scratch memory (K is never cut).
+extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+    return plm_gemm_tc_wide_scratch(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, status, stream);
 }
 
 // The same product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 tokens x 256 features; see

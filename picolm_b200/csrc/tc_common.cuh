@@ -4,6 +4,7 @@
 #pragma once
 #include "common.cuh"
 #include <cuda.h>
+#include <mutex>
 
 namespace plm_tc {
 
@@ -132,7 +133,22 @@ static inline EncodeTiledFn encode_fn() {
 }
 
 // A [rows, K] bf16 row-major matrix with leading dimension ld (elements); boxes of box_rows x 64.
+// Descriptors are kept in a small table by what they describe (a descriptor depends on nothing else, and
+// encoding one costs a few microseconds of host time per operand and launch).
 static inline int make_map(CUtensorMap* map, const void* ptr, long rows, long K, long ld, int box_rows) {
+    struct Entry { const void* ptr; long rows, K, ld; int box_rows; bool used; CUtensorMap map; };
+    constexpr int SLOTS = 512;
+    static Entry table[SLOTS];
+    static std::mutex lock;
+    const size_t h = ((size_t)ptr >> 4) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)K * 131 + (size_t)box_rows;
+    Entry& e = table[(h >> 20) % SLOTS];
+    {
+        std::lock_guard<std::mutex> g(lock);
+        if (e.used && e.ptr == ptr && e.rows == rows && e.K == K && e.ld == ld && e.box_rows == box_rows) {
+            *map = e.map;
+            return PLM_OK;
+        }
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return PLM_ERR_UNSUPPORTED;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -142,7 +158,10 @@ static inline int make_map(CUtensorMap* map, const void* ptr, long rows, long K,
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? PLM_OK : PLM_ERR_ALIGN;
+    if (r != CUDA_SUCCESS) return PLM_ERR_ALIGN;
+    std::lock_guard<std::mutex> g(lock);
+    e.ptr = ptr; e.rows = rows; e.K = K; e.ld = ld; e.box_rows = box_rows; e.map = *map; e.used = true;
+    return PLM_OK;
 }
 
 

@@ -114,7 +114,8 @@ class DecodeGraph:
         # replay is to read: it is left as it is; whatever valid ids it holds serve the warm-up run)
         self._fill([], [], [], device_tokens=self.d[0])
         # once outside the capture: first-call set-up of every kernel, allocator warm-up
-        eng.model.forward(self.step, eng.cache)
+        with ops.stream_scope():
+            eng.model.forward(self.step, eng.cache)
         torch.cuda.synchronize()
         n0 = ops.launch_count()
         self.graph = torch.cuda.CUDAGraph()
@@ -126,7 +127,7 @@ class DecodeGraph:
         was_enabled = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(self.graph):
+            with torch.cuda.graph(self.graph), ops.stream_scope():     # the capture has a stream of its own
                 self.logits = eng.model.forward(self.step, eng.cache)
         finally:
             if was_enabled:

@@ -167,7 +167,9 @@ class Engine:
             self.counters["h2d_bytes"] += batch.h2d_bytes
             if device_tokens is not None:
                 batch.tok_ids.copy_(device_tokens)
-            logits = self.model.forward(batch, self.cache)
+            from .. import ops
+            with ops.stream_scope():
+                logits = self.model.forward(batch, self.cache)
         self.counters["steps"] += 1
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))

@@ -26,6 +26,8 @@ _SIGNATURES = {
     "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _i, _f, _vp, _vp],
     "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
+    "plm_gemm_tc_wide_scratch": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
+    "plm_gemm_tc_wide_splits": [_i, _i, _i],
     "plm_gemm_tc_pair": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
     "plm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
@@ -105,8 +107,30 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_bound_stream = None
+
+
 def _stream():
+    if _bound_stream is not None:
+        return _bound_stream
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Within this scope every kernel goes to the stream that is current at its entry: asking torch for the
+    current stream costs a few microseconds, and a step launches a hundred kernels.  Whoever changes the
+    current stream inside (a CUDA graph capture does) opens a scope of its own there."""
+
+    def __enter__(self):
+        global _bound_stream
+        self.outer = _bound_stream
+        _bound_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _bound_stream
+        _bound_stream = self.outer
+        return False
 
 
 def _dt(t: torch.Tensor, name: str) -> int:

@@ -193,6 +193,15 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
     n_out = N // 2 if swiglu else N
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    if not pair and not swiglu:
+        # few tiles (a prompt of a few hundred tokens): K is cut into parts that pass through scratch memory
+        k_splits = _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(M, N, K)
+        if k_splits > 1:
+            scratch = torch.empty((k_splits, M, N), dtype=torch.float32, device=a.device)
+            _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_scratch")(
+                _p(a), _p(w), _p(out), _dt(out, "out"), 0, M, N, K, K, K, n_out, _p(scratch),
+                _p(status_word(a.device)), _stream()), "gemm_tc_wide", kernels=2)
+            return out
     _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair" if pair else "plm_gemm_tc_wide")(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
         _p(status_word(a.device)), _stream()), "gemm_tc_pair" if pair else "gemm_tc_wide")

@@ -324,9 +324,37 @@ def test_gemm_tc_pair(out_dtype, M, N, K, swiglu):
         assert torch.allclose(got.double().cpu(), ref, atol=2e-3, rtol=1e-4)
     else:
         assert torch.allclose(got.double().cpu(), ref, atol=3e-2, rtol=2e-2)
-    # the single-CTA kernel accumulates in the same order: the same bits
+    # the single-CTA kernel accumulates in the same order: the same bits (unless it cuts K into parts,
+    # which it does where the tiles are few)
     if not swiglu:
-        assert torch.equal(got, ops.gemm_tc_wide(a.to(DEV), w.to(DEV), DT[out_dtype]))
+        single = ops.gemm_tc_wide(a.to(DEV), w.to(DEV), DT[out_dtype])
+        if (M, N, K) == (1000, 1152, 2048):
+            assert torch.allclose(got.double(), single.double(), atol=2e-3 if out_dtype == "float32" else 3e-2, rtol=1e-2)
+        else:
+            assert torch.equal(got, single)
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(100, 2048, 2048), (300, 2048, 8192), (256, 3072, 2048), (65, 2052, 520)])
+def test_gemm_tc_wide_with_k_in_parts(out_dtype, M, N, K):
+    """Prompts of a few hundred tokens: few tiles, so the prompt-shaped product cuts K into parts that pass
+    through scratch memory and a second kernel; against float64, and the same bits on a second call."""
+    from picolm_b200 import ops
+    from picolm_b200.ops._lib import _fn
+    assert _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(M, N, K) > 1
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    ref = a.double() @ w.double().t()
+    got = ops.linear(a.to(DEV), w.to(DEV), DT[out_dtype])
+    ops.check_status(DEV)
+    if out_dtype == "float32":
+        assert torch.allclose(got.double().cpu(), ref, atol=2e-3, rtol=1e-4)
+    else:
+        assert torch.allclose(got.double().cpu(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.equal(got, ops.linear(a.to(DEV), w.to(DEV), DT[out_dtype]))
 
 
 @pytest.mark.parametrize("window", [None, 90])
