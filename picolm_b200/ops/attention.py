@@ -103,24 +103,27 @@ def decode_ctas_per_sm(head_dim: int, heads_per_kv_head: int) -> int:
 
 
 def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 64) -> int:
-    """Into how many ranges the decode kernel cuts each sequence's keys.  Where the whole grid runs at once
-    (up to three CTAs an SM), as many ranges as that allows, up to the eight that merge inside a
-    cluster, each of at least two pages.  Otherwise, and for long contexts (whose ranges would get too long
-    for one wave of CTAs), about eight pages a range, more when that leaves SMs without a CTA (measured at
-    batch 1, 8, 16 and 64 with 2,048 keys)."""
+    """Into how many ranges the decode kernel cuts each sequence's keys.  Short contexts, where the whole
+    grid runs at once (up to three CTAs an SM): as many ranges as that allows, up to the eight that merge
+    inside a cluster, each of at least two and at most sixteen pages.  Longer contexts: as many ranges as
+    make one wave of CTAs at full occupancy, each of at least eight pages (few long ranges read at 0.9 of the
+    copy bandwidth where many short ones reach 0.7: every range pays for its start and its partial result);
+    grids that fill the SMs without cutting get ranges of 32 pages (measured at batch 1, 8, 16 and 64 with
+    2,048 to 32,768 keys)."""
     row_groups = (num_heads // num_kv_heads + 15) // 16
     ctas = max(1, n_tokens * num_kv_heads * row_groups)
     pages = max(1, (max_kv_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
-    # (at most three CTAs an SM are counted on: a grid that fills the SMs to the brim keeps the next kernel's
-    # CTAs, which would already be asking for their weights, off them; measured at batch 8)
-    wave = min(3, decode_ctas_per_sm(head_dim, num_heads // num_kv_heads)) * SM_COUNT
+    per_sm = decode_ctas_per_sm(head_dim, num_heads // num_kv_heads)
+    # (at most three CTAs an SM are counted on for the cluster form: a grid that fills the SMs to the brim keeps
+    # the next kernel's CTAs, which would already be asking for their weights, off them; measured at batch 8)
+    wave = min(3, per_sm) * SM_COUNT
     in_cluster = min(DECODE_CLUSTER_SPLITS, wave // ctas, max(1, pages // 2))
     if in_cluster >= 2 and pages <= (16 if ctas * in_cluster >= SM_COUNT else 8) * in_cluster:
         return in_cluster
-    splits = (pages + 7) // 8
-    if ctas * splits < SM_COUNT:
-        splits = max(splits, min(max(1, pages // 2), (SM_COUNT + ctas - 1) // ctas))
-    return max(1, min(pages, splits))
+    in_wave = per_sm * SM_COUNT // ctas
+    if in_wave >= 2:
+        return max(1, min(pages, in_wave, max(2, pages // 8)))
+    return max(1, (pages + 31) // 32)
 
 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,

@@ -91,7 +91,9 @@ def run_case(harness, work, case, cfg, seed, tokens, rope_type, inject_table):
 
 def main():
     from util import TINY, random_tokens
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/picolm"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <the reference's source folder (the one with model_core.c)>")
+    ref_src = sys.argv[1]
     with tempfile.TemporaryDirectory() as work:
         harness = build_harness(ref_src, work)
         a, b = TINY["A"], TINY["B"]
