@@ -40,6 +40,7 @@ _SIGNATURES = {
     "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
+    "plm_mma_rate": [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
 }
 _fn_cache = {}
 

@@ -108,7 +108,7 @@ def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: 
     inside a cluster, each of at least two and at most sixteen pages.  Longer contexts: as many ranges as
     make one wave of CTAs at full occupancy, each of at least eight pages (few long ranges read at 0.9 of the
     copy bandwidth where many short ones reach 0.7: every range pays for its start and its partial result);
-    grids that fill the SMs without cutting get ranges of 32 pages (measured at batch 1, 8, 16 and 64 with
+    grids that fill the SMs without cutting get ranges of up to 64 pages (measured at batch 1, 8, 16 and 64 with
     2,048 to 32,768 keys)."""
     row_groups = (num_heads // num_kv_heads + 15) // 16
     ctas = max(1, n_tokens * num_kv_heads * row_groups)
@@ -123,7 +123,7 @@ def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: 
     in_wave = per_sm * SM_COUNT // ctas
     if in_wave >= 2:
         return max(1, min(pages, in_wave, max(2, pages // 8)))
-    return max(1, (pages + 31) // 32)
+    return max(1, (pages + 63) // 64)
 
 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
