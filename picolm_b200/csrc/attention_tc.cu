@@ -11,9 +11,13 @@
 //                  TMEM across pages; O is rescaled only when a row's maximum has outgrown the
 //                  reference it is kept against by a factor of 256
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
-// 128 softmax threads.  With head size 64 the scores have two TMEM buffers, so the next page's
-// Q K^T runs while this page's softmax does.  Keys of a KV head are shared by its query heads
-// through L2 (consecutive CTAs work on the heads of one group).
+// 128 softmax threads.  The scores have NSB buffers in TMEM (two with head size 64, one with 128).
+// As soon as all 128 threads have handed over P(i), and with that have read S(i), the issuing
+// thread puts Q K(i + NSB)^T into the freed buffer and only then P(i) V(i), so the scores of the
+// pages ahead are there when the softmax threads get to them.  The softmax warps may drift up to a
+// page apart (never two: page i + 2 needs what follows everybody's arrival for page i), so even and
+// odd pages count their arrivals on barriers of their own.  Keys of a KV head are shared by its
+// query heads through L2 (consecutive CTAs work on the heads of one group).
 //
 // Waits on mbarriers are bounded as in gemm_tc.cu: a wait that runs out records where in
 // `status`, the CTA stops issuing work, lets what is in flight land, frees its TMEM and returns.
@@ -31,13 +35,14 @@ constexpr int HD = PLM_HD;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention is built for head sizes 64 and 128");
 constexpr int CB = HD / 64;                       // 64-column blocks of a row (one 128-byte swizzle span each)
 constexpr int BQ = 128, BKV = 64;
-constexpr int STAGES = HD == 64 ? 3 : 2;
+constexpr int STAGES = HD == 64 ? 4 : 2;
 constexpr int NSB = HD == 64 ? 2 : 1;             // score buffers in TMEM
 constexpr uint32_t Q_BLOCK = BQ * 128, KV_BLOCK = BKV * 128;       // bytes of one 64-column block
 constexpr uint32_t Q_BYTES = CB * Q_BLOCK, K_BYTES = CB * KV_BLOCK, V_BYTES = K_BYTES;
 constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = TM_P + 2 * 32, TMEM_COLS = 256;      // two P buffers
 static_assert(TM_PV + HD <= TMEM_COLS, "TMEM budget");
+static_assert(STAGES > NSB, "the scores of page i + NSB are issued while page i still holds its stage");
 constexpr size_t SMEM = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -63,6 +68,34 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two fp32 lanes per instruction (fma.rn.f32x2 and add.rn.f32x2 round each lane as the scalar forms do) and
+// the three-input maximum: the softmax threads are bound by how many instructions a key costs them.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -114,7 +147,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
     const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * STAGES,
-                   s_full0 = kv_empty0 + 8 * STAGES, p_ready = s_full0 + 8 * NSB, pv_full0 = p_ready + 8;   // pv_full[2]
+                   s_full0 = kv_empty0 + 8 * STAGES, p_ready0 = s_full0 + 8 * NSB, pv_full0 = p_ready0 + 16;   // p_ready[2], pv_full[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (pv_full0 + 16 - raw));
     __shared__ int s_abort;
 
@@ -145,7 +178,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_init(q_full, 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int s = 0; s < NSB; ++s) mbar_init(s_full0 + 8 * s, 1);
-        mbar_init(p_ready, 128);
+        mbar_init(p_ready0, 128);
+        mbar_init(p_ready0 + 8, 128);
         mbar_init(pv_full0, 1);
         mbar_init(pv_full0 + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -206,20 +240,22 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_commit(s_full0 + 8 * (i % NSB));
             };
             bool ok = mbar_wait(q_full, 0, status, 2);
-            if (ok && NSB == 2) {
-                ok = mbar_wait(kv_full0, 0, status, 2);
-                if (ok) { tc_fence_after(); qk(0); }
+            for (int j = 0; j < NSB && j < n_pages && ok; ++j) {         // fill the score buffers
+                ok = mbar_wait(kv_full0 + 8 * (j % STAGES), (j / STAGES) & 1, status, 2);
+                if (ok) { tc_fence_after(); qk(j); }
             }
             for (int i = 0; i < n_pages && ok; ++i) {
                 if (*(volatile int*)&s_abort) { ok = false; break; }
-                const int nxt = NSB == 2 ? i + 1 : i;                    // the Q K^T to issue now
-                if (nxt < n_pages && (NSB == 1 || nxt > 0)) {
+                if (!mbar_spin(p_ready0 + 8 * (i & 1), (i >> 1) & 1, status, 2)) { ok = false; break; }
+                tc_fence_after();
+                // The softmax threads have read S(i): its buffer takes the scores of page i + NSB at once, before
+                // P(i) V(i) is issued, so that they are there when the softmax of the page in between is done.
+                const int nxt = i + NSB;
+                if (nxt < n_pages) {
                     if (!mbar_wait(kv_full0 + 8 * (nxt % STAGES), (nxt / STAGES) & 1, status, 2)) { ok = false; break; }
                     tc_fence_after();
                     qk(nxt);
                 }
-                if (!mbar_spin(p_ready, i & 1, status, 2)) { ok = false; break; }
-                tc_fence_after();
                 const uint32_t v_smem = kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES;
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k)                       // O_page = P V(i), 16 keys a step
@@ -264,8 +300,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int j = 0; j < 32; ++j) { s0[j] = 0xff800000u; s1[j] = 0xff800000u; }
             }
+            float mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;           // four chains instead of one of 32 links
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[j]), __uint_as_float(s1[j])));
+            for (int j = 0; j < 32; j += 4) {
+                mx = max3(mx, __uint_as_float(s0[j]), __uint_as_float(s1[j]));
+                mx1 = max3(mx1, __uint_as_float(s0[j + 1]), __uint_as_float(s1[j + 1]));
+                mx2 = max3(mx2, __uint_as_float(s0[j + 2]), __uint_as_float(s1[j + 2]));
+                mx3 = max3(mx3, __uint_as_float(s0[j + 3]), __uint_as_float(s1[j + 3]));
+            }
+            mx = fmaxf(fmaxf(mx, mx1), fmaxf(mx2, mx3));
             // the scale is positive, so the maximum of the scaled scores is the scaled maximum
             const float m_cand = fmaxf(m_ref, mx * scale_log2);
             const bool raise = m_cand > m_ref + RESCALE_LOG2 || (m_ref == -INFINITY && m_cand > -INFINITY);
@@ -290,19 +333,25 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (raise) { l *= alpha; m_ref = m_cand; }
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
             uint32_t p[32];
+            const uint64_t scale2 = pack2(__float_as_uint(scale_log2), __float_as_uint(scale_log2));
+            const uint64_t neg_m2 = pack2(__float_as_uint(-m_use), __float_as_uint(-m_use));
+            uint64_t sum2 = 0;                                           // two partial sums, (0.f, 0.f)
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {                              // p = 2^(s * scale - m_ref): one FFMA and one EX2 each
-                const float a0 = ex2(fmaf(__uint_as_float(s0[2 * j]), scale_log2, -m_use));
-                const float a1 = ex2(fmaf(__uint_as_float(s0[2 * j + 1]), scale_log2, -m_use));
-                const float c0 = ex2(fmaf(__uint_as_float(s1[2 * j]), scale_log2, -m_use));
-                const float c1 = ex2(fmaf(__uint_as_float(s1[2 * j + 1]), scale_log2, -m_use));
-                sum += (a0 + a1) + (c0 + c1);
+            for (int j = 0; j < 16; ++j) {                              // p = 2^(s * scale - m_ref): half an FFMA2 and one EX2 each
+                float xa0, xa1, xc0, xc1;
+                unpack2(fma2(pack2(s0[2 * j], s0[2 * j + 1]), scale2, neg_m2), xa0, xa1);
+                unpack2(fma2(pack2(s1[2 * j], s1[2 * j + 1]), scale2, neg_m2), xc0, xc1);
+                const float a0 = ex2(xa0), a1 = ex2(xa1), c0 = ex2(xc0), c1 = ex2(xc1);
+                sum2 = add2(sum2, add2(pack2(__float_as_uint(a0), __float_as_uint(a1)),
+                                       pack2(__float_as_uint(c0), __float_as_uint(c1))));
                 __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pc = __floats2bfloat162_rn(c0, c1);
                 p[j] = *reinterpret_cast<uint32_t*>(&pa);               // keys 2j, 2j+1
                 p[16 + j] = *reinterpret_cast<uint32_t*>(&pc);          // keys 32+2j, 32+2j+1
             }
+            float sum_lo, sum_hi;
+            unpack2(sum2, sum_lo, sum_hi);
+            const float sum = sum_lo + sum_hi;
             l += sum;
             tc_st32(tmem + lane_bits + TM_P + (i & 1) * 32, p);
             tc_wait_st();
@@ -319,7 +368,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tc_fence_before();
-            mbar_arrive(p_ready);
+            // Even and odd pages count their arrivals on barriers of their own: a warp may be a page ahead of
+            // another (never two: page i + 2 needs P V(i), which needs everybody's arrival for page i), and its
+            // arrival must not be counted among those of the page before.
+            mbar_arrive(p_ready0 + 8 * (i & 1));
         }
         if (ok && !mbar_spin(pv_full0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, status, 3)) ok = false;
         tc_fence_after();

@@ -640,6 +640,35 @@ def test_attention_prefill_tcgen05(H, G, hd, window):
             assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
 
 
+def test_attention_prefill_tcgen05_with_one_slow_warp():
+    """A long prompt in which the first 32 rows of every query tile meet a larger score on every page (their
+    running maximum rises by more than the kernel's lazy rescaling tolerates, so their warp rescales the
+    output page after page and waits for the tensor cores each time) while the other rows never rescale:
+    the softmax warps of a CTA drift apart, and a page must still get exactly its own 128 rows (the kernel
+    lets nobody arrive for a page before the page in front has all its arrivals; the long sequence of
+    test_gpu_real_widths.py is the case that showed the fault when that was missing)."""
+    from picolm_b200 import ops
+    H, G, hd, n = 4, 1, 64, 2900
+    torch.manual_seed(5)
+    u = torch.randn(hd)
+    u /= u.norm()
+    k = torch.randn(n, G, hd) * 0.3 + u * (torch.arange(n) // PAGE).float()[:, None, None]
+    v = torch.randn(n, G, hd)
+    q = torch.randn(n, H, hd) * 0.5
+    hot = (torch.arange(n) % 128) < 32
+    q[hot] = u * 64.0 + torch.randn(int(hot.sum()), H, hd) * 0.5          # 8 nats more per page at scale 1/8
+    ks, vs, qs = [k.to(torch.bfloat16).float()], [v.to(torch.bfloat16).float()], [q.to(torch.bfloat16).float()]
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attn_ref(ks, vs, qs, [n], [n], H, hd, scale)
+    kc, vc, table = _paged(ks, vs, [n], 50, torch.bfloat16, 3)
+    args = (qs[0].to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([0, n], dtype=torch.int32, device=DEV),
+            torch.tensor([n], dtype=torch.int32, device=DEV), table.to(DEV), n, G, scale)
+    for _ in range(3):
+        out = ops.attention_prefill_tc(*args)
+        ops.check_status(DEV)
+        assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(65, 128, 64), (128, 128, 128), (200, 136, 328), (300, 2048, 192),
                                    (256, 4096, 512), (1000, 264, 2048), (2048, 2560, 256), (5000, 2048, 64)])
