@@ -92,7 +92,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -128,7 +128,8 @@ def reference_arm():
     which exist here."""
     print(json.dumps({"impl": "reference",
                       "unavailable": "whoreson/picolm has no setup.py/pyproject.toml: `pip install --no-index "
-                                     "--target baseline/_ref /root/reference` fails (not a Python project)"}))
+                                     "--target baseline/_ref <its checkout>` fails (not a Python project), and its "
+                                     "command line needs GGUF files and a tokenizer that do not exist offline"}))
     return 0
 
 
@@ -143,7 +144,7 @@ def prefill_flops(cfg, T):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)

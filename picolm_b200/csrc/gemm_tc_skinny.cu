@@ -32,7 +32,7 @@ constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2;
 // ring depth: with the buffer that receives the partial sums (bn x 128 floats), two CTAs of any tile
 // width fit one SM (2 x ~105 KB)
 __host__ __device__ constexpr int stages_of(int bn) { return bn <= 16 ? 5 : (bn <= 32 ? 4 : 3); }
-constexpr int MAX_SPLITS = 8;               // portable cluster size
+constexpr int MAX_SPLITS = 8;               // portable cluster size (clusters of 16 were measured: much slower)
 
 __device__ __forceinline__ void st_cluster(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
@@ -73,6 +73,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                                                                          // [BN][rows of this CTA's slice]
     __shared__ int s_abort;
     __shared__ float s_scale[BN];
+    __shared__ float s_part[8 * 64];                                   // SCALE: eight partial sums a token
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -162,12 +163,22 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         cluster_wait();
         if (SCALE) {                                       // while the main loop runs: the rows' scale factors
             pdl_wait();
-            const int t = threadIdx.x - 64;
-            if (t < BN) {
+            // The 128 threads share the partial sums: thread (group, j) adds every eighth part of the tokens
+            // j, j + 16, ...; then one thread a token adds the eight groups' sums in order.  The order of the
+            // additions does not depend on the tile width, so neither does the result.
+            const int idx = threadIdx.x - 64, grp = idx >> 4, j = idx & 15;
+            for (int t = j; t < BN; t += 16) {
                 float ss = 0.f;
                 if (t < T)
-                    for (int p = 0; p < fz.n_parts; ++p) ss += fz.scale_parts[(size_t)p * fz.ld_parts + t];
-                s_scale[t] = 1.0f / sqrtf(ss * fz.inv_size + fz.eps);
+                    for (int p = grp; p < fz.n_parts; p += 8) ss += fz.scale_parts[(size_t)p * fz.ld_parts + t];
+                s_part[grp * 64 + t] = ss;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");             // the four warps of this branch
+            if (idx < BN) {
+                float ss = 0.f;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) ss += s_part[g * 64 + idx];
+                s_scale[idx] = 1.0f / sqrtf(ss * fz.inv_size + fz.eps);
             }
         }
         // send this CTA's partial tile, row by row, to the CTAs that own the rows

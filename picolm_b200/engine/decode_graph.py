@@ -78,6 +78,7 @@ class DecodeGraph:
             block_tables=[self.d[7 + g].view(B, P) for g in range(n_groups)],
             seq_slot_long=None, h2d_bytes=int(self.host_np.nbytes))
         self.copied = torch.cuda.Event()                  # the last metadata copy has left the pinned buffer
+        self.replayed: Optional[torch.cuda.Event] = None  # the last run of the step has read the metadata
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
@@ -99,13 +100,26 @@ class DecodeGraph:
         for g, table in enumerate(self.tables_h):
             table[:n] = cache.block_table_rows(g, slots)
             table[n:] = 0                                 # the null page
-        self.dev.copy_(self.host, non_blocking=True)
+        # The copy runs on a stream of its own, as soon as the last replay has read the buffers it overwrites:
+        # beside the sampling and the copy of the ids that follow that replay, not behind them.
+        cur = torch.cuda.current_stream(self.dev.device)
+        side = self.engine.side_stream("h2d")
+        if self.replayed is not None:
+            side.wait_event(self.replayed)
+        with torch.cuda.stream(side):
+            self.dev.copy_(self.host, non_blocking=True)
+            self.copied.record(side)
+        cur.wait_event(self.copied)
         if device_tokens is None:
             self.d[0].copy_(self.dev[:B])
         elif device_tokens.data_ptr() != self.d[0].data_ptr():
             # the token ids are on the device already; rows of padding keep whatever valid id they held
             self.d[0][:n].copy_(device_tokens)
-        self.copied.record()
+
+    def _mark_replayed(self) -> None:
+        if self.replayed is None:
+            self.replayed = torch.cuda.Event()
+        self.replayed.record(torch.cuda.current_stream(self.dev.device))
 
     def capture(self) -> None:
         from .. import ops
@@ -116,6 +130,7 @@ class DecodeGraph:
         # once outside the capture: first-call set-up of every kernel, allocator warm-up
         with ops.stream_scope():
             eng.model.forward(self.step, eng.cache)
+        self._mark_replayed()
         torch.cuda.synchronize()
         n0 = ops.launch_count()
         self.graph = torch.cuda.CUDAGraph()
@@ -143,5 +158,6 @@ class DecodeGraph:
         from .. import ops
         self._fill(slots, tokens, positions, device_tokens)
         self.graph.replay()
+        self._mark_replayed()
         ops.count_launches(self.launches)
         return self.logits[:len(slots)]

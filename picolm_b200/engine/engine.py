@@ -85,11 +85,33 @@ class Engine:
         e.record()
         return e
 
-    def fetch_later(self, tokens: torch.Tensor, pinned_row: torch.Tensor) -> None:
-        """Start copying sampled token ids into a row of pinned host memory without waiting for them;
-        `synchronize()` (or an event) says when they are there."""
-        pinned_row.copy_(tokens, non_blocking=True)
+    def side_stream(self, name: str) -> torch.cuda.Stream:
+        """One of the engine's streams beside the one that runs the steps: "h2d" carries a captured step's
+        metadata to the device, "d2h" carries sampled ids to the host, so that neither copy stands between two
+        steps on the stream that computes."""
+        streams = self.__dict__.setdefault("_side_streams", {})
+        if name not in streams:
+            streams[name] = torch.cuda.Stream(self.runtime.device)
+        return streams[name]
+
+    def fetch_later(self, tokens: torch.Tensor, pinned_row: torch.Tensor) -> torch.cuda.Event:
+        """Start copying sampled token ids into a row of pinned host memory without waiting for them.  The copy
+        runs on a stream of its own once the ids are there; the event that is returned says when they have
+        reached the host.  Whatever is launched after the engine's next step waits for the copy (a sampler may
+        then write the same buffer again); the step itself does not."""
+        cur = torch.cuda.current_stream(self.runtime.device)
+        side = self.side_stream("d2h")
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            pinned_row.copy_(tokens, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(side)
+        tokens.record_stream(side)
+        self._fetched = done
         self.counters["d2h_bytes"] += tokens.numel() * tokens.element_size()
+        return done
 
     # ----------------------------------------------------------- construction
     @staticmethod
@@ -170,6 +192,9 @@ class Engine:
             from .. import ops
             with ops.stream_scope():
                 logits = self.model.forward(batch, self.cache)
+        fetched = self.__dict__.pop("_fetched", None)
+        if fetched is not None:                              # what follows this step may write the ids' buffer
+            torch.cuda.current_stream(self.runtime.device).wait_event(fetched)
         self.counters["steps"] += 1
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))

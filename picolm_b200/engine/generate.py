@@ -140,8 +140,10 @@ def _decode_ahead(engine, sampler, batch, slots, live, first_tokens, stop, on_to
             logits = engine.step_device_tokens(cur_slots, tok_dev)
             tok_dev = sampler.sample(logits, out=buffer(len(cur))) if buffer else sampler.sample(logits)
             row = pinned[step_no % (depth + 1), :len(cur)]
-            engine.fetch_later(tok_dev, row)
-            inflight.append((list(cur), row, [engine.length(s) + 1 for s in cur_slots], mark() if mark else None))
+            fetched = engine.fetch_later(tok_dev, row)          # an event, if the engine has one for the copy
+            if fetched is None and mark:
+                fetched = mark()
+            inflight.append((list(cur), row, [engine.length(s) + 1 for s in cur_slots], fetched))
             for i in cur:
                 launched[i] += 1
             stats.steps += 1
