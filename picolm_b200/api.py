@@ -7,10 +7,10 @@ of token ids on the host: the reference's tokenizer is not part of this library.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 from .engine.engine import Engine
-from .engine.generate import GenerationStats, generate as _generate
+from .engine.generate import generate as _generate
 from .sampling import SamplingParams
 
 

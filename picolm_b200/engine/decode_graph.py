@@ -11,7 +11,7 @@ sequence sees, and their logits are dropped.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

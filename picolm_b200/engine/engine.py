@@ -11,18 +11,17 @@ of it: `model_forward(token, pos)` (picolm/model_core.c:1682) and
 """
 from __future__ import annotations
 
-import os
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
 from .. import architectures  # noqa: F401  (registers the known architectures)
-from ..cache import CacheFull, SequenceCache
+from ..cache import SequenceCache
 from ..config.registry import read_config, spec_of
 from ..runtime import Runtime
 from ..weights.loader import load_weights
 from .model import Model
-from .step_batch import StepBatch, build_step_batch
+from .step_batch import build_step_batch
 
 
 class Engine:
@@ -51,6 +50,8 @@ class Engine:
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
         self._tokens = torch.zeros(256, dtype=torch.int32, device=self.runtime.device)
+        self._side_streams: Dict[str, torch.cuda.Stream] = {}
+        self._fetched: Optional[torch.cuda.Event] = None      # the last copy of sampled ids to the host
         self.reset_counters()
 
     def token_buffer(self, n: int) -> torch.Tensor:
@@ -89,10 +90,9 @@ class Engine:
         """One of the engine's streams beside the one that runs the steps: "h2d" carries a captured step's
         metadata to the device, "d2h" carries sampled ids to the host, so that neither copy stands between two
         steps on the stream that computes."""
-        streams = self.__dict__.setdefault("_side_streams", {})
-        if name not in streams:
-            streams[name] = torch.cuda.Stream(self.runtime.device)
-        return streams[name]
+        if name not in self._side_streams:
+            self._side_streams[name] = torch.cuda.Stream(self.runtime.device)
+        return self._side_streams[name]
 
     def fetch_later(self, tokens: torch.Tensor, pinned_row: torch.Tensor) -> torch.cuda.Event:
         """Start copying sampled token ids into a row of pinned host memory without waiting for them.  The copy
@@ -192,9 +192,9 @@ class Engine:
             from .. import ops
             with ops.stream_scope():
                 logits = self.model.forward(batch, self.cache)
-        fetched = self.__dict__.pop("_fetched", None)
-        if fetched is not None:                              # what follows this step may write the ids' buffer
-            torch.cuda.current_stream(self.runtime.device).wait_event(fetched)
+        if self._fetched is not None:                        # what follows this step may write the ids' buffer
+            torch.cuda.current_stream(self.runtime.device).wait_event(self._fetched)
+            self._fetched = None
         self.counters["steps"] += 1
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))

@@ -4,7 +4,7 @@ rows' logits are wanted.  Built on the host, sent to the device in one copy.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import numpy as np

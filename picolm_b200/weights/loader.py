@@ -15,7 +15,7 @@ Two parts that name the same tensor (tied embeddings) get the same device buffer
 from __future__ import annotations
 
 import re
-from typing import Dict, List
+from typing import Dict
 
 import torch
 

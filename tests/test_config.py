@@ -3,7 +3,7 @@ import json
 
 import pytest
 
-from picolm_b200.config import (ConfigError, LlamaConfig, config_from_dict, read_config, registered_architectures,
+from picolm_b200.config import (ConfigError, config_from_dict, read_config, registered_architectures,
                                 spec_of)
 from util import TINY
 

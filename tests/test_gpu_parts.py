@@ -1,6 +1,5 @@
 """Each part of a layer alone, built from a PartSpec with sizes of its own and
 run against the plain implementation's function for that part."""
-import math
 
 import pytest
 import torch

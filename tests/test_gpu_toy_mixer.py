@@ -5,7 +5,6 @@ state) and lets every token see the mean so far; one layer of the toy model uses
 it, another uses the library's attention, the schedule runs that layer twice, and
 a last layer reads the attention layer's cache instead of owning one."""
 import dataclasses
-import json
 import os
 
 import pytest

@@ -6,7 +6,6 @@ float32 and in bfloat16, against the plain implementation."""
 import json
 import os
 import subprocess
-import sys
 
 import numpy as np
 import pytest
