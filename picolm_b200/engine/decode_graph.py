@@ -36,7 +36,7 @@ def length_class(max_len: int, longest: int) -> int:
     (how many ranges the decode attention cuts the keys into) get this instead of the true length,
     so that a graph serves all steps until the batch's longest sequence grows past it.  Steps of 512
     up to 2,048, then of a quarter of the next power of two (1,024 up to 4,096, 2,048 up to 8,192, ...):
-    at most 25 % above the true length, and a few dozen classes for any context."""
+    less than half the true length above it (beyond the first steps of 512), and a few dozen classes for any context."""
     q = LENGTH_QUANTUM
     while q * 4 < max_len:
         q *= 2

@@ -164,3 +164,21 @@ def test_steps_in_flight_give_the_same_output(most):
     assert fed <= sum(len(p) for p in prompts) + sum(len(o) + most - 1 for o in outs)
     eng.cache.check()
     assert eng.cache.slots.used == 0 and eng.cache.kv_groups[0].pool.used == 0
+
+
+def test_graph_size_and_length_classes():
+    """A captured decode step serves every batch up to its size class and every length up to its
+    length class: the classes must cover what they are asked for, never shrink, and stay few."""
+    from picolm_b200.engine.decode_graph import BUCKETS, bucket_for, length_class
+    assert [bucket_for(n) for n in (1, 2, 3, 8, 9, 64, 65, 256)] == [1, 2, 4, 8, 16, 64, 96, 256]
+    assert bucket_for(BUCKETS[-1] + 1) is None                     # beyond the largest class: no graph
+    longest = 1 << 17
+    classes, last = set(), 0
+    for n in range(1, longest + 1, 37):
+        c = length_class(n, longest)
+        assert n <= c <= longest and c >= last                      # covers the length, never shrinks
+        assert c - n < max(512, n // 2 + 1)                         # less than a step of 512, or than half the length, above it
+        classes.add(c)
+        last = c
+    assert len(classes) <= 40
+    assert length_class(100, 64) == 64                              # never beyond the longest sequence of the cache
