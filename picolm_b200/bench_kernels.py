@@ -69,7 +69,12 @@ def bench_gemm(args):
         nw = torch.ones(N, device="cuda", dtype=torch.bfloat16)
 
     def run(i):
-        if args.residual:
+        if args.library:                                     # the library's product of the same operands (bf16 out)
+            y = torch.matmul(a, ws[i].t())
+            if args.swiglu:                                  # rows in this kernel's order: tiles of 64 gate, 64 up rows
+                y = y.view(M, N // 128, 2, 64)
+                torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]
+        elif args.residual:
             ops.linear_residual_norm(ops.PendingLinear(a, ws[i]), x, nw, 1e-5)
         elif args.pair:
             ops.gemm_tc_wide(a, ws[i], out_dtype, swiglu=args.swiglu, pair=True)
@@ -82,7 +87,8 @@ def bench_gemm(args):
     ops.check_status()
     bytes_moved = w_bytes + M * K * 2 + M * N * (4 if out_dtype == torch.float32 else 2)
     flops = 2.0 * M * N * K
-    return {"kernel": "linear (tensor cores)", "m": M, "n": N, "k": K, "us": round(sec * 1e6, 2),
+    return {"kernel": "torch.matmul (library)" if args.library else "linear (tensor cores)", "m": M, "n": N, "k": K,
+            "us": round(sec * 1e6, 2),
             "GB/s": round(bytes_moved / sec / 1e9, 1), "TFLOP/s": round(flops / sec / 1e12, 2), "weight_copies": len(ws)}
 
 
@@ -125,13 +131,20 @@ def bench_attention_prefill(args):
     kvlen = torch.tensor([T], dtype=torch.int32, device="cuda")
 
     fn = ops.attention_prefill_tc if (ops.attention_tc_supported(q) and not args.mma) else ops.attention_prefill
+    if args.library:                                         # the library's causal attention on contiguous keys and values
+        ql = q.transpose(0, 1).unsqueeze(0).contiguous()
+        kl = [torch.randn(1, G, T, hd, device="cuda").to(torch.bfloat16) for _ in caches]
+        vl = [torch.randn(1, G, T, hd, device="cuda").to(torch.bfloat16) for _ in caches]
 
     def run(i):
-        fn(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
+        if args.library:
+            torch.nn.functional.scaled_dot_product_attention(ql, kl[i], vl[i], is_causal=True, enable_gqa=True)
+        else:
+            fn(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
 
     sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     flops = 2.0 * 2 * H * hd * T * (T + 1) / 2
-    return {"kernel": "attention_prefill", "tokens": T, "heads": H, "kv_heads": G, "head_dim": hd,
+    return {"kernel": "scaled_dot_product_attention (library)" if args.library else "attention_prefill", "tokens": T, "heads": H, "kv_heads": G, "head_dim": hd,
             "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 2)}
 
 
@@ -202,6 +215,9 @@ def main(argv=None):
     ap.add_argument("--min-p", type=float, default=0.05)
     ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
     ap.add_argument("--b-mn", action="store_true", help="mma_rate: B with its N dimension contiguous (as V in attention)")
+    ap.add_argument("--library", action="store_true",
+                    help="gemm, attention_prefill: time the library's routine on the same sizes instead (a yardstick; "
+                         "no model step uses it)")
     ap.add_argument("--copies", type=int, default=0,
                     help="gemm: weight copies to rotate through (default: enough to exceed L2; 1 keeps them in L2)")
     ap.add_argument("--iters", type=int, default=50)
