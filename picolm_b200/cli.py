@@ -48,6 +48,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="bfloat16 (serving kernels) or float32 (everything in true 32-bit)")
     e.add_argument("--max-batch", type=int, default=8, help="most sequences generated together (default: 8)")
     b = ap.add_argument_group("Benchmark options")
+    b.add_argument("--benchmark", action="store_true",
+                   help="benchmark mode: the prompt's step and -n decode steps with the time of every layer "
+                        "(three iterations; per-layer ms and effective weight GB/s on standard error)")
     b.add_argument("--benchmark-ctx", action="store_true",
                    help="benchmark prefill+gen speed at growing context sizes: the prompt (-p) is prefilled again and "
                         "again behind what is already cached, -n tokens are generated after each, up to the context (-c)")
@@ -92,6 +95,80 @@ def benchmark_context_scaling(args, base: List[int]) -> int:
     return 0
 
 
+def layer_times(marks, n_runs: int) -> List[float]:
+    """Mean milliseconds of every run of the schedule from (run, elapsed ms) pairs of one or more steps."""
+    total, count = [0.0] * n_runs, [0] * n_runs
+    for run, ms in marks:
+        total[run] += ms
+        count[run] += 1
+    return [t / c if c else 0.0 for t, c in zip(total, count)]
+
+
+def benchmark_layers(args, base: List[int], iterations: int = 3) -> int:
+    """The reference's `--benchmark` (picolm/picolm.c:1364-1475; its per-layer callback picolm/picolm.c:251-383):
+    the prompt in one step, then `-n` tokens greedily, with the time of every layer taken by events around it
+    (`Model.layer_hook`; the steps are launched kernel by kernel, not replayed from graphs).  Every iteration
+    starts from an empty cache and prints, per layer, the milliseconds in the prompt's step, the mean
+    milliseconds in a decode step and the rate at which the decode step reads the layer's weights; then the
+    reference's `Prefill:` / `Generation:` lines.  The reference loops until it is interrupted; this runs
+    `iterations` times (the first includes whatever is compiled or set up at first use)."""
+    import time
+
+    import torch
+
+    from . import ops
+    from .api import model_load
+    engine = model_load(args.model, dtype=args.dtype, context=args.context or None, max_batch=1)
+    model = engine.model
+    n_runs = len(model.spec.schedule)
+    n_new = max(0, min(args.max_tokens, engine.cache.max_seq_tokens - len(base)))
+    weight_mb = [sum(part.weight_bytes() for _, part in model.blocks[i].parts()) / 1e6 for i in model.spec.schedule]
+    events, started = [], {}
+
+    def hook(run: int, layer: int, done: bool) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        if done:
+            events.append((run, started.pop(run), e))
+        else:
+            started[run] = e
+
+    def collect():
+        engine.synchronize()
+        out = [(run, a.elapsed_time(b)) for run, a, b in events]
+        events.clear()
+        return out
+
+    try:
+        model.layer_hook = hook
+        for it in range(1, iterations + 1):
+            slot = engine.new_sequence()
+            try:
+                engine.synchronize()
+                t0 = time.perf_counter()
+                tok = ops.argmax(engine.step([(slot, base)]))
+                prefill = layer_times(collect(), n_runs)
+                t1 = time.perf_counter()
+                for _ in range(n_new):
+                    tok = ops.argmax(engine.step_device_tokens([slot], tok), out=engine.token_buffer(1))
+                decode = layer_times(collect(), n_runs)
+                t2 = time.perf_counter()
+            finally:
+                engine.end_sequence(slot)
+            print(f"=== iteration {it}: {len(base)} prompt tokens, {n_new} generated", file=sys.stderr)
+            print("layer,prefill_ms,gen_ms,weight_MB,gen_weight_GB/s", file=sys.stderr)
+            for run, i in enumerate(model.spec.schedule):
+                rate = weight_mb[run] / decode[run] if decode[run] > 0 else 0.0          # MB / ms = GB/s
+                print(f"{i},{prefill[run]:.3f},{decode[run]:.4f},{weight_mb[run]:.1f},{rate:.0f}", file=sys.stderr)
+            print(f"layers: prefill {sum(prefill):.2f} ms, gen {sum(decode):.3f} ms a token", file=sys.stderr)
+            pf, gn = t1 - t0, t2 - t1
+            print(f"Prefill: {len(base)} tokens in {pf:.2f}s ({len(base) / pf if pf > 0 else 0:.1f} tok/s)", file=sys.stderr)
+            print(f"Generation: {n_new} tokens in {gn:.2f}s ({n_new / gn if gn > 0 else 0:.1f} tok/s)", file=sys.stderr)
+    finally:
+        model.layer_hook = None
+    return 0
+
+
 def main(argv=None) -> int:
     ap = build_parser()
     args = ap.parse_args(argv)
@@ -130,6 +207,8 @@ def main(argv=None) -> int:
 
     if args.benchmark_ctx:
         return benchmark_context_scaling(args, prompts[0])
+    if args.benchmark:
+        return benchmark_layers(args, prompts[0])
 
     from .api import generate, model_load
     engine = model_load(args.model, dtype=args.dtype, context=args.context or None,

@@ -182,7 +182,7 @@ class Engine:
         self.cache.reserve([(slot, len(toks)) for slot, toks in entries])
         logits = None
         graphed = False
-        if self.use_graphs and all(len(toks) == 1 for _, toks in entries):
+        if self.use_graphs and self.model.layer_hook is None and all(len(toks) == 1 for _, toks in entries):
             logits, graphed = self._decode_with_graph(entries, wants, device_tokens)
         if not graphed:
             batch = build_step_batch(entries, wants, self.cache, self.runtime.device)

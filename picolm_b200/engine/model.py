@@ -35,6 +35,11 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.lm_head, runtime)
         self.loaded = False
+        # Called as layer_hook(run, layer, done) before (done False) and after (done True) every scheduled layer
+        # of a step: the reference's per-layer benchmark callback (bench_layer_cb_t, picolm/model.h:528-533,
+        # fired around each layer in picolm/model_core.c:235-252).  While it is set, steps are not replayed
+        # from captured graphs.
+        self.layer_hook: Optional[Callable[[int, int, bool], None]] = None
 
     # ---------------------------------------------------------------- weights
     def named_parts(self) -> List[Tuple[str, Part]]:
@@ -121,8 +126,13 @@ class Model:
         """Run the step's tokens through the scheduled layers; returns fp32 logits
         [wanted rows, vocab] (None if no row is wanted)."""
         stream = ResidualStream(self.embedding.forward(step))
+        hook = self.layer_hook
         for run, i in enumerate(self.spec.schedule):
+            if hook is not None:
+                hook(run, i, False)
             self.blocks[i].forward(stream, step, self.layer_cache(run, cache, step))
+            if hook is not None:
+                hook(run, i, True)
         if step.n_want == 0:
             # the last delta need not be added: nothing reads the stream after it
             return None
