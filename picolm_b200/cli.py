@@ -110,7 +110,8 @@ def benchmark_layers(args, base: List[int], iterations: int = 3) -> int:
     (`Model.layer_hook`; the steps are launched kernel by kernel, not replayed from graphs).  Every iteration
     starts from an empty cache and prints, per layer, the milliseconds in the prompt's step, the mean
     milliseconds in a decode step and the rate at which the decode step reads the layer's weights; then the
-    reference's `Prefill:` / `Generation:` lines.  The reference loops until it is interrupted; this runs
+    reference's `Prefill:` / `Generation:` lines.  (In a decode step a layer hands its last product to the norm that
+    follows, so that product's time is counted with the next layer; the sums are right.)  The reference loops until it is interrupted; this runs
     `iterations` times (the first includes whatever is compiled or set up at first use)."""
     import time
 
