@@ -111,7 +111,7 @@ def benchmark_layers(args, base: List[int], iterations: int = 3) -> int:
     starts from an empty cache and prints, per layer, the milliseconds in the prompt's step, the mean
     milliseconds in a decode step and the rate at which the decode step reads the layer's weights; then the
     reference's `Prefill:` / `Generation:` lines.  (In a decode step a layer hands its last product to the norm that
-    follows, so that product's time is counted with the next layer; the sums are right.)  The reference loops until it is interrupted; this runs
+    follows, so that product's time is counted with the next layer, the last layer's with none.)  The reference loops until it is interrupted; this runs
     `iterations` times (the first includes whatever is compiled or set up at first use)."""
     import time
 
