@@ -200,7 +200,7 @@ def main():
         return torch.cuda.Event(enable_timing=True)
 
     # ---------------------------------------------------------------- prefill
-    reps = 5
+    reps = 20
     times = []
     for i in range(args.warmup + reps):
         p = prompts(1, prefill_tokens)[0]
