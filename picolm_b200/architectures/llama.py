@@ -11,7 +11,8 @@ from __future__ import annotations
 
 from ..config.llama import LlamaConfig
 from ..config.registry import register_architecture
-from ..config.spec import LayerSpec, ModelSpec, PartSpec
+from ..config.spec import ModelSpec, PartSpec
+from ..parts.block import pre_norm_layer
 
 
 def llama_spec(cfg: LlamaConfig) -> ModelSpec:
@@ -44,9 +45,8 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
         "gate_name": "gate_proj.weight", "up_name": "up_proj.weight", "down_name": "down_proj.weight",
     }, prefix="mlp")
     layers = tuple(
-        LayerSpec(
+        pre_norm_layer(
             prefix=f"model.layers.{i}",
-            arrangement="pre_norm",
             mixer=attention,
             feed_forward=swiglu,
             mixer_norm=PartSpec("rmsnorm", norm, prefix="input_layernorm"),

@@ -168,29 +168,9 @@ def bench_sample(args):
             "us": round(sec * 1e6, 2), "GB/s": round(B * V * 4 / sec / 1e9, 1)}
 
 
-def bench_mma_rate(args):
-    """Cycles per tcgen05.mma (m x n x 16, bf16; --m 64 or 128) with one and with two issuing CTAs an SM."""
-    from .ops._lib import SM_COUNT, _check, _fn, _p, _stream, status_word
-    m = args.m if args.m in (64, 128) else 128
-    cycles = torch.zeros(1, dtype=torch.int64, device="cuda")
-    status = status_word(cycles.device)
-    fn = _fn("mma_rate", "plm_mma_rate")
-    reps, rows = 512, []
-    for a_tmem, n in ((0, 64), (0, 128), (0, 256), (1, 64), (1, 128)):
-        row = {"m": m, "n": n, "a": "tmem" if a_tmem else "smem", "b": "mn-major" if args.b_mn else "k-major",
-               "ideal": m * n * 16 // 4096}
-        for per_sm in (1, 2):
-            for r in (8, reps):                                      # a short run first: first-launch costs
-                _check(fn(a_tmem, int(args.b_mn), m, n, r, per_sm * SM_COUNT, _p(cycles), _p(status), _stream()), "mma_rate")
-            torch.cuda.synchronize()
-            row[f"cycles_{per_sm}_cta_per_sm"] = round(int(cycles.item()) / (reps * 4), 1)
-        rows.append(row)
-    return {"kernel": "tcgen05.mma rate", "rows": rows}
-
-
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m picolm_b200.bench_kernels", description=__doc__.split("\n\n")[0])
-    ap.add_argument("kernel", choices=["gemm", "attention_decode", "attention_prefill", "sample", "mma_rate"])
+    ap.add_argument("kernel", choices=["gemm", "attention_decode", "attention_prefill", "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -214,7 +194,6 @@ def main(argv=None):
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--min-p", type=float, default=0.05)
     ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
-    ap.add_argument("--b-mn", action="store_true", help="mma_rate: B with its N dimension contiguous (as V in attention)")
     ap.add_argument("--library", action="store_true",
                     help="gemm, attention_prefill: time the library's routine on the same sizes instead (a yardstick; "
                          "no model step uses it)")
@@ -228,7 +207,7 @@ def main(argv=None):
     global USE_GRAPH
     USE_GRAPH = args.graph and not args.once
     fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,
-          "attention_prefill": bench_attention_prefill, "sample": bench_sample, "mma_rate": bench_mma_rate}[args.kernel]
+          "attention_prefill": bench_attention_prefill, "sample": bench_sample}[args.kernel]
     print(json.dumps(fn(args)))
     return 0
 

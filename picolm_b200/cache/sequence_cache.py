@@ -7,8 +7,9 @@ storage of its own: a kv group owns `k`/`v` tensors
 `[layers_in_group, pages, kv_heads, PAGE_TOKENS, head_dim]` and one page list per
 slot (all layers of the group use the same page numbers); a group with a window
 gives pages back as soon as every position on them has left the window.  A state
-layer owns a tensor `[slots, *shape]`, zeroed when a slot is handed out.  Page 0
-of every kv group is never handed out: padding rows of a step point at it.
+layer owns a tensor `[slots + 1, *shape]`, a slot's row zeroed when the slot is
+handed out.  Page 0 of every kv group is never handed out, and neither is the last
+row of a state tensor (`null_slot`): the padding rows of a captured step point at them.
 
 The reference has one sequence per model: one K block and one V block
 `[kv_layers][max_seq_len][kv_heads*head_dim]` and a position counter held by the
@@ -63,7 +64,7 @@ class KVLayerCache:
 @dataclass
 class StateLayerCache:
     """What a mixer sees of its fixed-size state: `state[slot]` for each slot."""
-    state: torch.Tensor                         # [slots, *shape]
+    state: torch.Tensor                         # [slots + 1, *shape]; the last row belongs to padding rows
     writable: bool = True
 
 
@@ -71,9 +72,9 @@ class SequenceCache:
     def __init__(self, layer_specs: Sequence[Optional[CacheSpec]], max_tokens: int, max_seqs: int,
                  kv_dtype: torch.dtype = torch.bfloat16, device="cpu", max_seq_tokens: Optional[int] = None,
                  allocate_storage: bool = True):
-        """`layer_specs[i]` is what the mixer of the i-th run of the model's
-        schedule asked for (None: nothing).  The indices used throughout this class
-        are those run indices.
+        """`layer_specs[i]` is what cache number i holds (None: nothing): the model numbers
+        what the runs of its schedule keep, a Llama layer's keys and values being one
+        such cache per run.  The indices used throughout this class are those numbers.
         `max_tokens` is the most tokens live sequences hold together, each
         sequence's count rounded up to a page; `max_seqs` the most live
         sequences; `max_seq_tokens` the longest single sequence."""
@@ -86,6 +87,7 @@ class SequenceCache:
         self.device = torch.device(device)
         self.kv_dtype = kv_dtype
         self.slots = IndexPool(max_seqs, what="slot")
+        self.null_slot = max_seqs                      # the state row of a step's padding sequences
         self.lengths: Dict[int, int] = {}
         self.kv_groups: List[KVGroup] = []
         self.layer_group: Dict[int, int] = {}          # layer -> kv group index
@@ -116,7 +118,7 @@ class SequenceCache:
                 g.k = torch.zeros(shape, dtype=kv_dtype, device=self.device)
                 g.v = torch.zeros(shape, dtype=kv_dtype, device=self.device)
             for layer, spec in self.state_specs.items():
-                self.state[layer] = torch.zeros((max_seqs,) + spec.shape, dtype=_STATE_DTYPES[spec.dtype],
+                self.state[layer] = torch.zeros((max_seqs + 1,) + spec.shape, dtype=_STATE_DTYPES[spec.dtype],
                                                 device=self.device)
 
     # ------------------------------------------------------------------ slots

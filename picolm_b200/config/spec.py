@@ -28,17 +28,25 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (block kind) of a mixer, a feed-forward and
-    their norms.  `cache_of` names another layer whose cache this layer's mixer
-    reads instead of owning one (it then writes nothing)."""
+    """One layer: an arrangement (block kind) and the parts it is made of, by
+    the names the arrangement gives them (`pre_norm` wants "mixer_norm", "mixer",
+    "feed_forward_norm" and "feed_forward"; another arrangement may want four
+    norms, one, or two mixers).  The value of a name is `(family, PartSpec)`.
+    `cache_of` names another layer whose caches this layer's parts read instead
+    of owning their own (they then write nothing)."""
 
     prefix: str
     arrangement: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, Tuple[str, PartSpec]]
     cache_of: Optional[int] = None
+
+    def part(self, name: str) -> PartSpec:
+        """The spec of the part the arrangement calls `name`."""
+        try:
+            return self.parts[name][1]
+        except KeyError:
+            raise KeyError(f"layer {self.prefix!r} ({self.arrangement}) has no part {name!r}; it has: "
+                           + ", ".join(sorted(self.parts))) from None
 
 
 @dataclass(frozen=True)

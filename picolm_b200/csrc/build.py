@@ -40,7 +40,6 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "attention_tc": ["attention_tc.cu"],            # likewise, head sizes 64 and 128
     "sampling": ["sampling.cu"],
-    "mma_rate": ["mma_rate.cu"],                    # a measuring kernel for `python -m picolm_b200.bench_kernels mma_rate`
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
 

@@ -8,14 +8,16 @@
 // picolm/tensor.c:2174), for 16-bit weights (picolm/quant.c:133-153), as one
 // tensor-core kernel.
 //
-// One CTA computes one 128 x BN tile of D = P * Q^T, where P is the operand on
-// the 128 TMEM lanes and Q the operand on the BN accumulator columns:
-//   wide   (T > 64):  P = X (tokens), Q = W (features): BN = 128 or 256
-//   skinny (T <= 64): P = W (features), Q = X (tokens): BN = 16..64, so that a
-//                     decode step streams each weight once with full tiles, and
-//                     K is split over gridDim.z CTAs so that all SMs pull from
-//                     HBM; the fp32 partials go to a workspace and are summed in
-//                     a fixed order by a second kernel.
+// For outside callers with a plain C ABI and at most 64 rows of X (a decode step's
+// shapes): plm_gemm_tc takes a caller-provided fp32 workspace, plm_gemm_tc_static
+// (gemm_tc_static.h) keeps the workspace inside the library.  The engine itself
+// uses gemm_tc_skinny.cu (no workspace at all) and gemm_tc_wide.cu (more rows).
+//
+// One CTA computes one 128 x BN tile of D = W * X^T: the weights W on the 128 TMEM
+// lanes, the tokens X on the BN = 16..64 accumulator columns, so that the step
+// streams each weight once with full tiles.  K is split over gridDim.z CTAs so
+// that all SMs pull from HBM; the fp32 partials go to the workspace and are
+// summed in a fixed order by a second kernel.
 // Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).
 //
@@ -29,17 +31,17 @@ using namespace plm_tc;
 namespace {
 
 // skinny tiles (bn < 128) keep their ring small enough for two CTAs per SM
-__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 5); }
+__host__ __device__ constexpr int stages_for(int bn) { return 5; }
 __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
     return (size_t)stages_for(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
 
-// P: [p_rows, K], Q: [q_rows, K], both bf16 K-major, described by the tensor maps.
-// SWAP = false: out[p, q] (tokens on P);  SWAP = true: out[q, p] (tokens on Q).
+// P: the weights [p_rows, K], Q: the tokens [q_rows, K], both bf16 K-major, described by
+// the tensor maps; out[q, p].
 // gridDim = (P tiles, Q tiles, K splits).  With more than one split, OutT is
 // float and the CTA writes its partial sum to out + blockIdx.z * split_stride.
-template <int BN, bool SWAP, typename OutT>
-__global__ void __launch_bounds__(NUM_THREADS, (BN < 128 ? 2 : 1))
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                OutT* __restrict__ out, int p_rows, int q_rows, int K, long ldo, int kb_per_split, long split_stride,
                int* __restrict__ status) {
@@ -84,14 +86,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
-        // The weight operand (P when SWAP, else Q) is written by no kernel of the step, so its
-        // first ring of loads is issued before pdl_wait(); the activation operand only after it.
+        // The weight operand is assumed to be written by no kernel that runs just before this one,
+        // so its first ring of loads is issued before pdl_wait(); the activation operand only after it.
         if (lane == 0) {
-            const CUtensorMap* w_map = SWAP ? &map_p : &map_q;
-            const CUtensorMap* x_map = SWAP ? &map_q : &map_p;
-            const uint32_t w_smem = SWAP ? p_smem : q_smem, x_smem = SWAP ? q_smem : p_smem;
-            const uint32_t W_BYTES = SWAP ? P_BYTES : Q_BYTES, X_BYTES = SWAP ? Q_BYTES : P_BYTES;
-            const int w_row = SWAP ? p0 : q0, x_row = SWAP ? q0 : p0;
+            const CUtensorMap* w_map = &map_p;
+            const CUtensorMap* x_map = &map_q;
+            const uint32_t w_smem = p_smem, x_smem = q_smem;
+            const uint32_t W_BYTES = P_BYTES, X_BYTES = Q_BYTES;
+            const int w_row = p0, x_row = q0;
             const int early = n_kb < STAGES ? n_kb : STAGES;
             for (int i = 0; i < early; ++i) {              // the ring is empty: no wait needed
                 mbar_expect_tx(full0 + 8 * i, P_BYTES + Q_BYTES);
@@ -156,25 +158,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
                 if (CHUNK == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
                 tc_wait_ld();
-                if (!SWAP) {
-                    if (p < p_rows) {
-                        OutT* rowp = dst + (size_t)p * ldo + q0 + c;
-                        const bool vec = (q0 + c + CHUNK <= q_rows) && ((((size_t)p * ldo + q0 + c) * sizeof(OutT)) % 16 == 0);
-                        if (vec) {
+                if (p < p_rows) {
 #pragma unroll
-                            for (int j = 0; j < CHUNK; j += 8) store_vec8<OutT>(rowp + j, r + j);
-                        } else {
-                            for (int j = 0; j < CHUNK; ++j)
-                                if (q0 + c + j < q_rows) rowp[j] = from_f32<OutT>(__uint_as_float(r[j]));
-                        }
-                    }
-                } else {
-                    if (p < p_rows) {
-#pragma unroll
-                        for (int j = 0; j < CHUNK; ++j) {
-                            const int q = q0 + c + j;   // a token; lanes write consecutive features: coalesced
-                            if (q < q_rows) dst[(size_t)q * ldo + p] = from_f32<OutT>(__uint_as_float(r[j]));
-                        }
+                    for (int j = 0; j < CHUNK; ++j) {
+                        const int q = q0 + c + j;       // a token; lanes write consecutive features: coalesced
+                        if (q < q_rows) dst[(size_t)q * ldo + p] = from_f32<OutT>(__uint_as_float(r[j]));
                     }
                 }
             }
@@ -218,12 +206,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __
     }
 }
 
-template <int BN, bool SWAP, typename OutT>
+template <int BN, typename OutT>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, OutT* out, int p_rows, int q_rows, int K, long ldo,
            int splits, int kb_per_split, long split_stride, int* status, cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = smem_bytes_for(BN);
-    auto kern = gemm_tc_kernel<BN, SWAP, OutT>;
+    auto kern = gemm_tc_kernel<BN, OutT>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -258,7 +246,7 @@ extern "C" int plm_gemm_tc_supported(const void* x, const void* w, int T, int F,
 }
 
 // Number of K splits and fp32 workspace elements that plm_gemm_tc will use for a
-// problem (1 and 0 for the wide path).  Fixed by (T, F, K) alone.
+// problem.  Fixed by (T, F, K) alone.
 extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* workspace_elems) {
     int splits = 1;
     if (T <= 64) {
@@ -276,7 +264,9 @@ extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* work
     return PLM_OK;
 }
 
-// out[T, F] (out_dtype, leading dimension ldo) = x[T, K] * w[F, K]^T.
+// out[T, F] (out_dtype, leading dimension ldo) = x[T, K] * w[F, K]^T for T <= 64.
+// `w` must not be written by the kernel that runs just before this one on the stream
+// (its first tiles are requested before that kernel has finished).
 // `workspace` must hold the elements that plm_gemm_tc_plan reports; `status` is
 // a device int that is 0 unless a bounded wait ran out (then 1, 2 or 3: producer,
 // MMA issuer, epilogue).
@@ -285,22 +275,9 @@ extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtyp
     if (T <= 0 || F <= 0) return PLM_OK;
     if (!plm_gemm_tc_supported(x, w, T, F, K, ldx, ldw)) return PLM_ERR_ALIGN;
     if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    if (T > 64) return PLM_ERR_SHAPE;                      // more rows belong to plm_gemm_tc_wide
     CUtensorMap mp, mq;
     int rc;
-    if (T > 64) {
-        const int bn = (F >= 2048 && T >= 256) ? 256 : 128;
-        if ((rc = make_map(&mp, x, T, K, ldx, BM)) != PLM_OK) return rc;
-        if ((rc = make_map(&mq, w, F, K, ldw, bn)) != PLM_OK) return rc;
-        const int n_kb = (K + BK - 1) / BK;
-        if (bn == 256) {
-            return out_dtype == PLM_F32
-                ? launch<256, false, float>(mp, mq, (float*)out, T, F, K, ldo, 1, n_kb, 0, status, stream)
-                : launch<256, false, bf16>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
-        }
-        return out_dtype == PLM_F32
-            ? launch<128, false, float>(mp, mq, (float*)out, T, F, K, ldo, 1, n_kb, 0, status, stream)
-            : launch<128, false, bf16>(mp, mq, (bf16*)out, T, F, K, ldo, 1, n_kb, 0, status, stream);
-    }
     // skinny: weights on the TMEM lanes, tokens on the accumulator columns
     int splits;
     long ws_elems;
@@ -314,21 +291,21 @@ extern "C" int plm_gemm_tc(const void* x, const void* w, void* out, int out_dtyp
         if (!workspace) return PLM_ERR_SHAPE;
         const long stride = (long)T * F;
         if (ldo != F) return PLM_ERR_SHAPE;
-        if (bn == 16) rc = launch<16, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
-        else if (bn == 32) rc = launch<32, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
-        else rc = launch<64, true, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        if (bn == 16) rc = launch<16, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        else if (bn == 32) rc = launch<32, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
+        else rc = launch<64, float>(mp, mq, workspace, F, T, K, F, splits, per, stride, status, stream);
         if (rc != PLM_OK) return rc;
         return out_dtype == PLM_F32 ? launch_reduce<float>(workspace, (float*)out, splits, (size_t)stride, stream)
                                     : launch_reduce<bf16>(workspace, (bf16*)out, splits, (size_t)stride, stream);
     }
     if (out_dtype == PLM_F32) {
-        if (bn == 16) return launch<16, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
-        if (bn == 32) return launch<32, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
-        return launch<64, true, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+        if (bn == 16) return launch<16, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+        if (bn == 32) return launch<32, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+        return launch<64, float>(mp, mq, (float*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
     }
-    if (bn == 16) return launch<16, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
-    if (bn == 32) return launch<32, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
-    return launch<64, true, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    if (bn == 16) return launch<16, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    if (bn == 32) return launch<32, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
+    return launch<64, bf16>(mp, mq, (bf16*)out, F, T, K, ldo, 1, n_kb, 0, status, stream);
 }
 
 // ------------------------------------------------- the entry point that allocates nothing

@@ -16,7 +16,11 @@
  * whose partial sums need more are refused, and all calls share the one array,
  * so two calls that overlap on the GPU (different streams, or one stream with
  * programmatic overlap) race on it.  Calls on one stream, one after another, are
- * safe.
+ * safe, with one condition on `w`: the kernel requests its first tiles of `w`
+ * before the kernel in front of it on the stream has finished (programmatic
+ * dependent launch), so `w` must be complete before that kernel starts: weights
+ * that were uploaded earlier are, the output of the product just before is not.
+ * `x` and `out` have no such condition.
  */
 #ifndef PICOLM_B200_GEMM_TC_STATIC_H
 #define PICOLM_B200_GEMM_TC_STATIC_H
@@ -34,7 +38,7 @@ extern "C" {
 #define PLM_ERR_SCRATCH_TOO_SMALL (-6)   /* the problem's partial sums exceed the fixed array */
 #define PLM_ERR_SCRATCH_SETUP (-7)       /* the array's device address could not be obtained */
 
-/* out[T, F] = x[T, K] * w[F, K]^T, bfloat16 operands, fp32 accumulation; out is
+/* out[T, F] = x[T, K] * w[F, K]^T for T <= 64, bfloat16 operands, fp32 accumulation; out is
  * float32 (out_dtype 0) or bfloat16 (out_dtype 1) with leading dimension ldo.
  * Same arithmetic, same split of K and same result as plm_gemm_tc; only the
  * place of the partial sums differs.  `status` may be NULL; if given it is a

@@ -71,12 +71,12 @@ class DecodeGraph:
         self.h[6][:] = np.arange(B)                       # want_rows: every row
         self.tables_h = [self.h[7 + g].reshape(B, P) for g in range(n_groups)]
         self.step = StepBatch(
-            n_seqs=B, n_tokens=B, n_want=B, slots=[0] * B, new_lens=[1] * B, start_pos=[0] * B,
+            n_seqs=B, n_tokens=B, n_want=B, slots=None, new_lens=None, start_pos=None,
             max_position=max_len - 1,                     # the graph's length class (see length_class)
             is_decode=True, tok_ids=self.d[0], tok_seq=self.d[1], tok_pos=self.d[2], seq_slot=self.d[3],
             seq_start=self.d[4], seq_kv_len=self.d[5], want_rows=self.d[6],
             block_tables=[self.d[7 + g].view(B, P) for g in range(n_groups)],
-            seq_slot_long=None, h2d_bytes=int(self.host_np.nbytes))
+            h2d_bytes=int(self.host_np.nbytes))
         self.copied = torch.cuda.Event()                  # the last metadata copy has left the pinned buffer
         self.replayed: Optional[torch.cuda.Event] = None  # the last run of the step has read the metadata
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -94,7 +94,7 @@ class DecodeGraph:
         h[2][:n] = positions
         h[2][n:] = 0
         h[3][:n] = slots
-        h[3][n:] = 0
+        h[3][n:] = cache.null_slot                        # state of their own for the padding rows
         h[5][:n] = h[2][:n] + 1
         h[5][n:] = 1
         for g, table in enumerate(self.tables_h):
@@ -111,9 +111,11 @@ class DecodeGraph:
             self.copied.record(side)
         cur.wait_event(self.copied)
         if device_tokens is None:
+            self.engine.before_token_write()              # a copy of the last ids to the host may still read it
             self.d[0].copy_(self.dev[:B])
         elif device_tokens.data_ptr() != self.d[0].data_ptr():
             # the token ids are on the device already; rows of padding keep whatever valid id they held
+            self.engine.before_token_write()
             self.d[0][:n].copy_(device_tokens)
 
     def _mark_replayed(self) -> None:
@@ -132,6 +134,7 @@ class DecodeGraph:
             eng.model.forward(self.step, eng.cache)
         self._mark_replayed()
         torch.cuda.synchronize()
+        self.step._seq_slot_long = None                   # made again inside the capture, so that replays refresh it
         n0 = ops.launch_count()
         self.graph = torch.cuda.CUDAGraph()
         # Nothing may be freed while the stream is capturing: collect what is dead now and keep the

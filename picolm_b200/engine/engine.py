@@ -49,15 +49,28 @@ class Engine:
         safe = all(getattr(part, "graph_safe", False) for b in model.blocks for _, part in b.parts())
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
-        self._tokens = torch.zeros(256, dtype=torch.int32, device=self.runtime.device)
+        # one id per live sequence, and never fewer than the largest captured batch size (its padding rows read it)
+        from .decode_graph import BUCKETS
+        self._tokens = torch.zeros(max(BUCKETS[-1], self.cache.max_seqs), dtype=torch.int32,
+                                   device=self.runtime.device)
         self._side_streams: Dict[str, torch.cuda.Stream] = {}
         self._fetched: Optional[torch.cuda.Event] = None      # the last copy of sampled ids to the host
         self.reset_counters()
 
     def token_buffer(self, n: int) -> torch.Tensor:
         """The first `n` entries of the buffer from which captured decode steps read their token ids.  A
-        sampler that writes its result here (`out=`) saves `step_device_tokens` a copy."""
+        sampler that writes its result here (`out=`) saves `step_device_tokens` a copy.  The buffer holds one
+        id per sequence the cache can hold; more are refused."""
+        if not 0 < n <= self._tokens.numel():
+            raise ValueError(f"{n} token ids asked for; the engine holds at most {self._tokens.numel()} sequences")
         return self._tokens[:n]
+
+    def before_token_write(self) -> None:
+        """Called by whatever is about to write the token buffer on the current stream: that write has to
+        wait until the last copy of sampled ids to the host (`fetch_later`) has read the buffer."""
+        if self._fetched is not None:
+            torch.cuda.current_stream(self.runtime.device).wait_event(self._fetched)
+            self._fetched = None
 
     def reset_counters(self) -> None:
         """Bytes copied between host and device by the steps since the last reset."""
@@ -192,9 +205,7 @@ class Engine:
             from .. import ops
             with ops.stream_scope():
                 logits = self.model.forward(batch, self.cache)
-        if self._fetched is not None:                        # what follows this step may write the ids' buffer
-            torch.cuda.current_stream(self.runtime.device).wait_event(self._fetched)
-            self._fetched = None
+        self.before_token_write()                            # what follows this step may write the ids' buffer
         self.counters["steps"] += 1
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))

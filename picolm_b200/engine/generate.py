@@ -156,6 +156,20 @@ def _decode_ahead(engine, sampler, batch, slots, live, first_tokens, stop, on_to
         judge(members, row.tolist(), lengths)
 
 
+def greedy_steps_in_flight(engine, slots: Sequence[int], tok_dev, steps: int, pinned):
+    """`steps` greedy decode steps of the sequences in `slots`, none of which the host waits for: each
+    step's ids (int32 on the device, `tok_dev` for the first) feed the next step on the device and go to
+    row j of `pinned` (host memory, [steps, sequences]) by a copy of their own.  Returns the last ids on the
+    device; the rows of `pinned` are complete once the device has been synchronised.  This is the decode
+    loop of `generate` without its decisions: what a benchmark of the step itself times."""
+    from .. import ops
+    n = len(slots)
+    for j in range(steps):
+        tok_dev = ops.argmax(engine.step_device_tokens(slots, tok_dev), out=engine.token_buffer(n))
+        engine.fetch_later(tok_dev, pinned[j])
+    return tok_dev
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_ids: Optional[Sequence[int]] = None,
              max_batch: Optional[int] = None,

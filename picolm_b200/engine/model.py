@@ -84,42 +84,49 @@ class Model:
     # layer: a layer that the schedule names twice shares its weights between
     # the two runs, but each run sees other inputs and so has keys, values or
     # state of its own.  A layer with `cache_of = j` owns nothing: each of its
-    # runs reads what the latest earlier run of layer j wrote.
-    def cache_specs(self) -> List[Optional[CacheSpec]]:
-        """What each run of the schedule owns in the cache (None: nothing, or
-        another layer's)."""
-        out: List[Optional[CacheSpec]] = []
-        for i in self.spec.schedule:
+    # runs reads what the latest earlier run of layer j wrote.  What a layer keeps
+    # is its arrangement's business (`cache_specs()`): the model only numbers it.
+    def cache_specs(self) -> List[CacheSpec]:
+        """What the runs of the schedule own in the cache, as one flat list: for every run that owns
+        its caches, what its arrangement asks for (one entry per part that keeps something; none for a
+        layer without such parts).  The position in this list is the cache's number in `SequenceCache`."""
+        out: List[CacheSpec] = []
+        self._run_caches: List[Tuple[List[int], bool]] = []       # per run: (cache numbers, may write them)
+        for run, i in enumerate(self.spec.schedule):
             layer = self.spec.layers[i]
-            out.append(None if layer.cache_of is not None else self.blocks[i].mixer.cache_spec())
+            if layer.cache_of is None:
+                specs = list(self.blocks[i].cache_specs())
+                self._run_caches.append((list(range(len(out), len(out) + len(specs))), True))
+                out.extend(specs)
+                continue
+            src = next((r for r in range(run - 1, -1, -1) if self.spec.schedule[r] == layer.cache_of), None)
+            if src is None:
+                raise ValueError(f"run {run}: layer {layer.cache_of}, whose cache it reads, has not run before it")
+            ids = self._run_caches[src][0]
+            if len(ids) != len(self.blocks[i].cache_specs()):
+                raise ValueError(f"layer {i} reads the caches of layer {layer.cache_of}, which keeps {len(ids)}; "
+                                 f"its own parts want {len(self.blocks[i].cache_specs())}")
+            self._run_caches.append((ids, False))
         return out
-
-    def _cache_source(self, run: int) -> Tuple[int, bool]:
-        """(run whose cache this run uses, whether it may write it)."""
-        layer = self.spec.layers[self.spec.schedule[run]]
-        if layer.cache_of is None:
-            return run, True
-        for r in range(run - 1, -1, -1):
-            if self.spec.schedule[r] == layer.cache_of:
-                return r, False
-        raise ValueError(f"run {run}: layer {layer.cache_of}, whose cache it reads, has not run before it")
 
     def prepare(self, max_seq_tokens: int) -> None:
         for block in self.blocks:
-            prep = getattr(block.mixer, "prepare", None)
-            if prep is not None:
-                prep(max_seq_tokens)
+            block.prepare(max_seq_tokens)
 
-    def layer_cache(self, run: int, cache: SequenceCache, step):
-        src, writable = self._cache_source(run)
-        if src in cache.layer_group:
-            gi = cache.layer_group[src]
-            g = cache.kv_groups[gi]
-            o = g.ordinal(src)
-            return KVLayerCache(g.k[o], g.v[o], step.block_tables[gi], g.spec.window, writable)
-        if src in cache.state:
-            return StateLayerCache(cache.state[src], writable)
-        return None
+    def layer_caches(self, run: int, cache: SequenceCache, step) -> list:
+        """What the parts of a run see of the cache: one `KVLayerCache` or `StateLayerCache` per entry of
+        the arrangement's `cache_specs()`, in that order."""
+        ids, writable = self._run_caches[run]
+        out = []
+        for c in ids:
+            if c in cache.layer_group:
+                gi = cache.layer_group[c]
+                g = cache.kv_groups[gi]
+                o = g.ordinal(c)
+                out.append(KVLayerCache(g.k[o], g.v[o], step.block_tables[gi], g.spec.window, writable))
+            else:
+                out.append(StateLayerCache(cache.state[c], writable))
+        return out
 
     # ---------------------------------------------------------------- forward
     def forward(self, step, cache: SequenceCache) -> Optional[torch.Tensor]:
@@ -130,7 +137,7 @@ class Model:
         for run, i in enumerate(self.spec.schedule):
             if hook is not None:
                 hook(run, i, False)
-            self.blocks[i].forward(stream, step, self.layer_cache(run, cache, step))
+            self.blocks[i].forward(stream, step, self.layer_caches(run, cache, step))
             if hook is not None:
                 hook(run, i, True)
         if step.n_want == 0:

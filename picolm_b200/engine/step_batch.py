@@ -16,9 +16,12 @@ class StepBatch:
     n_seqs: int
     n_tokens: int
     n_want: int
-    slots: List[int]                      # host: cache slot of each sequence
-    new_lens: List[int]                   # host: tokens each sequence brings
-    start_pos: List[int]                  # host: position of each sequence's first new token
+    # The three host lists are None in a step that is replayed from a captured graph: the graph
+    # serves every batch of its size, so only what lives in device buffers may be read there
+    # (`seq_slot`, `tok_pos`, `seq_kv_len`, ...).
+    slots: Optional[List[int]]            # host: cache slot of each sequence
+    new_lens: Optional[List[int]]         # host: tokens each sequence brings
+    start_pos: Optional[List[int]]        # host: position of each sequence's first new token
     max_position: int                     # host: largest position written by this step
     is_decode: bool                       # every sequence brings exactly one token
     tok_ids: torch.Tensor                 # int32 [T]
@@ -29,8 +32,17 @@ class StepBatch:
     seq_kv_len: torch.Tensor              # int32 [B]  length after this step
     want_rows: torch.Tensor               # int32 [n_want] flat token indices
     block_tables: List[torch.Tensor]      # per kv group: int32 [B, pages per sequence]
-    seq_slot_long: Optional[torch.Tensor] = None     # int64 [B], for indexing state tensors
     h2d_bytes: int = 0                    # size of the one host-to-device copy that brought all of the above
+    _seq_slot_long: Optional[torch.Tensor] = None
+
+    @property
+    def seq_slot_long(self) -> torch.Tensor:
+        """`seq_slot` as int64 [B], for indexing state tensors with torch.  Made from the device buffer when
+        first asked for, on the current stream: inside a graph capture the conversion is part of the graph and
+        follows the buffer on every replay."""
+        if self._seq_slot_long is None:
+            self._seq_slot_long = self.seq_slot.to(torch.int64)
+        return self._seq_slot_long
 
 
 def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], cache, device) -> StepBatch:
@@ -90,6 +102,5 @@ def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], c
         tok_ids=dviews[0], tok_seq=dviews[1], tok_pos=dviews[2], seq_slot=dviews[3], seq_start=dviews[4],
         seq_kv_len=dviews[5], want_rows=dviews[6],
         block_tables=[dviews[7 + gi].view(B, P) for gi in range(n_groups)],
-        seq_slot_long=dviews[3].to(torch.int64),
         h2d_bytes=int(host.nbytes),
     )

@@ -2,7 +2,6 @@
 problems, the pieces of an RMSNorm that two products share, and the dispatcher `linear`."""
 from __future__ import annotations
 
-import ctypes
 from typing import Optional
 
 import torch
@@ -36,28 +35,6 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     # TMA's rule (the kernels check it again): rows start on 16-byte boundaries
     return (M > 0 and N > 0 and K % 8 == 0 and a.is_contiguous() and w.is_contiguous()
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bf16 in, fp32
-    accumulate).  With M <= 64 the weights take the 128-row side of the MMA and K
-    is split; the fp32 partial sums pass through a scratch buffer."""
-    _dev(a, "a"), _dev(w, "w")
-    if not gemm_tc_supported(a, w):
-        raise KernelError(f"gemm_tc: a {tuple(a.shape)} {a.dtype} @ w {tuple(w.shape)} {w.dtype} is not supported "
-                          f"(bfloat16, K a multiple of 8 and >= 64, 16-byte aligned)")
-    M, K = a.shape
-    N = w.shape[0]
-    if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    splits, ws_elems = ctypes.c_int(0), ctypes.c_long(0)
-    _fn("gemm_tc", "plm_gemm_tc_plan")(M, N, K, ctypes.byref(splits), ctypes.byref(ws_elems))
-    ws = torch.empty((ws_elems.value,), dtype=torch.float32, device=a.device) if ws_elems.value else None
-    _check(_fn("gemm_tc", "plm_gemm_tc")(
-        _p(a), _p(w), _p(out), _dt(out, "out"), M, N, K, K, K, N, _p(ws), _p(status_word(a.device)), _stream()),
-        "gemm_tc", kernels=2 if ws is not None else 1)
-    return out
 
 
 def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,

@@ -1,36 +1,58 @@
-"""Arrangements: how one layer's norms, mixer and feed-forward are wired around
+"""Arrangements: how one layer's norms, mixers and feed-forwards are wired around
 the residual stream.  Interface of the family: built from `(layer_spec,
-runtime)`; `parts()` lists `(relative prefix, part)` for the weights;
-`forward(stream, step, cache)` runs the layer on the stream in place.
+runtime)`; the arrangement alone reads `layer_spec.parts` (which parts a layer has
+and what they are called is its business, not the model's);
+`parts()` lists `(relative prefix, part)` for the weights; `cache_specs()` lists
+what the layer wants of the cache, one `CacheSpec` per part that keeps something;
+`prepare(max_seq_tokens)` runs once before the first step;
+`forward(stream, step, caches)` runs the layer on the stream in place, `caches`
+holding one entry per entry of `cache_specs()`, in that order.
 
 `pre_norm` is the reference's Llama layer: `x += mixer(norm(x));
 x += feed_forward(norm(x))` (picolm/model_core.c:1797-2210).
 """
 from __future__ import annotations
 
+from typing import List
+
+from ..config.spec import LayerSpec, PartSpec
 from .base import Part, build_part, register_part
 
 
-@register_part("arrangement", "pre_norm")
-class PreNormBlock(Part):
-    def __init__(self, layer_spec, runtime):
+class Arrangement(Part):
+    """Base of the arrangements: builds every part the layer's spec names and answers the model's
+    questions from them.  A subclass says which names it needs (`wants`) and how they are wired
+    (`forward`)."""
+
+    wants: tuple = ()
+
+    def __init__(self, layer_spec: LayerSpec, runtime):
         super().__init__({}, runtime)
         self.spec = layer_spec
-        self.mixer_norm = build_part("norm", layer_spec.mixer_norm, runtime)
-        self.mixer = build_part("mixer", layer_spec.mixer, runtime)
-        self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm, runtime)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
+        missing = [n for n in self.wants if n not in layer_spec.parts]
+        if missing:
+            raise ValueError(f"layer {layer_spec.prefix!r}: the {self.kind} arrangement needs the parts "
+                             f"{', '.join(missing)}; the spec has {', '.join(sorted(layer_spec.parts))}")
+        self.named = {name: build_part(family, spec, runtime) for name, (family, spec) in layer_spec.parts.items()}
+        for name, part in self.named.items():
+            setattr(self, name, part)
 
     def parts(self):
-        s = self.spec
-        return [(s.mixer_norm.prefix, self.mixer_norm), (s.mixer.prefix, self.mixer),
-                (s.feed_forward_norm.prefix, self.feed_forward_norm), (s.feed_forward.prefix, self.feed_forward)]
+        return [(self.spec.parts[name][1].prefix, part) for name, part in self.named.items()]
 
-    def forward(self, stream, step, cache):
-        h = self._norm(self.mixer_norm, self.mixer, stream)
-        stream.pending = self.mixer.forward(h, step, cache)
-        h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
-        stream.pending = self.feed_forward.forward(h, step)
+    def cache_owners(self) -> List[str]:
+        """Names of the parts that keep something in the cache, in the order of `cache_specs()`."""
+        return [name for name, part in self.named.items()
+                if getattr(part, "cache_spec", None) is not None and part.cache_spec() is not None]
+
+    def cache_specs(self):
+        return [self.named[name].cache_spec() for name in self.cache_owners()]
+
+    def prepare(self, max_seq_tokens: int) -> None:
+        for part in self.named.values():
+            prep = getattr(part, "prepare", None)
+            if prep is not None:
+                prep(max_seq_tokens)
 
     @staticmethod
     def _norm(norm, consumer, stream):
@@ -39,3 +61,23 @@ class PreNormBlock(Part):
         if getattr(norm, "can_defer_scale", False) and getattr(consumer, "takes_scaled_rows", False):
             return norm.forward(stream, defer_scale=True)
         return norm.forward(stream)
+
+
+@register_part("arrangement", "pre_norm")
+class PreNormBlock(Arrangement):
+    wants = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+
+    def forward(self, stream, step, caches):
+        h = self._norm(self.mixer_norm, self.mixer, stream)
+        stream.pending = self.mixer.forward(h, step, caches[0] if caches else None)
+        h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
+        stream.pending = self.feed_forward.forward(h, step)
+
+
+def pre_norm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                   feed_forward_norm: PartSpec, cache_of=None) -> LayerSpec:
+    """The spec of a `pre_norm` layer from its four parts."""
+    return LayerSpec(prefix, "pre_norm", {
+        "mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
+        "feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward),
+    }, cache_of=cache_of)

@@ -36,7 +36,8 @@ def test_groups_have_storage_of_their_own():
     assert c.kv_groups[0].k.shape == (2, 11, 2, PAGE_TOKENS, 16)           # 10 pages + the null page
     assert c.kv_groups[1].k.shape == (1, 11, 2, PAGE_TOKENS, 16)
     assert c.kv_groups[0].k.data_ptr() != c.kv_groups[1].k.data_ptr()
-    assert c.state[3].shape == (4, 3, 4) and 4 not in c.layer_group and 4 not in c.state
+    assert c.state[3].shape == (5, 3, 4) and 4 not in c.layer_group and 4 not in c.state     # 4 slots + the null slot
+    assert c.null_slot == 4 and not c.slots.holds(c.null_slot)
 
 
 def test_lengths_pages_and_release():

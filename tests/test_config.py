@@ -79,9 +79,9 @@ def test_spec_is_data_layer_by_layer():
     c = config_from_dict(TINY["B"]["config"])
     s = spec_of(c)
     assert len(s.layers) == 3 and s.schedule == (0, 1, 2)
-    assert s.layers[1].mixer.kind == "attention" and s.layers[1].feed_forward.kind == "gated_mlp"
-    assert s.layers[2].mixer.params["num_kv_heads"] == 1
-    assert s.layers[0].mixer.params["position"].params["scaling"]["factor"] == 4.0
+    assert s.layers[1].part("mixer").kind == "attention" and s.layers[1].part("feed_forward").kind == "gated_mlp"
+    assert s.layers[2].part("mixer").params["num_kv_heads"] == 1
+    assert s.layers[0].part("mixer").params["position"].params["scaling"]["factor"] == 4.0
     assert s.lm_head.params["name"] == "model.embed_tokens.weight"          # tied
     assert s.stop_token_ids == (3, 4)
     a = spec_of(config_from_dict(TINY["A"]["config"]))
@@ -124,7 +124,7 @@ def test_layer_hook_brackets_every_run_of_the_schedule():
     model.blocks = [Block(i) for i in range(len(spec.layers))]
     model.final_norm = SimpleNamespace(forward=lambda stream, rows=None: "h")
     model.head = SimpleNamespace(forward=lambda h: "logits")
-    model.layer_cache = lambda run, cache, step: None
+    model.layer_caches = lambda run, cache, step: []
     step = SimpleNamespace(n_want=1, want_rows=None)
     assert model.forward(step, None) == "logits"
     assert log == [("layer", 0), ("layer", 1), ("layer", 0)]
@@ -141,62 +141,3 @@ def test_benchmark_layer_times_are_means_per_run():
     assert layer_times([(0, 1.0), (1, 2.0), (0, 3.0), (1, 4.0)], 3) == [2.0, 3.0, 0.0]
     args = build_parser().parse_args(["model", "-p", "1,2", "--benchmark", "-n", "4"])
     assert args.benchmark and not args.benchmark_ctx and args.max_tokens == 4
-
-
-def test_benchmark_mode_runs_its_course_with_stand_ins(monkeypatch, capsys):
-    """`--benchmark` end to end with a stand-in engine, events and argmax (no device): the hook is set while it
-    runs and taken away afterwards, every iteration starts from a fresh slot, and the table has a row per run of
-    the schedule."""
-    from types import SimpleNamespace
-    import torch
-    import picolm_b200.api as api
-    import picolm_b200.ops as ops
-    from picolm_b200 import cli
-
-    clock = [0.0]
-
-    class Event:
-        def __init__(self, enable_timing=False):
-            self.t = None
-
-        def record(self):
-            clock[0] += 0.5
-            self.t = clock[0]
-
-        def elapsed_time(self, other):
-            return other.t - self.t
-
-    part = SimpleNamespace(weight_bytes=lambda: 2_000_000)
-    block = SimpleNamespace(parts=lambda: [("mixer", part), ("ffn", part)])
-    model = SimpleNamespace(spec=SimpleNamespace(schedule=[0, 1, 0]), blocks=[block, block], layer_hook=None)
-    calls = {"new": 0, "end": 0, "steps": 0}
-
-    def run_layers():
-        assert model.layer_hook is not None
-        for run, layer in enumerate(model.spec.schedule):
-            model.layer_hook(run, layer, False)
-            model.layer_hook(run, layer, True)
-        calls["steps"] += 1
-        return torch.zeros(1, 8)
-
-    def new_sequence():
-        calls["new"] += 1
-        return 0
-
-    def end_sequence(slot):
-        calls["end"] += 1
-
-    engine = SimpleNamespace(model=model, cache=SimpleNamespace(max_seq_tokens=6), new_sequence=new_sequence,
-                             end_sequence=end_sequence, synchronize=lambda: None, step=lambda entries: run_layers(),
-                             step_device_tokens=lambda slots, tok: run_layers(),
-                             token_buffer=lambda n: torch.zeros(n, dtype=torch.int32))
-    monkeypatch.setattr(torch.cuda, "Event", Event)
-    monkeypatch.setattr(api, "model_load", lambda *a, **k: engine)
-    monkeypatch.setattr(ops, "argmax", lambda logits, out=None: torch.zeros(1, dtype=torch.int32))
-    assert cli.main(["model", "-p", "1,2,3", "-n", "9", "--benchmark"]) == 0
-    assert model.layer_hook is None
-    assert calls == {"new": 3, "end": 3, "steps": 3 * (1 + 3)}          # 6 - 3 = 3 tokens fit the context
-    err = capsys.readouterr().err
-    assert err.count("=== iteration") == 3 and err.count("layer,prefill_ms") == 3
-    rows = [l for l in err.splitlines() if l.startswith(("0,", "1,"))]
-    assert len(rows) == 9 and rows[0] == "0,0.500,0.5000,4.0,8"          # 4 MB in 0.5 ms = 8 GB/s

@@ -182,3 +182,102 @@ def test_graph_size_and_length_classes():
         last = c
     assert len(classes) <= 40
     assert length_class(100, 64) == 64                              # never beyond the longest sequence of the cache
+
+
+class LateCopyEngine(StretchEngine):
+    """A fake engine with a token buffer of its own whose copies to the host run as late as they may:
+    when their event is waited for.  If the buffer has been written in between, the copy would carry
+    other ids than were sampled: the stand-in raises.  `guard` says whether a write of the buffer first
+    waits for the pending copy, as `Engine.before_token_write` does."""
+
+    class Copy:
+        def __init__(self, src, row):
+            self.src, self.row, self.seen, self.done = src, row, src.clone(), False
+
+        def synchronize(self):
+            if not self.done:
+                import torch
+                assert torch.equal(self.src, self.seen), "the token buffer was overwritten before its copy to the host ran"
+                self.row.copy_(self.src)
+                self.done = True
+
+    def __init__(self, guard=True, **kw):
+        import torch
+        super().__init__(**kw)
+        self.buf = torch.zeros(self.cache.max_seqs, dtype=torch.int32)
+        self.pending, self.guard = None, guard
+
+    def token_buffer(self, n):
+        return self.buf[:n]
+
+    def before_token_write(self):
+        if self.pending is not None:
+            self.pending.synchronize()
+            self.pending = None
+
+    def step_device_tokens(self, slots, tokens):
+        n = len(slots)
+        if tokens.data_ptr() != self.buf.data_ptr():          # the batch shrank: other rows than the buffer holds
+            if self.guard:
+                self.before_token_write()
+            self.buf[:n] = tokens
+        out = super().step_device_tokens(slots, self.buf[:n])
+        self.before_token_write()                             # the sampler that follows writes the buffer
+        return out
+
+    def fetch_later(self, tokens, row):
+        self.pending = self.Copy(tokens, row)
+        return self.pending
+
+
+class BufferSampler(TensorSampler):
+    def sample(self, logits, out=None):
+        import torch
+        t = torch.as_tensor(logits, dtype=torch.int32)
+        if out is None:
+            return t
+        out.copy_(t)
+        return out
+
+
+def test_the_token_buffer_is_not_written_under_a_pending_copy():
+    """A sequence that leaves the batch from its first row (here: its context is full) makes the loop
+    regroup the ids on the device and write them into the engine's token buffer; that write has to wait
+    for the last copy of the buffer to the host."""
+    prompts = [[90] * 97, [10, 11, 12], [45], [20] * 40]
+    want, _ = generate(FakeEngine(max_seqs=4, max_tokens=64 * 6), prompts, max_tokens=7,
+                       sampling=SamplingParams(temperature=0.0), sampler_factory=FakeSampler, steps_per_sync=1)
+    assert [len(o) for o in want] == [4, 7, 5, 7]
+    eng = LateCopyEngine(max_seqs=4, max_tokens=64 * 6)
+    outs, _ = generate(eng, prompts, max_tokens=7, sampling=SamplingParams(temperature=0.0),
+                       sampler_factory=BufferSampler, steps_per_sync=3)
+    assert outs == want
+    with pytest.raises(AssertionError, match="overwritten before its copy"):
+        generate(LateCopyEngine(guard=False, max_seqs=4, max_tokens=64 * 6), prompts, max_tokens=7,
+                 sampling=SamplingParams(temperature=0.0), sampler_factory=BufferSampler, steps_per_sync=3)
+
+
+def test_more_sequences_than_token_ids_are_refused():
+    """The engine's token buffer holds one id per sequence of the cache; a sampler's `out` that is not
+    exactly the batch's size is refused before any kernel writes it."""
+    import torch
+    from picolm_b200.engine.engine import Engine
+    from picolm_b200.ops import KernelError
+    from picolm_b200.ops.sampling import _token_out
+    eng = Engine.__new__(Engine)
+    eng._tokens = torch.zeros(300, dtype=torch.int32)
+    assert eng.token_buffer(257).numel() == 257
+    with pytest.raises(ValueError, match="at most 300"):
+        eng.token_buffer(301)
+    logits = torch.zeros((257, 8))
+    assert _token_out(None, 257, logits, "argmax").shape == (257,)
+    with pytest.raises(KernelError, match=r"int32 \[257\]"):
+        _token_out(torch.zeros(256, dtype=torch.int32), 257, logits, "argmax")
+    with pytest.raises(KernelError, match="int32"):
+        _token_out(torch.zeros(257, dtype=torch.int64), 257, logits, "sample")
+    # the loop with 257 sequences alive at once and a buffer sized by the cache
+    big = LateCopyEngine(max_seqs=257, max_tokens=64 * 257)
+    prompts = [[1 + i % 40] for i in range(257)]
+    outs, _ = generate(big, prompts, max_tokens=3, sampling=SamplingParams(temperature=0.0),
+                       sampler_factory=BufferSampler, steps_per_sync=2)
+    assert outs == [[p[0] + 1, p[0] + 2, p[0] + 3] for p in prompts]

@@ -118,3 +118,13 @@ def test_command_line(model_dirs):
     rows = [ln.split(",") for ln in r.stderr.splitlines() if re.fullmatch(r"\d+,[0-9.]+,[0-9.]+", ln)]
     assert "ctx_size,prefill_tok/s,gen_tok/s" in r.stderr
     assert [int(x[0]) for x in rows] == [0, 16, 32, 48] and all(float(x[1]) > 0 and float(x[2]) > 0 for x in rows)
+    # the reference's --benchmark: per iteration a row for every run of the schedule with the time of the layer
+    # in the prompt's step and in a decode step (events around every layer, on the device)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
+                        "-p", "5,6,7,8,9,10", "-n", "6", "--benchmark"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert r.stderr.count("=== iteration") == 3 and r.stderr.count("layer,prefill_ms,gen_ms") == 3
+    rows = [ln.split(",") for ln in r.stderr.splitlines() if re.fullmatch(r"\d+,[0-9.]+,[0-9.]+,[0-9.]+,\d+", ln)]
+    assert [int(x[0]) for x in rows] == [0, 1] * 3                     # two layers, three iterations
+    assert all(float(x[1]) > 0 and float(x[2]) > 0 and float(x[3]) > 0 for x in rows)
+    assert r.stderr.count("Prefill: 6 tokens") == 3 and r.stderr.count("Generation: 6 tokens") == 3

@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 def _register():
     from picolm_b200 import register_architecture, register_part
     from picolm_b200.cache import CacheSpec
-    from picolm_b200.config import LayerSpec, ModelSpec, PartSpec
+    from picolm_b200.config import ModelSpec, PartSpec
+    from picolm_b200.parts.block import pre_norm_layer
     from picolm_b200.parts import Part, WeightSpec
 
     @register_part("mixer", "toy_running_mean")
@@ -71,7 +72,7 @@ def _register():
                                       "o_name": "o.weight"}, prefix="attn")
 
         def layer(i, mixer, cache_of=None):
-            return LayerSpec(f"blocks.{i}", "pre_norm", mixer, ff, PartSpec("rmsnorm", norm, prefix="n1"),
+            return pre_norm_layer(f"blocks.{i}", mixer, ff, PartSpec("rmsnorm", norm, prefix="n1"),
                              PartSpec("rmsnorm", norm, prefix="n2"), cache_of=cache_of)
 
         return ModelSpec(
@@ -99,7 +100,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     eng = Engine.from_folder(d, dtype="float32", max_tokens=64 * 8, max_seqs=4)
     # the cache is kept per run of the schedule (0: toy state; 1 and 2: the two runs of the attention layer)
     assert sorted(eng.cache.state) == [0] and sorted(eng.cache.layer_group) == [1, 2]          # run 3 owns nothing
-    assert eng.cache.state[0].shape == (4, 33) and eng.cache.kv_groups[0].k.shape[0] == 2
+    assert eng.cache.state[0].shape == (5, 33) and eng.cache.kv_groups[0].k.shape[0] == 2
     a, b = random_tokens(50, 90, 1), random_tokens(21, 90, 2)
     whole_a, whole_b = run_whole(eng, a), run_whole(eng, b)
     assert torch.isfinite(whole_a).all() and whole_a.std() > 0

@@ -22,7 +22,8 @@ def _wave(pos: torch.Tensor, head_dim: int) -> torch.Tensor:
 
 def _register():
     from picolm_b200 import ops, register_architecture, register_part
-    from picolm_b200.config import LayerSpec, ModelSpec, PartSpec
+    from picolm_b200.config import ModelSpec, PartSpec
+    from picolm_b200.parts.block import pre_norm_layer
     from picolm_b200.parts import Part, WeightSpec
 
     @register_part("feed_forward", "toy_routed")
@@ -105,7 +106,7 @@ def _register():
                                  "pairing": "half", "max_positions": 256})
 
         def layer(i, mixer, ff):
-            return LayerSpec(f"blocks.{i}", "pre_norm", mixer, ff, PartSpec("rmsnorm", norm, prefix="n1"),
+            return pre_norm_layer(f"blocks.{i}", mixer, ff, PartSpec("rmsnorm", norm, prefix="n1"),
                              PartSpec("rmsnorm", norm, prefix="n2"))
 
         return ModelSpec(

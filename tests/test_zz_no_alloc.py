@@ -34,7 +34,7 @@ def _symbols():
 @pytest.mark.parametrize("T,F,K,out_dtype", [(8, 3072, 2048, torch.bfloat16), (33, 264, 1024, torch.float32),
                                               (64, 2048, 8192, torch.float32), (1, 4096, 512, torch.bfloat16)])
 def test_static_scratch_entry_matches_the_ordinary_one_twice(T, F, K, out_dtype):
-    from picolm_b200 import ops
+    from util import gemm_tc_workspace
     lib = _symbols()
     torch.manual_seed(T + F + K)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -44,7 +44,7 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice(T, F, K, out_dtype)
     for round_ in range(2):                                # the second call inherits the first one's partial sums
         x = (torch.randn(T, K) / K ** 0.25).to(torch.bfloat16).to(DEV)
         w = (torch.randn(F, K) / K ** 0.25).to(torch.bfloat16).to(DEV)
-        want = ops.gemm_tc(x, w, out_dtype)                # the existing entry point, workspace from torch
+        want = gemm_tc_workspace(x, w, out_dtype)          # the existing entry point, workspace from torch
         got = torch.full((T, F), float("nan"), dtype=out_dtype, device=DEV)
         before = torch.cuda.memory_allocated()
         rc = lib.plm_gemm_tc_static(x.data_ptr(), w.data_ptr(), got.data_ptr(), code, T, F, K, K, K, F, None, stream)

@@ -94,3 +94,27 @@ def assert_close(got, ref, dtype, what=""):
         assert_close_fp32(got, ref, what)
     else:
         assert_close_bf16(got, ref, what)
+
+
+def gemm_tc_workspace(a, w, out_dtype):
+    """out = a @ w^T through `plm_gemm_tc`, the exported split-K product for at most 64 rows that takes a
+    caller-allocated fp32 workspace (csrc/gemm_tc.cu), called through its C symbol with a workspace from
+    torch.  The engine does not use it; `plm_gemm_tc_static` is its twin without the workspace."""
+    import ctypes
+    from picolm_b200.csrc.build import load_library
+    lib = load_library("gemm_tc")
+    vp, i, l = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+    lib.plm_gemm_tc.argtypes = [vp, vp, vp, i, i, i, i, l, l, l, vp, vp, vp]
+    lib.plm_gemm_tc_plan.argtypes = [i, i, i, ctypes.POINTER(i), ctypes.POINTER(l)]
+    M, K = a.shape
+    N = w.shape[0]
+    splits, elems = i(0), l(0)
+    lib.plm_gemm_tc_plan(M, N, K, ctypes.byref(splits), ctypes.byref(elems))
+    ws = torch.empty((max(elems.value, 1),), dtype=torch.float32, device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    rc = lib.plm_gemm_tc(a.data_ptr(), w.data_ptr(), out.data_ptr(), 0 if out_dtype == torch.float32 else 1, M, N, K,
+                         K, K, N, ws.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, f"plm_gemm_tc returned {rc}"
+    assert int(status.item()) == 0
+    return out
