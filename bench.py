@@ -122,14 +122,71 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def reference_arm():
-    """The reference is a C program (Makefile, no Python package): the offline
-    pip install of it fails, and it reads GGUF files with a tokenizer, none of
-    which exist here."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "whoreson/picolm has no setup.py/pyproject.toml: `pip install --no-index "
-                                     "--target baseline/_ref <its checkout>` fails (not a Python project), and its "
-                                     "command line needs GGUF files and a tokenizer that do not exist offline"}))
+def reference_arm(args):
+    """whoreson/picolm itself on this GPU: its stock CUDA command line, built by its own Makefile into
+    baseline/_ref, on a GGUF file with random bfloat16 weights of the benchmark's shape (baseline/reference_arm.py).
+    The reference serves one sequence at a time, so its decode rate is a batch-1 rate; `--steps` is the number of
+    tokens it generates in the timed run, `--warmup` counts short runs before it."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as R
+    cfg_dict, context, prompt_len, seed, model_name = bench_config(args.config)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    prefill_tokens = min(2048, context)
+    new_tokens = max(args.steps, 16)
+    try:
+        binary = R.build()
+        with tempfile.TemporaryDirectory() as tmp:
+            gguf = os.path.join(tmp, "model.gguf")
+            t0 = time.time()
+            size = R.write_gguf(gguf, dict(cfg_dict, context=context), seed)
+            print(f"[bench] wrote {size / 1e9:.2f} GB of GGUF in {time.time() - t0:.0f} s", file=sys.stderr)
+            gpu = True
+            try:
+                small = R.run(binary, gguf, 16, 8, context, gpu=True, timeout=900)       # a small run first
+                if small["backend"] != "cuda":
+                    raise R.Unavailable("the reference's GPU backend did not initialise: " + "; ".join(small["stderr_head"]))
+            except (R.Unavailable, subprocess.TimeoutExpired) as e:
+                # its GPU path is not run again; the same binary without PICOLM_GPU is its CPU path
+                print(f"[bench] the reference's GPU path failed ({e}); running its CPU path", file=sys.stderr)
+                gpu = False
+                small = R.run(binary, gguf, 16, 8, context, gpu=False, timeout=900)
+            for _ in range(max(args.warmup - 1, 0)):
+                R.run(binary, gguf, 16, 8, context, gpu=gpu, timeout=900)
+            with ClockSampler() as sampler:
+                res = R.run(binary, gguf, prefill_tokens, new_tokens, context, gpu=gpu, seed=seed, timeout=1800)
+            clocks = sampler.summary()
+    except R.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's command line did not finish in its time limit"}))
+        return 0
+    value = res["gen_tok_s"]
+    out = {
+        "metric": f"decode tokens/s ({model_name}, bf16, batch 1, 1 B200)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": res["gen_tokens"], "warmup": args.warmup,
+        "ms_per_step": round(1e3 / value, 4) if value > 0 else None, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random letter prompts, random-init weights N(0, 0.02)",
+        "impl": "reference",
+        "config": {"model": model_name, "layers": cfg_dict["num_hidden_layers"], "layers_in_config": full_layers,
+                   "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
+                   "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
+                   "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
+                   "tied": cfg_dict["tie_word_embeddings"], "global_batch": 1, "seq_len": context,
+                   "prompt_len": res["prefill_tokens"], "prefill_tokens": res["prefill_tokens"],
+                   "parallelism": "none (1 GPU)", "backend": res["backend"],
+                   "how": "stock picolm CLI (make cuda), PICOLM_GPU=1, -t 0 -s 42; its own Prefill:/Generation: lines"},
+        "clocks": clocks,
+        # the command line's own timing is end to end: text in, text out, one process
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "prefill_tokens_per_s": res["prefill_tok_s"]},
+        "prefill": {"value": res["prefill_tok_s"], "tokens": res["prefill_tokens"], "ms": round(res["prefill_s"] * 1e3, 1)},
+        "points": {"decode_b1": value},
+        "notes": res["stderr_head"],
+    }
+    print(json.dumps(out))
     return 0
 
 
@@ -155,12 +212,12 @@ def main():
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"picolm_b200 is a one-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return reference_arm(args)
 
     import torch
     from picolm_b200 import ops
