@@ -28,15 +28,19 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}     # an earlier measurement on this pool
 
 
+def baseline_text(index=2):
+    """The text of BASELINE.json's configs[index] ("" if it cannot be read)."""
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            return json.load(f)["configs"][index]
+    except (OSError, KeyError, IndexError, ValueError):
+        return ""
+
+
 def bench_config(index=2):
     """The sizes of BASELINE.json's configs[index] (2, the Llama-3.2-1B shape, unless asked otherwise),
     read from its text."""
-    text = ""
-    try:
-        with open(os.path.join(ROOT, "BASELINE.json")) as f:
-            text = json.load(f)["configs"][index]
-    except (OSError, KeyError, IndexError, ValueError):
-        pass
+    text = baseline_text(index)
 
     def num(pattern, default):
         m = re.search(pattern, text)
@@ -209,6 +213,9 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="which of BASELINE.json's configs gives the layer sizes (default 2, the headline)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 decode points")
+    ap.add_argument("--unequal", action="store_true",
+                    help="also time one step of eight prompts of 128 to 2,048 tokens (always done for a configuration "
+                         "that names an unequal batch)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
     args = ap.parse_args()
@@ -224,6 +231,7 @@ def main():
     from picolm_b200.api import generate
     from picolm_b200.config import config_from_dict
     from picolm_b200.engine import Engine
+    from picolm_b200.engine.generate import greedy_steps_in_flight
     from picolm_b200.weights import write_random_model
 
     cfg_dict, context, prompt_len, seed, model_name = bench_config(args.config)
@@ -243,7 +251,11 @@ def main():
         write_random_model(cfg, seed, tmp, norm_std=0.0)
         # the cache holds what the largest run needs (its prompts, warm-up and timed steps), not
         # max_b full contexts: at the 13B shape those would not fit the GPU
-        per_seq = min(context, (max(prompt_len, prefill_tokens) + 2 * args.warmup + 3 * args.steps + 16 + 63) // 64 * 64)
+        need = max(prompt_len, prefill_tokens) + 2 * args.warmup + 3 * args.steps + 16
+        per_seq = min(context, max((need + 63) // 64 * 64, prompt_len + 1536))
+        kv_tok = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * 2
+        while max_b * per_seq * kv_tok > 70e9 and per_seq > (need + 63) // 64 * 64:   # leave room for the weights
+            per_seq -= 64
         engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=max_b * per_seq, max_seqs=max_b,
                                     max_seq_tokens=context, use_graphs=False if args.no_graphs else None)
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr)
@@ -277,7 +289,18 @@ def main():
                "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ----------------------------------------------------------------- decode
+    w_bytes = engine.model.weight_bytes_per_step()
+    kv_per_token = engine.cache.kv_bytes_per_token()
+
     def decode_run(batch, steps, warmup, sample_clocks=False):
+        """Decode at `batch` after prompts of `prompt_len`: `warmup` steps, then untimed steps for at least
+        UNTIMED_S (the clocks dip after the prompts' step and come back), then R blocks of `steps` steps,
+        each block between two events, the blocks back to back without the host waiting in between; R is
+        chosen so that the blocks last at least TIMED_S together (as far as the context allows).  The median
+        block gives the step's time whatever `steps` is.  The timed steps feed each sampled token to the next
+        step on the device; the ids reach the host by a copy per step that nobody waits for until the end
+        (`greedy_steps_in_flight`, which the tests compare with `generate`)."""
+        UNTIMED_S, TIMED_S = 0.2, 0.5
         slots = [engine.new_sequence() for _ in range(batch)]
         ps = prompts(batch)
         toks = []
@@ -286,45 +309,88 @@ def main():
             toks += ops.argmax(logits).tolist()
         for _ in range(warmup):
             toks = ops.argmax(engine.step([(s, [t]) for s, t in zip(slots, toks)])).tolist()
-        n0 = ops.launch_count()
+        room = per_seq - prompt_len - warmup - 2                 # steps the cache still has room for
+        tok_dev = torch.tensor(toks, dtype=torch.int32, device="cuda:0")
+        # a first look at the step's time, to size what follows
+        probe = max(1, min(8, room // 8))
+        pinned = torch.empty((max(room, 1), batch), dtype=torch.int32).pin_memory()
         a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        tok_dev = greedy_steps_in_flight(engine, slots, tok_dev, probe, pinned)
+        b.record()
+        torch.cuda.synchronize()
+        est_ms = max(a.elapsed_time(b) / probe, 1e-3)
+        room -= probe
+        steps = max(1, min(steps, room // 2))
+        untimed = max(0, min(int(UNTIMED_S * 1e3 / est_ms) + 1, room - steps))
+        blocks = max(1, min(int(TIMED_S * 1e3 / (est_ms * steps)) + 1, (room - untimed) // steps))
+        tok_dev = greedy_steps_in_flight(engine, slots, tok_dev, untimed, pinned)
+        n0 = ops.launch_count()
         sampler = ClockSampler() if sample_clocks else None
         if sampler:
             sampler.__enter__()
-        # The timed steps feed each sampled token to the next step on the device; the ids reach the
-        # host by a copy per step that nobody waits for until the end (as the generation loop does).
-        pinned = torch.empty((steps, batch), dtype=torch.int32).pin_memory()
-        tok_dev = torch.tensor(toks, dtype=torch.int32, device="cuda:0")
+        marks = [ev() for _ in range(blocks + 1)]
         torch.cuda.synchronize()
-        a.record()
-        for j in range(steps):
-            tok_dev = ops.argmax(engine.step_device_tokens(slots, tok_dev), out=engine.token_buffer(batch))
-            engine.fetch_later(tok_dev, pinned[j])
-        b.record()
+        marks[0].record()
+        for r in range(blocks):
+            tok_dev = greedy_steps_in_flight(engine, slots, tok_dev, steps, pinned[r * steps:])
+            marks[r + 1].record()
         torch.cuda.synchronize()
         if sampler:
             sampler.__exit__()
-        ms = a.elapsed_time(b) / steps
-        launches = ops.launch_count() - n0
-        ctx_mean = prompt_len + warmup + (steps + 1) / 2.0
+        per_block = [marks[r].elapsed_time(marks[r + 1]) / steps for r in range(blocks)]
+        ms = statistics.median(per_block)
+        launches = (ops.launch_count() - n0) // blocks           # of one block of `steps` steps
+        ctx_mean = prompt_len + warmup + probe + untimed + (blocks * steps + 1) / 2.0
         for s in slots:
             engine.end_sequence(s)
-        return ms, launches, ctx_mean, (sampler.summary() if sampler else None)
+        achieved = (w_bytes + kv_per_token * ctx_mean * batch) / (ms * 1e-3) / 1e9
+        return {"ms": ms, "launches": launches, "ctx_mean": ctx_mean, "achieved": achieved,
+                "clocks": sampler.summary() if sampler else None, "steps": steps, "blocks": blocks,
+                "untimed_steps": warmup + probe + untimed,
+                "block_ms": [round(min(per_block), 4), round(ms, 4), round(max(per_block), 4)]}
 
-    ms, launches, ctx_mean, clocks = decode_run(B, args.steps, args.warmup, sample_clocks=True)
+    run = decode_run(B, args.steps, args.warmup, sample_clocks=True)
+    ms, launches, clocks = run["ms"], run["launches"], run["clocks"]
     value = B / ms * 1e3
-    w_bytes = engine.model.weight_bytes_per_step()
-    kv_bytes = engine.cache.kv_bytes_per_token() * ctx_mean * B
-    achieved = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
-    points = {}
+    roofline = {"bound": "hbm", "achieved": round(run["achieved"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(run["achieved"] / pk["hbm_gbs"], 4), "peaks": pk_src}
+    points, points_frac = {}, {}
     for pb in points_b:
-        pms, _, _, _ = decode_run(pb, min(args.steps, 32), args.warmup)
-        points[f"decode_b{pb}"] = round(pb / pms * 1e3, 1)
+        pr = decode_run(pb, args.steps, args.warmup)
+        points[f"decode_b{pb}"] = round(pb / pr["ms"] * 1e3, 1)
+        points_frac[f"decode_b{pb}"] = round(pr["achieved"] / pk["hbm_gbs"], 4)
+
+    # The unequal batch that the 8B configuration names: prompts of 128 to 2,048 tokens in one step.
+    if "Unequal batch" in baseline_text(args.config) or args.unequal:
+        lens = [128 + (2048 - 128) * i // 7 for i in range(8)]
+        lens = [min(n, per_seq) for n in lens]
+        times = []
+        for i in range(3 + 10):
+            slots = [engine.new_sequence() for _ in lens]
+            ps = [prompts(1, n)[0] for n in lens]
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            engine.step(list(zip(slots, ps)))
+            b.record()
+            torch.cuda.synchronize()
+            for sl in slots:
+                engine.end_sequence(sl)
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        ums = statistics.median(times)
+        total = sum(lens)
+        uflops = sum(prefill_flops(cfg_dict, n) for n in lens)
+        points["prefill_unequal_128_2048"] = round(total / ums * 1e3, 1)
+        points_frac["prefill_unequal_128_2048"] = round(uflops / (ums * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
 
     # ------------------------------------------- end to end, host ids in and out
-    gen_new = args.warmup + 2 * args.steps            # long enough to outlast the clock dip after the prompts' step
+    # long enough to outlast the clock dip after the prompts' step: about a second of decoding, as far as the
+    # cache has room
+    gen_new = max(args.warmup + 2 * args.steps, int(1000.0 / ms))
+    gen_new = max(8, min(gen_new, per_seq - prompt_len - 2))
     ps = prompts(B)
     generate(engine, ps, max_tokens=4, temperature=0.0, stop_ids=[], max_batch=B)            # warm-up
     engine.reset_counters()
@@ -348,7 +414,9 @@ def main():
                    "prefill_tokens": prefill_tokens, "parallelism": "none (1 GPU)",
                    "l2": f"every step reads all weights ({w_bytes / 1e9:.1f} GB > 126 MB L2); no flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
-        "points": points,
+        "points": points, "points_roofline": points_frac,
+        "window": {"blocks": run["blocks"], "steps_per_block": run["steps"], "untimed_steps_before": run["untimed_steps"],
+                   "block_ms_min_median_max": run["block_ms"]},
     }
     print(json.dumps(out))
     return 0
