@@ -91,7 +91,7 @@ int plm_sample(plm_ctx* ctx, const float* logits, int rows, const plm_sampling* 
 /* Generate up to `max_new` tokens for each of `n_prompts` prompts: batches of unequal prompts in one step,
  * then one token each; a sequence ends with a stop token (recorded, not fed), at max_new, or when its
  * context is full; as many batches one after another as the slots and the cache allow.  `stop_ids` NULL:
- * the model's own end-of-sequence ids.  `out_tokens[i]` must have room for max_new ints; `out_lens[i]`
+ * the model's own end-of-sequence ids (a non-NULL pointer with n_stop 0: no stop tokens).  `out_tokens[i]` must have room for max_new ints; `out_lens[i]`
  * receives how many were generated.  All slots of the context must be empty. */
 int plm_generate(plm_ctx* ctx, int n_prompts, const int* const* prompts, const int* prompt_lens, int max_new,
                  const plm_sampling* sampling, const int* stop_ids, int n_stop, int* const* out_tokens, int* out_lens);
