@@ -194,7 +194,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     if ((int)blockIdx.x >= n_tiles) return;
     const int tile = n_tiles - 1 - blockIdx.x;        // the longest tiles first
     const int row0 = tile * 64;
-    const int kv_len = seq_kv_len[b];
+    const int kv_len = PLM_POSITION(seq_kv_len[b] - 1) + 1;
     const int pos0 = kv_len - n_new;                  // position of the sequence's first new token
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)b * max_pages;
@@ -221,7 +221,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     const int n_pages = page_last - page_first + 1;
 
     auto issue = [&](int i) {                          // page i of this tile's range into stage i % PF_STAGES
-        const size_t base = ((size_t)pages[page_first + i] * G + g) * PLM_PAGE * HD;
+        const size_t base = ((size_t)PLM_PAGE_NO(pages[page_first + i]) * G + g) * PLM_PAGE * HD;
         const int valid = kv_len - (page_first + i) * PLM_PAGE;
         load_tile(k_s + (i % PF_STAGES) * TILE_ELEMS, kc + base, valid);
         load_tile(v_s + (i % PF_STAGES) * TILE_ELEMS, vc + base, valid);
@@ -352,7 +352,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int R = H / G;
     const int h0 = g * R + rg * 16;                     // first head of this row group
     const int n_rows = min(16, R - rg * 16);
-    const int pos = tok_pos[t];
+    const int pos = PLM_POSITION(tok_pos[t]);
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int page_first = lo / PLM_PAGE, page_last = pos / PLM_PAGE;
     const int total_pages = page_last - page_first + 1;
@@ -361,10 +361,10 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int p_end = min(page_last + 1, p_begin + per);
     const int n_pages = p_end - p_begin;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
+    const int* pages = block_table + (size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages;
 
     auto issue = [&](int i) {
-        const size_t base = ((size_t)pages[p_begin + i] * G + g) * PLM_PAGE * HD;
+        const size_t base = ((size_t)PLM_PAGE_NO(pages[p_begin + i]) * G + g) * PLM_PAGE * HD;
         const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
         load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
         load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
@@ -428,8 +428,9 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
             const int in_page = pos - page_last * PLM_PAGE;
             bf16* k_row = k_s + (i % DC_STAGES) * TILE_ELEMS + in_page * LDS;
             bf16* v_row = v_s + (i % DC_STAGES) * TILE_ELEMS + in_page * LDS;
-            const size_t cache_row = (((size_t)pages[page_last] * G + g) * PLM_PAGE + in_page) * HD;
-            const bool to_cache = rg == 0 && pages[page_last] > 0;       // page 0 is the null page of padding rows
+            const int own_page = PLM_PAGE_NO(pages[page_last]);
+            const size_t cache_row = (((size_t)own_page * G + g) * PLM_PAGE + in_page) * HD;
+            const bool to_cache = rg == 0 && own_page > 0;       // page 0 is the null page of padding rows
             if (threadIdx.x < GRP) {
                 const int j = threadIdx.x * 8;
                 uint4 lo = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + g) * HD + j);
@@ -574,7 +575,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
 // 9 query rows (8 heads and a row of zeros) make room for a fourth CTA on an SM.  That pays where the grid
 // is several waves long (large batches: a third more bytes in flight); a grid of one wave runs better with
 // three, which leave room for the CTAs of the kernel behind it to ask for their weights meanwhile.
-int decode_q_rows(int heads_per_kv_head, long ctas) { return heads_per_kv_head <= 8 && ctas > 3 * 148 ? 9 : 16; }
+int decode_q_rows(int heads_per_kv_head, long ctas) { return heads_per_kv_head <= 8 && ctas > 3 * PLM_SM_COUNT ? 9 : 16; }
 
 template <typename K>
 int set_smem(K kern, size_t bytes) {

@@ -32,8 +32,8 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
     const int h = blockIdx.y * WARPS + warp;
     if (h >= H) return;                             // warp-level exit; no block barrier below
     const int g = h / (H / G);
-    const int pos = tok_pos[t];
-    const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
+    const int pos = PLM_POSITION(tok_pos[t]);
+    const int* pages = block_table + (size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages;
     float* qs = q_sm + warp * hd;
     const Ta* qrow = q + ((size_t)t * H + h) * hd;
     for (int i = lane; i < hd; i += 32) qs[i] = to_f32<Ta>(qrow[i]);
@@ -50,7 +50,7 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
         float s = -1e30f;
         const bool valid = key <= pos;
         if (valid) {
-            const int page = pages[key / PLM_PAGE];
+            const int page = PLM_PAGE_NO(pages[key / PLM_PAGE]);
             const Tc* kr = kc + (((size_t)page * G + g) * PLM_PAGE + key % PLM_PAGE) * hd;
             float dot = 0.f;
             for (int i = 0; i < hd; ++i) dot = fmaf(qs[i], to_f32<Tc>(kr[i]), dot);
@@ -66,7 +66,7 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
         for (int j = 0; j < n_keys; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const int kj = base + j;
-            const int page = pages[kj / PLM_PAGE];
+            const int page = PLM_PAGE_NO(pages[kj / PLM_PAGE]);
             const Tc* vr = vc + (((size_t)page * G + g) * PLM_PAGE + kj % PLM_PAGE) * hd;
 #pragma unroll
             for (int i = 0; i < MAX_HD / 32; ++i) {

@@ -162,7 +162,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_tiles = (n_new + BQ - 1) / BQ;
     if (rank_of_tile >= n_tiles) return;
     const int tile = n_tiles - 1 - rank_of_tile;
-    const int kv_len = seq_kv_len[b];
+    const int kv_len = PLM_POSITION(seq_kv_len[b] - 1) + 1;
     const int pos0 = kv_len - n_new + tile * BQ;                         // position of the tile's first row
     const int rows = min(BQ, n_new - tile * BQ);
     const int g = h / (H / G);
@@ -208,7 +208,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (*(volatile int*)&s_abort) break;
                 if (!mbar_wait(kv_empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; break; }
                 mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
-                const int row = (pages[page_first + i] * G + g) * BKV;
+                const int row = (PLM_PAGE_NO(pages[page_first + i]) * G + g) * BKV;
                 const uint32_t k_dst = kv_smem + s * STAGE_BYTES, v_dst = k_dst + K_BYTES;
 #pragma unroll
                 for (int cb = 0; cb < CB; ++cb) {

@@ -16,6 +16,12 @@
 #define PLM_ERR_ALIGN (-3)
 #define PLM_ERR_UNSUPPORTED (-4)
 
+// SMs of a B200, the one target of these kernels (sm_100a): what grids, split factors and wave sizes are
+// planned for.  A plan must not depend on the device it is made on (the same shapes must give the same
+// order of sums everywhere), so this is a constant and not a device attribute; ops/_lib.py's SM_COUNT is
+// the same number (tests/test_config.py compares the two).
+#define PLM_SM_COUNT 148
+
 // dtype codes shared with the Python side
 #define PLM_F32 0
 #define PLM_BF16 1
@@ -139,6 +145,43 @@ __device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
 }
+
+// The checked build (-DPLM_CHECK; the serving build has none of this).  The kernels that follow indices
+// which the host computed (page numbers from a page table, a token's sequence and position, gathered rows)
+// compare every such index with its bound before they use it.  An index outside its bound is not followed:
+// the status word gets the kind of index (16 page, 17 sequence, 18 position, 19 row; the first one wins),
+// and index 0 is used in its place (page 0 is the cache's null page).  The bounds are set per library by
+// plm_check_bounds, on the stream, before the launches they are meant for; a bound of 0 is not checked.
+// This is what stands in for a memory checker where none can be run; the reference's counterparts are its
+// address-sanitizer build and its attention stress test (picolm/Makefile:249-250, picolm/picolm.c:661-761).
+#ifdef PLM_CHECK
+struct PlmBounds {
+    int n_pages, n_seqs, n_positions, n_rows;
+    int* status;
+};
+__device__ PlmBounds plm_bounds = {0, 0, 0, 0, nullptr};
+__device__ __forceinline__ int plm_checked(int v, int limit, int kind) {
+    if (limit > 0 && (unsigned)v >= (unsigned)limit) {
+        if (plm_bounds.status) atomicCAS(plm_bounds.status, 0, kind);
+        return 0;
+    }
+    return v;
+}
+#define PLM_PAGE_NO(p) plm_checked((p), plm_bounds.n_pages, 16)
+#define PLM_SEQ_NO(s) plm_checked((s), plm_bounds.n_seqs, 17)
+#define PLM_POSITION(p) plm_checked((p), plm_bounds.n_positions, 18)
+#define PLM_ROW_NO(r) plm_checked((r), plm_bounds.n_rows, 19)
+extern "C" int plm_check_bounds(int n_pages, int n_seqs, int n_positions, int n_rows, int* status, cudaStream_t stream) {
+    const PlmBounds b = {n_pages, n_seqs, n_positions, n_rows, status};
+    cudaError_t e = cudaMemcpyToSymbolAsync(plm_bounds, &b, sizeof(b), 0, cudaMemcpyHostToDevice, stream);
+    return e == cudaSuccess ? PLM_OK : (int)e;
+}
+#else
+#define PLM_PAGE_NO(p) (p)
+#define PLM_SEQ_NO(s) (s)
+#define PLM_POSITION(p) (p)
+#define PLM_ROW_NO(r) (r)
+#endif
 
 static inline int plm_status_of(cudaError_t e) { return e == cudaSuccess ? PLM_OK : (int)e; }
 

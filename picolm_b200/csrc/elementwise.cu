@@ -50,7 +50,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
-    const int src = rows ? rows[r] : r;
+    const int src = rows ? PLM_ROW_NO(rows[r]) : r;
     float* xr = x + (size_t)src * d;
     const float* dr = delta ? delta + (size_t)src * d : nullptr;
     float ss = 0.f;
@@ -97,7 +97,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
-    const int src = rows ? rows[r] : r;
+    const int src = rows ? PLM_ROW_NO(rows[r]) : r;
     float* xr = x + (size_t)src * d;
     const float* dr = delta ? delta + (size_t)src * d : nullptr;
     float4 v[4];
@@ -211,7 +211,7 @@ extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int 
     if (F <= 0) return PLM_ERR_SHAPE;
     const size_t total = (size_t)n_rows * F;
     int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > PLM_SM_COUNT * 16) blocks = PLM_SM_COUNT * 16;
     if (dtype == PLM_F32)
         return plm_status_of(launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, F, total));
     if (dtype == PLM_BF16)
@@ -237,7 +237,7 @@ __global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int pos = tok_pos[t];
+    const int pos = PLM_POSITION(tok_pos[t]);
     const int half = hd / 2, rot_half = rot_dim / 2;
     const int n_heads = H + 2 * G;
     const Ta* row = qkv + (size_t)t * n_heads * hd;
@@ -245,7 +245,7 @@ __global__ void rope_store_kernel(const Ta* __restrict__ qkv, Ta* __restrict__ q
     int in_page = 0;
     bool have_page = false;
     if (store) {
-        const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / PLM_PAGE];
+        const int page = PLM_PAGE_NO(block_table[(size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages + pos / PLM_PAGE]);
         have_page = page >= 0;
         page_base = (size_t)(page < 0 ? 0 : page) * G;
         in_page = pos % PLM_PAGE;
@@ -302,7 +302,7 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int pos = tok_pos[t];
+    const int pos = PLM_POSITION(tok_pos[t]);
     const int half = hd / 2, groups = half / 8;
     const int n_heads = H + 2 * G;
     const bf16* row = qkv + (size_t)t * n_heads * hd;
@@ -310,7 +310,7 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
     int in_page = 0;
     bool have_page = false;
     if (store) {
-        const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / PLM_PAGE];
+        const int page = PLM_PAGE_NO(block_table[(size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages + pos / PLM_PAGE]);
         have_page = page >= 0;
         page_base = (size_t)(page < 0 ? 0 : page) * G;
         in_page = pos % PLM_PAGE;

@@ -253,7 +253,7 @@ extern "C" int plm_gemm_tc_plan(int T, int F, int K, int* splits_out, long* work
         const int bn = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         const int tiles = ((F + BM - 1) / BM) * ((T + bn - 1) / bn);
         const int n_kb = (K + BK - 1) / BK;
-        int want = (2 * 148 + tiles - 1) / tiles;              // about two CTAs per SM
+        int want = (2 * PLM_SM_COUNT + tiles - 1) / tiles;              // about two CTAs per SM
         if (want > n_kb / 2) want = n_kb / 2;                  // at least two K blocks per split
         if (want < 1) want = 1;
         const int per = (n_kb + want - 1) / want;

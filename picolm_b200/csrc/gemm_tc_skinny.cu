@@ -44,6 +44,17 @@ __host__ __device__ constexpr size_t skinny_smem(int bn) {
     return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + (size_t)bn * BM * 4 + 1024 + 256;
 }
 
+// A test build only (-DPLM_TEST_STALL, never the library that serves): while the switch is on, the producer
+// announces 64 bytes more for every stage than it loads, so no stage ever fills.  Every wait of the kernel
+// then runs out: the kernel must record that in the status word, let what it has in flight land, free its
+// tensor memory and return.  Nothing faults and nothing is left running.
+#ifdef PLM_TEST_STALL
+__device__ int plm_stall_switch = 0;
+#define PLM_STALL_BYTES (plm_stall_switch ? 64u : 0u)
+#else
+#define PLM_STALL_BYTES 0u
+#endif
+
 constexpr int SS_STRIDE = 64;   // tokens per row of the partial sums of squares that this kernel writes (the most it takes)
 
 // W: [F, K] (P operand, 128 rows per tile), X: [T, K] (Q operand, BN rows).  grid = (F tiles, 1, S),
@@ -113,7 +124,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const int early = n_kb < STAGES ? n_kb : STAGES;
         if (lane == 0) {
             for (int i = 0; i < early; ++i) {                      // weights: nobody in this step writes them
-                mbar_expect_tx(full0 + 8 * i, W_BYTES + X_BYTES);
+                mbar_expect_tx(full0 + 8 * i, W_BYTES + X_BYTES + PLM_STALL_BYTES);
                 tma_load_2d(w_smem + i * W_BYTES, &map_w, full0 + 8 * i, (kb_begin + i) * BK, p0);
             }
         }
@@ -129,7 +140,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 const uint32_t phase = (i / STAGES) & 1;
                 if (*(volatile int*)&s_abort) break;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1, status, 1)) { s_abort = 1; break; }
-                mbar_expect_tx(full0 + 8 * s, W_BYTES + X_BYTES);
+                mbar_expect_tx(full0 + 8 * s, W_BYTES + X_BYTES + PLM_STALL_BYTES);
                 const int k = (kb_begin + i) * BK;
                 tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, k, p0);
                 tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, k, 0);
@@ -388,13 +399,19 @@ int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, OutT* out,
 
 }  // namespace
 
+#ifdef PLM_TEST_STALL
+extern "C" int plm_test_stall(int on, cudaStream_t stream) {
+    return plm_status_of(cudaMemcpyToSymbolAsync(plm_stall_switch, &on, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
+}
+#endif
+
 // How many CTAs share a tile's K range: the largest power of two (at most 8) that keeps the grid
 // within one wave of two CTAs per SM and leaves every CTA at least two K blocks.  Fixed by (F, K).
 extern "C" int plm_gemm_tc_skinny_splits(int F, int K) {
     const int tiles = (F + BM - 1) / BM;
     const int n_kb = (K + BK - 1) / BK;
     int S = MAX_SPLITS;
-    while (S > 1 && (tiles * S > 2 * 148 || n_kb < 2 * S)) S >>= 1;
+    while (S > 1 && (tiles * S > 2 * PLM_SM_COUNT || n_kb < 2 * S)) S >>= 1;
     return S;
 }
 

@@ -276,7 +276,7 @@ int sm_count() {
     if (!n) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
+            n = PLM_SM_COUNT;
     }
     return n;
 }

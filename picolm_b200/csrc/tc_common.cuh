@@ -12,7 +12,10 @@ constexpr int BM = 128;                  // rows of P per tile (TMEM lanes)
 constexpr int BK = 64;                   // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;   // polls of mbarrier.try_wait before giving up
+#ifndef PLM_WAIT_LIMIT
+#define PLM_WAIT_LIMIT (1u << 24)        // a test build shortens it so that a wait that runs out does so at once
+#endif
+constexpr uint32_t WAIT_LIMIT = PLM_WAIT_LIMIT;   // polls of mbarrier.try_wait before giving up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

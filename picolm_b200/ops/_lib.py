@@ -3,6 +3,7 @@ error codes, the launch counter, argument helpers and the device status word of 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -35,10 +36,18 @@ _SIGNATURES = {
     "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "plm_check_bounds": [_i, _i, _i, _i, _vp, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
 }
 _fn_cache = {}
+
+# The checked build of the kernels that follow host-computed indices (csrc/common.cuh, PLM_CHECK): with
+# PICOLM_B200_CHECK=1 in the environment these libraries are compiled with -DPLM_CHECK, and the faces in
+# this package hand them the bounds before every launch.  An index outside its bound is then recorded in
+# the status word (`check_status` raises) instead of being followed.
+CHECKED = os.environ.get("PICOLM_B200_CHECK", "") == "1"
+CHECKED_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "attention_tc")
 
 
 class KernelError(RuntimeError):
@@ -50,6 +59,9 @@ _CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", 
 
 
 def _fn(library: str, name: str, extra_flags=()):
+    if CHECKED and library.split("@")[0] in CHECKED_LIBRARIES:
+        library = library + ("_check" if "@" in library else "@check")
+        extra_flags = tuple(extra_flags) + ("-DPLM_CHECK",)
     key = (library, name, tuple(extra_flags))
     f = _fn_cache.get(key)
     if f is None:
@@ -142,7 +154,7 @@ def _i32(t: torch.Tensor, name: str) -> None:
         raise KernelError(f"{name} must be int32, got {t.dtype}")
 
 
-SM_COUNT = 148              # SMs of a B200: what grids are sized for
+SM_COUNT = 148              # SMs of a B200: what grids are sized for; PLM_SM_COUNT in csrc/common.cuh
 
 _status = {}
 
@@ -158,6 +170,19 @@ def status_word(device) -> torch.Tensor:
     return t
 
 
+def set_bounds(library: str, extra_flags=(), *, n_pages: int = 0, n_seqs: int = 0, n_positions: int = 0,
+               n_rows: int = 0, device=None) -> None:
+    """In the checked build: tell `library` the bounds of the indices that its next launches follow (pages
+    of the cache, sequences of the step, positions a sequence may have, rows that may be gathered; 0: not
+    checked).  Nothing happens in the serving build."""
+    if not CHECKED or library.split("@")[0] not in CHECKED_LIBRARIES:
+        return
+    code = _fn(library, "plm_check_bounds", extra_flags)(
+        int(n_pages), int(n_seqs), int(n_positions), int(n_rows), _p(status_word(device or "cuda:0")), _stream())
+    if code:
+        raise KernelError(f"plm_check_bounds: CUDA error {code}")
+
+
 def check_status(device="cuda:0") -> None:
     """Raise if a kernel gave up a bounded wait since the last check (this
     synchronises with the device)."""
@@ -167,6 +192,10 @@ def check_status(device="cuda:0") -> None:
     code = int(t.item())
     if code:
         t.zero_()
+        if code >= 16:
+            what = {16: "page number", 17: "sequence index", 18: "position", 19: "row index"}.get(code, str(code))
+            raise KernelError(f"a kernel of the checked build met a {what} outside its bounds and did not follow it; "
+                              f"its output is not valid")
         where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
         raise KernelError(f"a tensor-core kernel gave up waiting on an mbarrier ({where}); its output is not valid")
 

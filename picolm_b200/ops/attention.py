@@ -7,7 +7,8 @@ from typing import Optional
 import torch
 
 from ..csrc.build import attention_variant
-from ._lib import PAGE_TOKENS, SM_COUNT, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, status_word
+from ._lib import (PAGE_TOKENS, SM_COUNT, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, set_bounds,
+                   status_word)
 
 
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
@@ -24,10 +25,17 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
         raise KernelError(f"attention: head_dim {hd} exceeds 256, the largest this kernel takes")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    _cache_bounds("attention_simt", (), k_cache, block_table)
     _check(_fn("attention_simt", "plm_attention_rows")(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _dt(q, "q"), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _stream()), "attention_rows")
     return out
+
+
+def _cache_bounds(library, flags, k_cache, block_table) -> None:
+    """The checked build's bounds for a kernel that walks `block_table` into `k_cache`."""
+    set_bounds(library, flags, n_pages=k_cache.shape[0], n_seqs=block_table.shape[0],
+               n_positions=block_table.shape[1] * PAGE_TOKENS, device=k_cache.device)
 
 
 def attention_mma_supported(q: torch.Tensor) -> bool:
@@ -59,6 +67,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
     lib, flags = attention_variant(hd)
+    _cache_bounds(lib, flags, k_cache, block_table)
     _check(_fn(lib, "plm_attn_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale), int(window or 0),
@@ -84,6 +93,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
     lib, flags = attention_variant(hd, "attention_tc")
+    _cache_bounds(lib, flags, k_cache, block_table)
     _check(_fn(lib, "plm_attn_tc_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], k_cache.shape[0], T, seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale),
@@ -146,6 +156,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     scratch = n_splits > 1 and (scratch or n_splits > DECODE_CLUSTER_SPLITS)
     ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=q.device) if scratch else None
     lib, flags = attention_variant(hd)
+    _cache_bounds(lib, flags, k_cache, block_table)
     _check(_fn(lib, "plm_attn_decode", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
@@ -193,6 +204,7 @@ def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_he
     out = torch.empty((T, H * hd), dtype=qkv.dtype, device=qkv.device)
     ws = torch.empty((T * H * n_splits * (hd + 2),), dtype=torch.float32, device=qkv.device) if scratch else None
     lib, flags = attention_variant(hd)
+    _cache_bounds(lib, flags, kv.k, kv.block_table)
     _check(_fn(lib, "plm_attn_decode_rope", flags)(
         _p(qkv), _p(kv.k), _p(kv.v), _p(out), _p(ws), _p(rotation.cos), _p(rotation.sin), _p(step.tok_pos),
         _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, float(scale), int(kv.window or 0),

@@ -5,7 +5,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import PAGE_TOKENS, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream
+from ._lib import PAGE_TOKENS, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, set_bounds
 
 
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -45,6 +45,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         n_rows = rows.numel()
     if out is None:
         out = torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
+    set_bounds("elementwise", n_rows=T, device=x.device)
     _check(_fn("elementwise", "plm_rmsnorm")(
         _p(x), _p(delta), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
         float(eps), _stream()), "rmsnorm")
@@ -90,6 +91,8 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
             raise KernelError("rope_store: cos/sin tables must be float32 [positions, rotary_dim/2]")
     if pairing not in ("half", "adjacent"):
         raise KernelError(f"rope_store: unknown pairing {pairing!r}")
+    set_bounds("elementwise", n_pages=k_cache.shape[0] if store else 0, n_seqs=block_table.shape[0],
+               n_positions=block_table.shape[1] * PAGE_TOKENS, device=qkv.device)
     _check(_fn("elementwise", "plm_rope_store")(
         _p(qkv), _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None, _dt(qkv, "qkv"),
         _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1], T, H, G, hd,

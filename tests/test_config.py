@@ -141,3 +141,18 @@ def test_benchmark_layer_times_are_means_per_run():
     assert layer_times([(0, 1.0), (1, 2.0), (0, 3.0), (1, 4.0)], 3) == [2.0, 3.0, 0.0]
     args = build_parser().parse_args(["model", "-p", "1,2", "--benchmark", "-n", "4"])
     assert args.benchmark and not args.benchmark_ctx and args.max_tokens == 4
+
+
+def test_one_sm_count_on_both_sides():
+    """Plans (K splits, waves, cluster sizes) are made for the B200's SM count on the Python side and in the
+    kernels' host code; both read it from one constant each, and the two agree."""
+    import os
+    import re
+    from picolm_b200.ops._lib import SM_COUNT
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "picolm_b200", "csrc")
+    with open(os.path.join(csrc, "common.cuh")) as f:
+        assert int(re.search(r"#define PLM_SM_COUNT (\d+)", f.read()).group(1)) == SM_COUNT
+    for name in os.listdir(csrc):
+        if name.endswith((".cu", ".cuh")):
+            with open(os.path.join(csrc, name)) as f:
+                assert not re.search(r"\b148\b", re.sub(r"#define PLM_SM_COUNT 148", "", f.read())), name
