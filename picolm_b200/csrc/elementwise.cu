@@ -189,9 +189,17 @@ extern "C" int plm_scale_rows(const void* x, const float* parts, int n_parts, in
                                     ld_parts, 1.0f / (float)size, eps, (bf16*)out, d));
 }
 
-// --------------------------------------------------------------------- SwiGLU
-// gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  out[T,F] = silu(gate) * up.
-template <typename T>
+// ----------------------------------------------------------- gated activation
+// gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  out[T,F] = act(gate) * up, with
+// ACT 0: silu(g) = g / (1 + expf(-g))                                  (picolm/tensor.c:3306-3315)
+// ACT 1: gelu(g) = 0.5 g (1 + tanhf(0.79788456 (g + 0.044715 g^3)))    (picolm/tensor.c:3317-3323)
+template <int ACT> __device__ __forceinline__ float gate_act(float g);
+template <> __device__ __forceinline__ float gate_act<0>(float g) { return g / (1.0f + expf(-g)); }
+template <> __device__ __forceinline__ float gate_act<1>(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.79788456f * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
     pdl_launch_dependents();
     pdl_wait();
@@ -202,20 +210,26 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int c = (int)(i - t * F);
         const float g = to_f32<T>(gu[t * 2 * F + c]);
         const float u = to_f32<T>(gu[t * 2 * F + F + c]);
-        out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+        out[i] = from_f32<T>(gate_act<ACT>(g) * u);
     }
 }
 
-extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int n_rows, int F, cudaStream_t stream) {
+template <typename T>
+static int launch_gated(int act, int blocks, cudaStream_t stream, const T* gu, T* out, int F, size_t total) {
+    if (act == 0) return plm_status_of(launch_pdl(swiglu_kernel<T, 0>, blocks, 256, 0, stream, gu, out, F, total));
+    if (act == 1) return plm_status_of(launch_pdl(swiglu_kernel<T, 1>, blocks, 256, 0, stream, gu, out, F, total));
+    return PLM_ERR_UNSUPPORTED;
+}
+
+// act: 0 silu, 1 gelu (tanh form)
+extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int act, int n_rows, int F, cudaStream_t stream) {
     if (n_rows <= 0) return PLM_OK;
     if (F <= 0) return PLM_ERR_SHAPE;
     const size_t total = (size_t)n_rows * F;
     int blocks = (int)((total + 255) / 256);
     if (blocks > PLM_SM_COUNT * 16) blocks = PLM_SM_COUNT * 16;
-    if (dtype == PLM_F32)
-        return plm_status_of(launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, F, total));
-    if (dtype == PLM_BF16)
-        return plm_status_of(launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, F, total));
+    if (dtype == PLM_F32) return launch_gated<float>(act, blocks, stream, (const float*)gu, (float*)out, F, total);
+    if (dtype == PLM_BF16) return launch_gated<bf16>(act, blocks, stream, (const bf16*)gu, (bf16*)out, F, total);
     return PLM_ERR_DTYPE;
 }
 

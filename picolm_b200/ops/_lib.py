@@ -19,7 +19,7 @@ _vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 _SIGNATURES = {
     "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
-    "plm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "plm_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],

@@ -52,16 +52,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """gate_up [T, 2F] (gate columns first) -> silu(gate) * up, [T, F]."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+    """gate_up [T, 2F] (gate columns first) -> act(gate) * up, [T, F]; `activation` "silu" or "gelu_tanh"
+    (the reference's two: picolm/tensor.c:3306-3323)."""
     _dev(gate_up, "gate_up")
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"activation {activation!r} has no kernel; known: {', '.join(GATE_ACTIVATIONS)}")
     T, F2 = gate_up.shape
     if F2 % 2:
         raise KernelError("gate_up must have an even number of columns")
     if out is None:
         out = torch.empty((T, F2 // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _check(_fn("elementwise", "plm_swiglu")(_p(gate_up), _p(out), _dt(gate_up, "gate_up"), T, F2 // 2, _stream()),
-           "swiglu")
+    _check(_fn("elementwise", "plm_swiglu")(_p(gate_up), _p(out), _dt(gate_up, "gate_up"),
+                                            GATE_ACTIVATIONS[activation], T, F2 // 2, _stream()), "swiglu")
     return out
 
 

@@ -16,13 +16,16 @@ from .mixer import _stack_rows
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(Part):
-    """params: hidden_size, intermediate_size, activation ("silu"),
-    gate_name/up_name/down_name (relative tensor names)."""
+    """params: hidden_size, intermediate_size, activation ("silu", or "gelu_tanh": the reference's gelu,
+    picolm/tensor.c:3317-3323), gate_name/up_name/down_name (relative tensor names).  The product whose
+    epilogue applies the activation exists for silu; any other activation runs as a kernel of its own
+    after a plain product."""
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
-        if self.params["activation"] != "silu":
-            raise ValueError(f"activation {self.params['activation']!r} has no kernel (silu only)")
+        if self.params["activation"] not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {self.params['activation']!r} has no kernel; known: "
+                             + ", ".join(ops.GATE_ACTIVATIONS))
 
     def weight_specs(self):
         p = self.params
@@ -39,7 +42,7 @@ class GatedMLP(Part):
         # One projection for both branches.  Where the tensor-core product can apply the activation
         # in its epilogue, the rows are laid out in tiles of 64 gate rows and their 64 up rows;
         # otherwise plainly [gate | up] with the activation as a kernel of its own.
-        self.fused = (gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape[0] % 64 == 0
+        self.fused = (p["activation"] == "silu" and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape[0] % 64 == 0
                       and gate.shape[1] % 8 == 0 and gate.shape[1] >= 64)
         self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else _stack_rows([gate, up])
         self.w_down = tensors[p["down_name"]]
@@ -54,5 +57,5 @@ class GatedMLP(Part):
         if self.fused:
             act = ops.linear_swiglu(h, self.w_gate_up)
         else:
-            act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype))
+            act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype), activation=self.params["activation"])
         return ops.linear(act, self.w_down, torch.float32, defer=True)

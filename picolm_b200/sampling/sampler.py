@@ -4,6 +4,11 @@ with the reference's defaults: temperature 0.8, top-p 0.9, top-k 40
 (picolm/picolm.c:774-776), min-p 0.05 (picolm/picolm.c:1230), seed 42 and seed 0
 read as 42 (picolm/sampler.c:43).
 
+The kept set and the weights are the reference's; the draw is not token-identical to it: the kernel walks
+the kept tokens in index order where the reference walks them in descending probability
+(picolm/sampler.c:112-121), so with the same seed and the same logits the two pick from the same
+distribution but not always the same token (tests/test_plain.py shows a case).
+
 Random numbers are the reference's xorshift64 (picolm/sampler.c:10-21).  The
 reference has one stream for its one sequence; here every sequence has a stream
 of its own, seeded `seed + index of the request`, so that what a request

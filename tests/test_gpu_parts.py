@@ -74,7 +74,17 @@ def test_feed_forward_part(dtype):
     assert torch.allclose(out.cpu(), ref, **_tol(dtype))
     with pytest.raises(ValueError, match="activation"):
         build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8,
-                                                          "activation": "gelu"}), rt)
+                                                          "activation": "relu"}), rt)
+    # the reference's other activation (picolm/tensor.c:3317-3323), through the same part
+    gelu = build_part("feed_forward", PartSpec("gated_mlp", {
+        "hidden_size": d, "intermediate_size": F, "activation": "gelu_tanh",
+        "gate_name": "g.weight", "up_name": "u.weight", "down_name": "d.weight"}), rt)
+    gelu.load({n: t.to(DEV) for n, t in w.items()})
+    act = 0.5 * gate * (1.0 + torch.tanh(0.79788456 * (gate + 0.044715 * gate ** 3))) * up
+    ref_gelu = P.linear(rnd(act), w["d.weight"].float())
+    got = gelu.forward(h.to(DEV), None)
+    got = got.compute() if hasattr(got, "compute") else got
+    assert torch.allclose(got.cpu(), ref_gelu, **_tol(dtype)) and not torch.allclose(ref_gelu, ref, atol=1e-3)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

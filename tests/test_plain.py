@@ -113,3 +113,49 @@ def test_sampler_chain_by_hand():
     s1, a = P.sample_reference_order(logits, 1.0, 3, 1.0, 0.0, 7)
     s2, b = P.sample_index_order(logits, 1.0, 3, 1.0, 0.0, 7)
     assert s1 == s2 and a in (0, 1, 2) and b in (0, 1, 2)
+
+
+def test_llama3_rule_on_the_tiny_configuration_by_hand():
+    """The scaling rule on Tiny B's numbers (theta 500000, head size 32, factor 4, low 1, high 4, original
+    context 64), against values worked out by hand from the published rule rather than by either
+    implementation: the 16 wavelengths 2 pi theta^(i/16) start 6.28, 14.27, 32.40, 73.58; 6.28 and 14.27 lie
+    below 64/4 = 16 and are kept; 73.58 and all later ones lie above 64/1 and are divided by 4; 32.40 lies
+    between: smooth = (64/32.40 - 1) / (4 - 1) = 0.3251, so the frequency becomes
+    (0.6749 / 4 + 0.3251) f = 0.49382 f.  The library's function (which builds the kernels' tables) must give
+    the same as the plain one.  (No installed package's implementation of the rule is used as a mark: the
+    packages' model code is not a source for this library.)"""
+    from picolm_b200.parts.position import rope_inverse_frequencies
+    sc = {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 64}
+    plain = P.rope_frequencies(32, 500000.0, sc)
+    mine = torch.tensor(rope_inverse_frequencies(32, 500000.0, sc), dtype=torch.float64)
+    assert torch.allclose(plain.double(), mine, rtol=1e-12, atol=0)
+    base = [500000.0 ** (-i / 16.0) for i in range(16)]
+    wl = [2 * math.pi / f for f in base]
+    assert [round(x, 2) for x in wl[:4]] == [6.28, 14.27, 32.40, 73.58]
+    ratio = [float(mine[i]) / base[i] for i in range(16)]
+    assert ratio[0] == 1.0 and ratio[1] == 1.0
+    smooth = (64.0 / wl[2] - 1.0) / 3.0
+    assert smooth == pytest.approx(0.3251, abs=5e-5)
+    assert ratio[2] == pytest.approx((1.0 - smooth) / 4.0 + smooth, rel=1e-12) and ratio[2] == pytest.approx(0.49382, abs=5e-6)
+    assert all(r == pytest.approx(0.25, rel=1e-12) for r in ratio[3:])
+    # the shapes the benchmarks use: every frequency is kept, divided by the factor, or in between, and the
+    # rule is monotone (a longer wavelength is never scaled less)
+    for hd, theta, factor, L0 in ((64, 500000.0, 32.0, 8192), (128, 500000.0, 8.0, 8192)):
+        s = {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+             "original_max_position_embeddings": L0}
+        a = rope_inverse_frequencies(hd, theta, None)
+        b = rope_inverse_frequencies(hd, theta, s)
+        r = [y / x for x, y in zip(a, b)]
+        assert r[0] == 1.0 and r[-1] == pytest.approx(1.0 / factor) and all(r[i + 1] <= r[i] + 1e-15 for i in range(len(r) - 1))
+        assert torch.allclose(P.rope_frequencies(hd, theta, s).double(), torch.tensor(b, dtype=torch.float64), rtol=1e-12, atol=0)
+
+
+def test_the_draw_order_is_not_the_reference_s():
+    """The engine's sampler walks the kept tokens in index order, the reference in descending probability
+    (picolm/sampler.c:112-121): the same distribution, but not the same token for the same seed.  This case
+    shows the difference, so that nobody reads the sampler's description as a promise of equal tokens."""
+    logits = torch.log(torch.tensor([0.1, 0.2, 0.7]))
+    s1, a = P.sample_reference_order(logits, 1.0, 0, 1.0, 0.0, 1)
+    s2, b = P.sample_index_order(logits, 1.0, 0, 1.0, 0.0, 1)
+    assert s1 == s2 and (a, b) == (2, 0)
