@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_tc": ["gemm_tc.cu"],
     "gemm_tc_skinny": ["gemm_tc_skinny.cu"],
     "gemm_tc_wide": ["gemm_tc_wide.cu"],
+    "decode_chain": ["decode_chain.cu"],
     "attention_simt": ["attention_simt.cu"],
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "attention_tc": ["attention_tc.cu"],            # likewise, head sizes 64 and 128

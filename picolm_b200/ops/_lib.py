@@ -37,6 +37,9 @@ _SIGNATURES = {
     "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "plm_check_bounds": [_i, _i, _i, _i, _vp, _vp],
+    "plm_decode_chain": [_vp, _i, _i, _vp, _vp, _vp, _vp],
+    "plm_decode_chain_ctas": [],
+    "plm_decode_chain_scratch": [_i, _i, _i],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
 }
@@ -196,6 +199,6 @@ def check_status(device="cuda:0") -> None:
             what = {16: "page number", 17: "sequence index", 18: "position", 19: "row index"}.get(code, str(code))
             raise KernelError(f"a kernel of the checked build met a {what} outside its bounds and did not follow it; "
                               f"its output is not valid")
-        where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
+        where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "the CTAs' meeting"}.get(code, str(code))
         raise KernelError(f"a tensor-core kernel gave up waiting on an mbarrier ({where}); its output is not valid")
 

@@ -6,7 +6,9 @@ from typing import Optional
 
 import torch
 
+from . import chain as _chain
 from ._lib import SM_COUNT, KernelError, _check, _dev, _dt, _fn, _p, _stream, status_word
+from .chain import LazyRows
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
@@ -27,6 +29,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the tensor-core kernel takes a @ w^T: both bfloat16, K a multiple of
     8 (rows start on 16-byte boundaries, as TMA needs) and at least one K block."""
+    if isinstance(a, LazyRows):
+        a = a.rows
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     (M, K), (N, K2) = a.shape, w.shape
@@ -46,6 +50,7 @@ def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = Fa
     (an RMSNorm whose scale is still due): the epilogue then scales each row of the result, in bfloat16."""
     scaled = a if isinstance(a, ScaledRows) else None
     if scaled is not None:
+        scaled.ready()
         a = scaled.x
         if out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc_skinny: rows with a scale that is still due give a bfloat16 result only")
@@ -80,14 +85,18 @@ class PendingLinear:
     calls `compute()`."""
     __slots__ = ("a", "w")
 
-    def __init__(self, a: torch.Tensor, w: torch.Tensor):
-        self.a, self.w = a, w
+    def __init__(self, a, w: torch.Tensor):
+        self.a, self.w = a, w                  # a: a tensor, or `LazyRows` of a chain that has not run
 
     @property
     def shape(self):
         return (self.a.shape[0], self.w.shape[0])
 
     def compute(self) -> torch.Tensor:
+        if isinstance(self.a, LazyRows):       # the chain's last product, with a plain fp32 result
+            out = self.a.chain.add_plain(self.w)
+            self.a.chain.run()
+            return out
         return linear(self.a, self.w, torch.float32)
 
 
@@ -96,10 +105,17 @@ class ScaledRows:
     `parts` [n, >= T] partial sums of squares of the rows (column t for row t), so that the normalised
     row t is x[t] / sqrt(sum(parts[:, t]) / size + eps).  A product takes it as its left operand and
     applies the scale to its result (`linear`, `linear_swiglu`); `materialize()` gives the rows."""
-    __slots__ = ("x", "parts", "size", "eps")
+    __slots__ = ("x", "parts", "size", "eps", "chain")
 
-    def __init__(self, x: torch.Tensor, parts: torch.Tensor, size: int, eps: float):
+    def __init__(self, x: torch.Tensor, parts: torch.Tensor, size: int, eps: float, chain=None):
         self.x, self.parts, self.size, self.eps = x, parts, size, eps
+        self.chain = chain                     # a chain whose run writes x and parts (None: they are written)
+
+    def ready(self) -> None:
+        """Run the chain that writes these rows, if it has not run."""
+        if self.chain is not None:
+            self.chain.run()
+            self.chain = None
 
     @property
     def shape(self):
@@ -114,6 +130,7 @@ class ScaledRows:
         return self.x.dtype
 
     def materialize(self) -> torch.Tensor:
+        self.ready()
         out = torch.empty_like(self.x)
         T, d = self.x.shape
         _check(_fn("elementwise", "plm_scale_rows")(
@@ -133,12 +150,20 @@ def residual_norm_supported(pending, x: torch.Tensor, norm_weight: torch.Tensor)
 
 
 def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> ScaledRows:
-    """x += pending (in place, the fp32 residual stream) and the RMSNorm of the new x as `ScaledRows`:
+    """x += pending (in place, the fp32 residual stream; done when the returned rows are made `ready()`,
+    which every product that takes them does) and the RMSNorm of the new x as `ScaledRows`:
     one tensor-core product whose epilogue does the add, applies the norm weight and leaves the rows'
     sums of squares; the scale itself is applied by the product that takes the result."""
     if not residual_norm_supported(pending, x, norm_weight):
         raise KernelError("linear_residual_norm: not a case the fused kernel takes")
     a, w = pending.a, pending.w
+    if _chain.wanted(a.shape[0]) and a.shape[0] * (w.shape[0] // SM_COUNT + 2) <= 4096:
+        # collected, not run: the product that takes the result decides when (see ops/chain.py)
+        ch = a.chain if isinstance(a, LazyRows) else _chain.Chain(a)
+        xw, parts = ch.add_residual(w, x, norm_weight)
+        return ScaledRows(xw, parts, w.shape[0], eps, chain=ch)
+    if isinstance(a, LazyRows):
+        a = a.materialize()
     _dev(a, "a"), _dev(w, "w"), _dev(x, "x"), _dev(norm_weight, "norm_weight")
     M, K = a.shape
     N = w.shape[0]
@@ -202,9 +227,19 @@ def pair_pays(m: int, n: int) -> bool:
     return m >= 256 and n >= 256 and ((m + 255) // 256) * ((n + 255) // 256) >= SM_COUNT
 
 
-def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):
     """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
-    whose epilogue applies the activation; [M, F] in bfloat16.  `a` may be `ScaledRows`."""
+    whose epilogue applies the activation; [M, F] in bfloat16.  `a` may be `ScaledRows`.  With `defer` (the
+    caller hands the result to `linear(..., defer=True)` and nowhere else) the result may be `LazyRows`."""
+    if isinstance(a, ScaledRows) and a.chain is not None and a.chain.pending:
+        if gemm_tc_supported(a.x, w_gate_up) and w_gate_up.shape[0] % 128 == 0:
+            ch = a.chain
+            rows = ch.add_swiglu(w_gate_up, a.parts, a.size, a.eps)
+            if defer:
+                return LazyRows(ch, rows)
+            ch.run()
+            return rows
+        a.ready()
     if isinstance(a, ScaledRows) and not (a.shape[0] <= 64 and gemm_tc_supported(a.x, w_gate_up)):
         a = a.materialize()
     x = a.x if isinstance(a, ScaledRows) else a
@@ -227,8 +262,17 @@ def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):
     `a` may be `ScaledRows`.  With `defer` (a float32 delta for the residual stream) the product may
     come back as a `PendingLinear` for the next norm to run; whoever cannot use that calls `compute()`."""
     if isinstance(a, ScaledRows):
+        if a.chain is not None and a.chain.pending and out_dtype == torch.bfloat16 and gemm_tc_supported(a.x, w):
+            ch = a.chain                           # the chain's last product: run it all
+            out = ch.add_scaled(w, a.parts, a.size, a.eps)
+            ch.run()
+            return out
         if a.shape[0] <= 64 and out_dtype == torch.bfloat16 and gemm_tc_supported(a.x, w):
             return gemm_tc_skinny(a, w, out_dtype)
+        a = a.materialize()
+    if isinstance(a, LazyRows):
+        if defer and out_dtype == torch.float32 and gemm_tc_supported(a, w):
+            return PendingLinear(a, w)
         a = a.materialize()
     if defer and out_dtype == torch.float32 and a.shape[0] <= 64 and gemm_tc_supported(a, w):
         return PendingLinear(a, w)

@@ -55,7 +55,7 @@ class GatedMLP(Part):
 
     def forward(self, h, step):
         if self.fused:
-            act = ops.linear_swiglu(h, self.w_gate_up)
+            act = ops.linear_swiglu(h, self.w_gate_up, defer=True)      # handed to the next product and nowhere else
         else:
             act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype), activation=self.params["activation"])
         return ops.linear(act, self.w_down, torch.float32, defer=True)

@@ -422,6 +422,7 @@ def test_norm_split_over_two_products(T, F, K, N2, swiglu):
     pending = ops.linear(a.to(DEV), w.to(DEV), torch.float32, defer=True)
     assert isinstance(pending, ops.PendingLinear)
     rows = ops.linear_residual_norm(pending, xd, nw.to(DEV), eps)
+    rows.ready()                                                            # (the product may be held back for a chain)
     assert torch.allclose(xd.double().cpu(), xn, atol=2e-3, rtol=1e-4)      # the stream, updated in place
     assert torch.allclose(rows.materialize().double().cpu(), h, atol=3e-2, rtol=2e-2)
     if swiglu:
@@ -439,6 +440,7 @@ def test_norm_split_over_two_products(T, F, K, N2, swiglu):
         x1 = x[-1:].contiguous().to(DEV)
         rows1 = ops.linear_residual_norm(ops.linear(a[-1:].contiguous().to(DEV), w.to(DEV), torch.float32, defer=True),
                                          x1, nw.to(DEV), eps)
+        rows1.ready()
         assert torch.equal(x1[0], xd[-1])
         assert torch.equal(rows1.materialize()[0], rows.materialize()[-1])
 
