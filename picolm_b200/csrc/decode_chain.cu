@@ -42,7 +42,7 @@ constexpr int MAX_PHASES = 4;
 enum { KIND_RESIDUAL = 0, KIND_SWIGLU = 1, KIND_SCALED = 2, KIND_PLAIN = 3 };
 constexpr int SS_LD = 64;                   // floats per row of a sums-of-squares table (one row per CTA)
 constexpr int MAX_SHARE = 4096;             // (tokens x columns) of a RESIDUAL phase that one CTA sums: 64 x 64
-constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of the meeting counter (with a short sleep each) before giving up
+constexpr uint32_t SPIN_LIMIT = 1u << 24;   // polls of the meeting counter before giving up
 
 struct Phase {
     CUtensorMap map_w;                      // [N, K] bf16, boxes of 128 x 64
@@ -75,6 +75,34 @@ __host__ __device__ inline int cta_of_block(long long b, long long total, int n_
     return (int)(((b + 1) * n_ctas - 1) / total);
 }
 
+// A trace of one CTA's way through the chain (a build with -DPLM_CHAIN_TRACE only): nanoseconds since the
+// kernel's start at the points marked below, [CTA][point].
+#ifdef PLM_CHAIN_TRACE
+__device__ unsigned long long plm_chain_trace[PLM_SM_COUNT * 2][64];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(point) do { if (threadIdx.x == 64 && (point) < 64) plm_chain_trace[blockIdx.x][point] = trace_now(); } while (0)
+__device__ unsigned long long plm_chain_blocks[4][256];      // CTA 70: per block, when W was asked for, A was asked for, the stage was full, its MMAs were issued
+#define TRACE_BLOCK(kind, n) do { if (blockIdx.x == 70 && (n) < 256) plm_chain_blocks[kind][n] = trace_now(); } while (0)
+#else
+#define TRACE(point) do { } while (0)
+#define TRACE_BLOCK(kind, n) do { } while (0)
+#endif
+
+// Whether the phase is complete, without waiting (mbarrier.try_wait may suspend the thread for a while; the
+// producer has other work to look after meanwhile).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -101,15 +129,14 @@ __device__ __forceinline__ bool epilogue_any(bool v) {
 // visible to every thread of the grid after (also to TMA loads that are issued after).  Returns false if
 // the wait ran out or another CTA has reported a failure.
 __device__ bool meet(unsigned int* counter, unsigned int target, int* status, volatile int* s_abort) {
-    __threadfence();
-    asm volatile("fence.proxy.async.global;" ::: "memory");
-    epilogue_bar();
+    epilogue_bar();                         // this CTA's writes have happened before its leader's fence
     if (threadIdx.x == 64) {
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
         atomicAdd(counter, 1u);
         uint32_t spins = 0;
         while (ld_acquire(counter) < target) {
-            __nanosleep(40);
-            if (++spins > SPIN_LIMIT || *(volatile int*)status != 0) {
+            if (++spins > SPIN_LIMIT || ((spins & 63u) == 0u && *(volatile int*)status != 0)) {
                 atomicCAS(status, 0, 4);
                 *s_abort = 1;
                 break;
@@ -120,7 +147,46 @@ __device__ bool meet(unsigned int* counter, unsigned int target, int* status, vo
     return !epilogue_any(*s_abort != 0);
 }
 
+// A walk over one CTA's blocks of all phases in the order in which they pass through the ring.  The
+// producer keeps two (weights ahead, activations behind), the MMA issuer one.  One thread steps it once per
+// block, so it steps without divisions: a single thread's arithmetic is slow enough to bound the ring's rate.
+struct Walk {
+    int p;                      // phase (n_phases: done)
+    int tile, kb, n_kb, left;   // the next block, the phase's K blocks per tile, blocks of this CTA left in the phase
+    int stage;                  // the ring stage the next block goes through
+    uint32_t lap;               // parity of how often the ring has been gone round
+};
+__device__ __forceinline__ void walk_enter(Walk& w, const Chain& ch, int cta, int n_ctas) {
+    while (w.p < ch.n_phases) {                         // (skips phases in which this CTA has no block)
+        const Phase& P = ch.ph[w.p];
+        const long long b = first_block(P.total, cta, n_ctas), e = first_block(P.total, cta + 1, n_ctas);
+        if (e > b) {
+            w.n_kb = P.n_kb;
+            w.tile = (int)(b / P.n_kb);
+            w.kb = (int)(b - (long long)w.tile * P.n_kb);
+            w.left = (int)(e - b);
+            return;
+        }
+        ++w.p;
+    }
+}
+template <int STAGES>
+__device__ __forceinline__ void walk_step(Walk& w, const Chain& ch, int cta, int n_ctas) {
+    if (++w.stage == STAGES) { w.stage = 0; w.lap ^= 1u; }
+    if (--w.left == 0) {
+        ++w.p;
+        walk_enter(w, ch, cta, n_ctas);
+    } else if (++w.kb == w.n_kb) {
+        w.kb = 0;
+        ++w.tile;
+    }
+}
+
+#ifdef PLM_CHAIN_STAGES
+template <int BN> __host__ __device__ constexpr int stages_of() { return PLM_CHAIN_STAGES; }
+#else
 template <int BN> __host__ __device__ constexpr int stages_of() { return BN <= 16 ? 11 : (BN <= 32 ? 10 : 8); }
+#endif
 template <int BN> __host__ __device__ constexpr size_t chain_smem() {
     return (size_t)stages_of<BN>() * (BM * BK * 2 + BN * BK * 2) + 1024 /*alignment*/ + 512 /*barriers*/;
 }
@@ -141,6 +207,7 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
     __shared__ int s_abort;
     __shared__ int s_ready;                 // phases up to this one have their input (-1: none yet)
     __shared__ float s_rstd[64];
+    __shared__ float s_part[128];
     __shared__ float s_sq[MAX_SHARE];         // RESIDUAL: the squares of this CTA's share, [token][column]
 
     pdl_launch_dependents();
@@ -175,46 +242,33 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
         if (lane == 0) {
             // two walks over this CTA's blocks of all phases: the weights run ahead, the activations
             // follow as their phases' inputs come to exist
-            int wp = 0, ap = 0;
-            long long wb = 0, we = 0, ab = 0, ae = 0;
-            auto range = [&](int p, long long& b, long long& e) {
-                b = first_block(ch.ph[p].total, cta, n_ctas);
-                e = first_block(ch.ph[p].total, cta + 1, n_ctas);
-            };
-            auto settle = [&](int& p, long long& b, long long& e) {      // skip phases where this CTA has no block
-                while (p < ch.n_phases && b >= e) {
-                    ++p;
-                    if (p < ch.n_phases) range(p, b, e);
-                }
-            };
-            range(0, wb, we); settle(wp, wb, we);
-            range(0, ab, ae); settle(ap, ab, ae);
-            long long w_n = 0, a_n = 0;                                 // blocks asked for so far
+            Walk ww = {0, 0, 0, 1, 0, 0, 0u}, aw = ww;
+            walk_enter(ww, ch, cta, n_ctas);
+            walk_enter(aw, ch, cta, n_ctas);
+            int w_n = 0, a_n = 0;                                       // blocks asked for so far
             bool waited = false;
+            int fenced = -1;
             uint32_t idle = 0;
-            while (wp < ch.n_phases || ap < ch.n_phases) {
+            while (ww.p < ch.n_phases || aw.p < ch.n_phases) {
                 bool moved = false;
-                if (wp < ch.n_phases) {
-                    const int s = (int)(w_n % STAGES);
-                    if (mbar_try_wait(empty0 + 8 * s, (uint32_t)(((w_n / STAGES) & 1) ^ 1))) {
-                        const Phase& P = ch.ph[wp];
-                        const int tile = (int)(wb / P.n_kb), kb = (int)(wb - (long long)tile * P.n_kb);
-                        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                        tma_load_2d(base + s * STAGE_BYTES, &P.map_w, full0 + 8 * s, kb * BK, tile * BM);
-                        ++wb; ++w_n;
-                        settle(wp, wb, we);
-                        moved = true;
-                    }
+                if (ww.p < ch.n_phases && mbar_test(empty0 + 8 * ww.stage, ww.lap ^ 1u)) {
+                    mbar_expect_tx(full0 + 8 * ww.stage, STAGE_BYTES);
+                    tma_load_2d(base + ww.stage * STAGE_BYTES, &ch.ph[ww.p].map_w, full0 + 8 * ww.stage, ww.kb * BK, ww.tile * BM);
+                    TRACE_BLOCK(0, w_n);
+                    ++w_n;
+                    walk_step<STAGES>(ww, ch, cta, n_ctas);
+                    moved = true;
                 }
-                if (ap < ch.n_phases && a_n < w_n && *(volatile int*)&s_ready >= ap) {
+                if (aw.p < ch.n_phases && a_n < w_n && *(volatile int*)&s_ready >= aw.p) {
                     if (!waited) { pdl_wait(); waited = true; }
-                    const Phase& P = ch.ph[ap];
-                    const int s = (int)(a_n % STAGES);
-                    const int kb = (int)(ab % P.n_kb);
-                    asm volatile("fence.proxy.async.global;" ::: "memory");     // what other CTAs wrote before the meeting
-                    tma_load_2d(base + s * STAGE_BYTES + W_BYTES, &P.map_a, full0 + 8 * s, kb * BK, 0);
-                    ++ab; ++a_n;
-                    settle(ap, ab, ae);
+                    if (fenced != aw.p) {   // once per phase: what other CTAs wrote before the meeting, for the copies below
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                        fenced = aw.p;
+                    }
+                    tma_load_2d(base + aw.stage * STAGE_BYTES + W_BYTES, &ch.ph[aw.p].map_a, full0 + 8 * aw.stage, aw.kb * BK, 0);
+                    TRACE_BLOCK(1, a_n);
+                    ++a_n;
+                    walk_step<STAGES>(aw, ch, cta, n_ctas);
                     moved = true;
                 }
                 if (moved) { idle = 0; continue; }
@@ -232,39 +286,37 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
         // ---------------------------------------------------------- the MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(BN);
-            long long n = 0;
-            int seg = 0;
-            bool ok = true;
-            for (int p = 0; p < ch.n_phases && ok; ++p) {
-                const Phase& P = ch.ph[p];
-                long long b = first_block(P.total, cta, n_ctas);
-                const long long e = first_block(P.total, cta + 1, n_ctas);
-                while (b < e && ok) {
-                    const long long tile = b / P.n_kb;
-                    const long long seg_end = min(e, (tile + 1) * P.n_kb);
-                    const int buf = seg & 1;
-                    if (*(volatile int*)&s_abort) { ok = false; break; }
-                    if (!mbar_wait(acc_empty0 + 8 * buf, (uint32_t)(((seg >> 1) & 1) ^ 1), ch.status, 2)) { s_abort = 1; ok = false; break; }
+            Walk cw = {0, 0, 0, 1, 0, 0, 0u};
+            walk_enter(cw, ch, cta, n_ctas);
+            int seg = 0, n = 0;
+            bool first = true;                                          // the next block opens a segment (a tile's run of blocks)
+            while (cw.p < ch.n_phases) {
+                const int buf = seg & 1;
+                if (*(volatile int*)&s_abort) break;
+                if (first) {
+                    if (!mbar_wait(acc_empty0 + 8 * buf, (uint32_t)(((seg >> 1) & 1) ^ 1), ch.status, 2)) { s_abort = 1; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                    for (bool first = true; b < seg_end; ++b, ++n, first = false) {
-                        const int s = (int)(n % STAGES);
-                        if (*(volatile int*)&s_abort) { ok = false; break; }
-                        if (!mbar_wait(full0 + 8 * s, (uint32_t)((n / STAGES) & 1), ch.status, 2)) { s_abort = 1; ok = false; break; }
-                        tc_fence_after();
-                        const uint64_t wd = smem_desc_sw128(base + s * STAGE_BYTES);
-                        const uint64_t ad = smem_desc_sw128(base + s * STAGE_BYTES + W_BYTES);
-#pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k)
-                            tc_mma_bf16(d_tmem, wd + (uint64_t)(k * UMMA_K * 2 / 16), ad + (uint64_t)(k * UMMA_K * 2 / 16),
-                                        idesc, (!first || k > 0) ? 1u : 0u);
-                        tc_commit(empty0 + 8 * s);
-                    }
-                    if (ok) {
-                        tc_commit(acc_full0 + 8 * buf);
-                        ++seg;
-                    }
                 }
+                if (!mbar_wait(full0 + 8 * cw.stage, cw.lap, ch.status, 2)) { s_abort = 1; break; }
+                TRACE_BLOCK(2, n);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const uint64_t wd = smem_desc_sw128(base + cw.stage * STAGE_BYTES);
+                const uint64_t ad = smem_desc_sw128(base + cw.stage * STAGE_BYTES + W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc_mma_bf16(d_tmem, wd + (uint64_t)(k * UMMA_K * 2 / 16), ad + (uint64_t)(k * UMMA_K * 2 / 16),
+                                idesc, (!first || k > 0) ? 1u : 0u);
+                tc_commit(empty0 + 8 * cw.stage);
+                TRACE_BLOCK(3, n);
+                ++n;
+                const bool closes = cw.left == 1 || cw.kb == cw.n_kb - 1;   // the CTA's range or the tile ends here
+                if (closes) {
+                    tc_commit(acc_full0 + 8 * buf);
+                    ++seg;
+                }
+                first = closes;
+                walk_step<STAGES>(cw, ch, cta, n_ctas);
             }
         }
     } else {
@@ -275,7 +327,9 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
         unsigned int meetings = 0;
         int seg = 0;
         bool ok = true;
+        TRACE(0);
         pdl_wait();                                         // the chain's input and the stream are there
+        TRACE(1);
         if (tid == 0) s_ready = 0;
         for (int p = 0; p < ch.n_phases && ok; ++p) {
             const Phase& P = ch.ph[p];
@@ -290,15 +344,16 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
                 if (epilogue_any(!got || *(volatile int*)&s_abort != 0)) { ok = false; break; }
                 tc_fence_after();
                 const int slot = cta - cta_of_block(tile * P.n_kb, P.total, n_ctas);
-                float* dst = ch.partial + (((size_t)tile * P.slots + slot) * BN) * BM + row;
+                float* dst = ch.partial + (((size_t)tile * P.slots + slot) * BM + row) * BN;   // [tile][slot][row][token]
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t r[32];
                     tc_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                     tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c + j < ch.T) dst[(size_t)(c + j) * BM] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 16; j += 4)
+                        if (c + j < ch.T)
+                            *reinterpret_cast<uint4*>(dst + c + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -307,54 +362,102 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
                 ++seg;
             }
             if (!ok) break;
+            TRACE(2 + 4 * p);
             // ---- everyone's partial sums of this phase are written
             if (!meet(ch.sync, ++meetings * (unsigned)n_ctas, ch.status, &s_abort)) { ok = false; break; }
+            TRACE(3 + 4 * p);
 
             // ---- this CTA's share of the phase's columns: sum, epilogue, write
             const int n_cols = P.kind == KIND_SWIGLU ? P.N / 2 : P.N;
             const int c_lo = (int)((long long)n_cols * cta / n_ctas), c_hi = (int)((long long)n_cols * (cta + 1) / n_ctas);
             if (P.kind == KIND_SWIGLU || P.kind == KIND_SCALED) {
+                // every token's sum of squares: the CTAs' parts are dealt over the groups of BN threads (loads of a
+                // group's thread are asked for sixteen at a time), then one thread a token adds the groups' sums in order
+                constexpr int GROUPS = 128 / BN;
+                const int t = tid % BN, grp = tid / BN;
+                float ss = 0.f;
+                if (t < ch.T) {
+                    for (int c0 = grp; c0 < n_ctas; c0 += 16 * GROUPS) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int c = c0 + j * GROUPS;
+                            v[j] = c < n_ctas ? __ldcg(P.ss_in + (size_t)c * SS_LD + t) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) ss += v[j];
+                    }
+                }
+                s_part[grp * BN + t] = ss;
+                epilogue_bar();
                 if (tid < BN) {
-                    float ss = 0.f;
-                    if (tid < ch.T)
-                        for (int c = 0; c < n_ctas; ++c) ss += __ldcg(P.ss_in + (size_t)c * SS_LD + tid);
-                    s_rstd[tid] = 1.0f / sqrtf(ss * P.inv_size + P.eps);
+                    float sum = 0.f;
+#pragma unroll
+                    for (int g2 = 0; g2 < GROUPS; ++g2) sum += s_part[g2 * BN + tid];
+                    s_rstd[tid] = 1.0f / sqrtf(sum * P.inv_size + P.eps);
                 }
                 epilogue_bar();
             }
-            auto summed = [&](int tile, int r, int t) {     // the partial sums of (row r of a tile, token t), in slot order
+            // Four tokens of one row of a tile, summed over the tile's slots in slot order.  All loads are asked for
+            // before any is added, so a thread waits for the second-level cache once, not once per slot.
+            auto summed4 = [&](int tile, int r, int t4) {
                 const int s0 = cta_of_block((long long)tile * P.n_kb, P.total, n_ctas);
                 const int s1 = cta_of_block((long long)(tile + 1) * P.n_kb - 1, P.total, n_ctas);
-                const float* src = ch.partial + (((size_t)tile * P.slots) * BN + t) * BM + r;
-                float v = 0.f;
-                for (int s = 0; s <= s1 - s0; ++s) {
-                    // (with fewer blocks than CTAs, CTAs in between have no block and wrote nothing)
-                    if (P.total >= n_ctas || first_block(P.total, s0 + s, n_ctas) < first_block(P.total, s0 + s + 1, n_ctas))
-                        v += __ldcg(src + (size_t)s * BN * BM);
+                const float* src = ch.partial + (((size_t)tile * P.slots) * BM + r) * BN + t4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sb = 0; sb <= s1 - s0; sb += 12) {
+                    float4 v[12];
+#pragma unroll
+                    for (int j = 0; j < 12; ++j) {
+                        const int s = sb + j;
+                        // (with fewer blocks than CTAs, CTAs in between have no block and wrote nothing)
+                        const bool there = s <= s1 - s0 &&
+                            (P.total >= n_ctas || first_block(P.total, s0 + s, n_ctas) < first_block(P.total, s0 + s + 1, n_ctas));
+                        v[j] = there ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * BM * BN))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 12; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
                 }
-                return v;
+                return acc;
             };
-            const int ncols = c_hi - c_lo, items = ncols * ch.T;
-            for (int idx = tid; idx < items; idx += 128) {  // all (token, column) pairs of the share at once
-                const int t = idx / ncols, c = c_lo + (idx - t * ncols);
+            const int ncols = c_hi - c_lo, quads = (ch.T + 3) / 4, items = ncols * quads;
+            for (int idx = tid; idx < items; idx += 128) {  // all (column, four tokens) pairs of the share at once
+                const int qd = idx / ncols, c = c_lo + (idx - qd * ncols), t0 = qd * 4;
+                float val[4], xv[4] = {0.f, 0.f, 0.f, 0.f}, nwc = 0.f;
+                if (P.kind == KIND_RESIDUAL) {                  // asked for before the partial sums are waited for
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (t0 + e < ch.T) xv[e] = __ldcg(P.resid + (size_t)(t0 + e) * P.ld_resid + c);
+                    nwc = __bfloat162float(P.norm_w[c]);
+                }
                 if (P.kind == KIND_SWIGLU) {
                     const int tile = c >> 6, r = c & 63;
-                    const float sc = s_rstd[t];
-                    const float g = summed(tile, r, t) * sc, u = summed(tile, 64 + r, t) * sc;
-                    reinterpret_cast<bf16*>(P.out)[(size_t)t * P.ldo + c] = __float2bfloat16_rn(swiglu_bf16(g, u));
+                    const float4 g = summed4(tile, r, t0), u = summed4(tile, 64 + r, t0);
+                    const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float sc = s_rstd[min(t0 + e, BN - 1)];
+                        val[e] = swiglu_bf16(gs[e] * sc, us[e] * sc);
+                    }
                 } else {
-                    const float v = summed(c >> 7, c & 127, t);
+                    const float4 v = summed4(c >> 7, c & 127, t0);
+                    val[0] = v.x; val[1] = v.y; val[2] = v.z; val[3] = v.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int t = t0 + e;
+                    if (t >= ch.T) break;
                     if (P.kind == KIND_RESIDUAL) {
-                        float* xp = P.resid + (size_t)t * P.ld_resid + c;
-                        const float xn = __ldcg(xp) + v;
-                        *xp = xn;
-                        reinterpret_cast<bf16*>(P.out)[(size_t)t * P.ldo + c] =
-                            __float2bfloat16_rn(xn * __bfloat162float(P.norm_w[c]));
-                        s_sq[idx] = xn * xn;
-                    } else if (P.kind == KIND_SCALED) {
-                        reinterpret_cast<bf16*>(P.out)[(size_t)t * P.ldo + c] = __float2bfloat16_rn(v * s_rstd[t]);
+                        const float xn = xv[e] + val[e];
+                        P.resid[(size_t)t * P.ld_resid + c] = xn;
+                        reinterpret_cast<bf16*>(P.out)[(size_t)t * P.ldo + c] = __float2bfloat16_rn(xn * nwc);
+                        s_sq[t * ncols + (c - c_lo)] = xn * xn;
+                    } else if (P.kind == KIND_PLAIN) {
+                        reinterpret_cast<float*>(P.out)[(size_t)t * P.ldo + c] = val[e];
                     } else {
-                        reinterpret_cast<float*>(P.out)[(size_t)t * P.ldo + c] = v;
+                        const float o = P.kind == KIND_SCALED ? val[e] * s_rstd[t] : val[e];
+                        reinterpret_cast<bf16*>(P.out)[(size_t)t * P.ldo + c] = __float2bfloat16_rn(o);
                     }
                 }
             }
@@ -366,10 +469,12 @@ decode_chain_kernel(const __grid_constant__ Chain ch) {
                     P.ss_out[(size_t)cta * SS_LD + tid] = sq;
                 }
             }
+            TRACE(4 + 4 * p);
             if (p + 1 < ch.n_phases) {
                 // ---- the phase's output is complete everywhere: the next phase may read it
                 if (!meet(ch.sync, ++meetings * (unsigned)n_ctas, ch.status, &s_abort)) { ok = false; break; }
                 if (tid == 0) s_ready = p + 1;
+                TRACE(5 + 4 * p);
             }
         }
     }
@@ -430,6 +535,15 @@ struct PlmChainPhase {
     const float* ss_in;         // SWIGLU, SCALED
     int size; float eps;        // the norm's width and eps
 };
+
+#ifdef PLM_CHAIN_TRACE
+extern "C" int plm_chain_trace_read(unsigned long long* host, int n_ctas) {
+    return plm_status_of(cudaMemcpyFromSymbol(host, plm_chain_trace, sizeof(unsigned long long) * 64 * n_ctas));
+}
+extern "C" int plm_chain_blocks_read(unsigned long long* host) {
+    return plm_status_of(cudaMemcpyFromSymbol(host, plm_chain_blocks, sizeof(unsigned long long) * 4 * 256));
+}
+#endif
 
 // How many CTAs the chain kernel runs (the rows of a sums-of-squares table).
 extern "C" int plm_decode_chain_ctas() { return persistent_ctas(); }

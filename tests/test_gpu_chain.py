@@ -10,6 +10,16 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(autouse=True)
+def chains_on():
+    """Chains are off by default (they are slower than single launches so far); these tests switch them on."""
+    from picolm_b200.ops import chain
+    old = chain.ENABLED
+    chain.ENABLED = True
+    yield
+    chain.ENABLED = old
+
+
 def _case(T, K0, d, F, N2, seed):
     g = torch.Generator().manual_seed(seed)
     rnd = lambda *s: torch.randn(*s, generator=g)                                        # noqa: E731
