@@ -49,8 +49,10 @@ class Engine:
         safe = all(getattr(part, "graph_safe", False) for b in model.blocks for _, part in b.parts())
         self.use_graphs = safe if use_graphs is None else (use_graphs and safe)
         from ..ops import _lib
-        if _lib.CHECKED:
-            self.use_graphs = False      # the checked build hands its kernels their bounds by a copy before every launch
+        if _lib.CHECKED or _lib.TRACED:
+            # the checked build hands its kernels their bounds by a copy before every launch; the per-kernel
+            # table needs every launch between two events
+            self.use_graphs = False
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
         # one id per live sequence, and never fewer than the largest captured batch size (its padding rows read it)
         from .decode_graph import BUCKETS

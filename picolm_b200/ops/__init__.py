@@ -4,7 +4,7 @@ raises `KernelError` if the kernel library refuses or fails.  There is no CPU
 path: a tensor that is not on a CUDA device is an error.
 """
 from ._lib import (PAGE_TOKENS, SM_COUNT, KernelError, check_status, count_launches, launch_count,  # noqa: F401
-                   status_word, stream_scope)
+                   status_word, stream_scope, trace_report)
 from .attention import (DECODE_CLUSTER_SPLITS, Rotation, attention, attention_decode,  # noqa: F401
                         attention_decode_rope, attention_decode_rope_supported, attention_mma_supported,
                         attention_prefill, attention_prefill_tc, attention_rows, attention_tc_supported, decode_splits)

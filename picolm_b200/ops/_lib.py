@@ -72,8 +72,71 @@ def _fn(library: str, name: str, extra_flags=()):
         f = getattr(lib, name)
         f.argtypes = _SIGNATURES[name]
         f.restype = ctypes.c_int
+        if TRACED:
+            f = _traced(f)
         _fn_cache[key] = f
     return f
+
+
+# ------------------------------------------------------------------ the per-kernel table
+# With PICOLM_B200_TRACE=1 every entry point is called between two CUDA events, and when the process ends (or
+# `trace_report()` is called) a table goes to stderr: per kind of launch its count, its device time, the bytes
+# and flops its face in this package declared for it, and what fraction of the memory's or the tensor cores'
+# rate that is.  Steps are launched kernel by kernel while tracing (no graphs).  The reference's counterpart is
+# the per-layer table of its --benchmark (picolm/picolm.c:251-383); this one is per kernel.
+TRACED = os.environ.get("PICOLM_B200_TRACE", "") == "1"
+PEAK_GBS = float(os.environ.get("PICOLM_B200_PEAK_GBS", "6535.7"))        # a B200's copy bandwidth as measured
+PEAK_TFLOPS = float(os.environ.get("PICOLM_B200_PEAK_TFLOPS", "1636.8"))  # and its cuBLAS bf16 rate
+_trace_open = []          # (start, stop) of launches whose `_check` has not run yet
+_trace_rows = []          # (what, start, stop, bytes, flops)
+
+
+def _traced(f):
+    def call(*args):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        code = f(*args)
+        b.record()
+        _trace_open.append((a, b))
+        return code
+    return call
+
+
+def trace_report(file=None, reset: bool = True):
+    """The per-kernel table of what ran since the last report (needs PICOLM_B200_TRACE=1).  Returns the rows."""
+    import sys
+    torch.cuda.synchronize()
+    agg = {}
+    for what, a, b, nbytes, flops in _trace_rows:
+        r = agg.setdefault(what, [0, 0.0, 0, 0])
+        r[0] += 1
+        r[1] += a.elapsed_time(b)
+        r[2] += nbytes
+        r[3] += flops
+    rows = sorted(agg.items(), key=lambda kv: -kv[1][1])
+    total = sum(r[1] for _, r in rows) or 1.0
+    out = file or sys.stderr
+    print(f"{'launch':44s} {'count':>6s} {'ms':>9s} {'share':>6s} {'GB/s':>8s} {'of peak':>7s} {'TFLOP/s':>8s} {'of peak':>7s}", file=out)
+    for what, (n, ms, nbytes, flops) in rows:
+        gbs = nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+        tf = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+        print(f"{what[:44]:44s} {n:6d} {ms:9.3f} {ms / total:6.1%} {gbs:8.0f} {gbs / PEAK_GBS:7.2f} {tf:8.1f} {tf / PEAK_TFLOPS:7.2f}",
+              file=out)
+    if reset:
+        _trace_rows.clear()
+    return rows
+
+
+if TRACED:
+    import atexit
+
+    @atexit.register
+    def _report_at_exit():
+        if _trace_rows:
+            try:
+                trace_report()
+            except Exception:
+                pass
 
 
 _launches = 0
@@ -91,8 +154,15 @@ def count_launches(n: int) -> None:
     _launches += n
 
 
-def _check(code: int, what: str, kernels: int = 1) -> None:
+def _check(code: int, what: str, kernels: int = 1, nbytes: int = 0, flops: int = 0) -> None:
+    """After an entry point returned `code`: count its launches, or raise.  `nbytes` and `flops` are what the
+    launch has to move and compute (for the per-kernel table)."""
     global _launches
+    if TRACED and _trace_open:
+        a, b = _trace_open.pop()
+        _trace_open.clear()
+        if code == 0:
+            _trace_rows.append((what, a, b, int(nbytes), int(flops)))
     if code == 0:
         _launches += kernels
         return

@@ -28,7 +28,7 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     _cache_bounds("attention_simt", (), k_cache, block_table)
     _check(_fn("attention_simt", "plm_attention_rows")(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _dt(q, "q"), _p(tok_pos), _p(tok_seq), _p(block_table),
-        block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _stream()), "attention_rows")
+        block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _stream()), f"attention_rows T={T} H={H} hd={hd}")
     return out
 
 
@@ -71,7 +71,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     _check(_fn(lib, "plm_attn_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale), int(window or 0),
-        _stream()), "attention_prefill")
+        _stream()), f"attention_prefill(mma) T={T} H={H} hd={hd}", flops=2 * H * hd * T * int(max_new))
     return out
 
 
@@ -97,7 +97,8 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _check(_fn(lib, "plm_attn_tc_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], k_cache.shape[0], T, seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale),
-        int(window or 0), _p(status_word(q.device)), _stream()), "attention_prefill_tc")
+        int(window or 0), _p(status_word(q.device)), _stream()), f"attention_prefill_tc T={T} H={H} hd={hd}",
+        flops=2 * H * hd * T * int(max_new))
     return out
 
 
@@ -160,7 +161,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _check(_fn(lib, "plm_attn_decode", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
-        "attention_decode", kernels=2 if scratch else 1)
+        f"attention_decode T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1)
     return out
 
 
@@ -208,7 +209,8 @@ def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_he
     _check(_fn(lib, "plm_attn_decode_rope", flags)(
         _p(qkv), _p(kv.k), _p(kv.v), _p(out), _p(ws), _p(rotation.cos), _p(rotation.sin), _p(step.tok_pos),
         _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, float(scale), int(kv.window or 0),
-        int(n_splits), _stream()), "attention_decode_rope", kernels=2 if scratch else 1)
+        int(n_splits), _stream()), f"attention_decode_rope T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1,
+        nbytes=T * (step.max_position + 1) * 2 * G * hd * 2)
     return out
 
 

@@ -48,7 +48,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     set_bounds("elementwise", n_rows=T, device=x.device)
     _check(_fn("elementwise", "plm_rmsnorm")(
         _p(x), _p(delta), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
-        float(eps), _stream()), "rmsnorm")
+        float(eps), _stream()), f"rmsnorm rows={n_rows} d={d}",
+        nbytes=n_rows * d * (4 + (8 if delta is not None else 0) + out.element_size()))
     return out
 
 

@@ -11,6 +11,12 @@ from ._lib import SM_COUNT, KernelError, _check, _dev, _dt, _fn, _p, _stream, st
 from .chain import LazyRows
 
 
+def _work(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, extra: int = 0) -> dict:
+    """What a product has to move and compute: both operands and the result once, 2 M N K flops."""
+    return {"nbytes": a.numel() * a.element_size() + w.numel() * w.element_size() + out.numel() * out.element_size() + extra,
+            "flops": 2 * a.shape[0] * w.shape[0] * w.shape[1]}
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, fp32 accumulation."""
@@ -22,7 +28,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     _check(_fn("gemm_simt", "plm_gemm_simt")(
-        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, K, K, N, _stream()), "gemm_simt")
+        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, K, K, N, _stream()),
+        f"gemm_simt {M}x{N}x{K}", **_work(a, w, out))
     return out
 
 
@@ -70,11 +77,11 @@ def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = Fa
         _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_scaled")(
             _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
             scaled.parts.shape[1], scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()),
-            "gemm_tc_skinny_scaled")
+            f"gemm_tc_skinny{'_swiglu' if swiglu else ''}_scaled {M}x{N}x{K}", **_work(a, w, out))
         return out
     _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
-        _p(status_word(a.device)), _stream()), "gemm_tc_skinny")
+        _p(status_word(a.device)), _stream()), f"gemm_tc_skinny{'_swiglu' if swiglu else ''} {M}x{N}x{K}", **_work(a, w, out))
     return out
 
 
@@ -172,7 +179,7 @@ def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: t
     parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
     _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_residual")(
         _p(a), _p(w), _p(x), _p(norm_weight), _p(xw), _p(parts), M, N, K, K, K, N, N,
-        _p(status_word(x.device)), _stream()), "gemm_tc_skinny_residual")
+        _p(status_word(x.device)), _stream()), f"gemm_tc_skinny_residual {M}x{N}x{K}", **_work(a, w, x, extra=x.numel() * 4))
     return ScaledRows(xw, parts, N, eps)
 
 
@@ -202,11 +209,13 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
             scratch = torch.empty((k_splits, M, N), dtype=torch.float32, device=a.device)
             _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_scratch")(
                 _p(a), _p(w), _p(out), _dt(out, "out"), 0, M, N, K, K, K, n_out, _p(scratch),
-                _p(status_word(a.device)), _stream()), "gemm_tc_wide", kernels=2)
+                _p(status_word(a.device)), _stream()), f"gemm_tc_wide(K in {k_splits} parts) {M}x{N}x{K}", kernels=2,
+                **_work(a, w, out, extra=2 * scratch.numel() * 4))
             return out
     _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair" if pair else "plm_gemm_tc_wide")(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
-        _p(status_word(a.device)), _stream()), "gemm_tc_pair" if pair else "gemm_tc_wide")
+        _p(status_word(a.device)), _stream()),
+        f"{'gemm_tc_pair' if pair else 'gemm_tc_wide'}{'_swiglu' if swiglu else ''} {M}x{N}x{K}", **_work(a, w, out))
     return out
 
 

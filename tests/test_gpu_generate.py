@@ -128,3 +128,12 @@ def test_command_line(model_dirs):
     assert [int(x[0]) for x in rows] == [0, 1] * 3                     # two layers, three iterations
     assert all(float(x[1]) > 0 and float(x[2]) > 0 and float(x[3]) > 0 for x in rows)
     assert r.stderr.count("Prefill: 6 tokens") == 3 and r.stderr.count("Generation: 6 tokens") == 3
+    # the per-kernel table: every launch between two events, a row per kind of launch with its time and rates
+    env = dict(os.environ, PICOLM_B200_TRACE="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "picolm_b200"), model_dirs["A_sharp"],
+                        "-p", "5,6,7,8,9,10", "-n", "4", "-t", "0", "--dtype", "bfloat16"], capture_output=True, text=True,
+                       timeout=300, env=env)
+    assert r.returncode == 0, r.stderr
+    table = [ln for ln in r.stderr.splitlines() if re.match(r"^(gemm|attention|rmsnorm|embed|argmax)", ln)]
+    assert any(ln.startswith("gemm_tc_skinny") for ln in table) and any(ln.startswith("attention") for ln in table)
+    assert all(float(ln.split()[-6]) > 0 for ln in table)              # every row has a device time
