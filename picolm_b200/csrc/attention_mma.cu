@@ -17,10 +17,13 @@
 //            splits' partial (max, sum, acc) go to a workspace and a small kernel
 //            merges them with exp(m_i - m) weights, as the reference's split
 //            kernel does (picolm/backend_gpu_kernels.cu:802, :911).
-// K and V pages are [64 keys][HD] contiguous in the cache; they are copied to
-// shared memory with cp.async (rows padded by 16 bytes so that ldmatrix has no
-// bank conflicts) in a multi-stage ring.
-#include "common.cuh"
+// K and V pages are [64 keys][HD] contiguous in the cache.  The prefill kernel copies them to shared
+// memory with cp.async (rows padded by 16 bytes so that ldmatrix has no bank conflicts) in a multi-stage
+// ring.  The decode kernel does the same for head sizes that are no multiple of 64; for those that are, one
+// thread asks for whole pages by TMA (cp.async.bulk.tensor through a tensor map over the cache, 128-byte
+// swizzle, an mbarrier per stage): unpadded tiles, one instruction per 8 KB instead of 512 copies of 16
+// bytes, and ldmatrix addresses that undo the swizzle.
+#include "tc_common.cuh"
 
 #ifndef PLM_HD
 #define PLM_HD 64
@@ -62,6 +65,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// A tile as TMA writes it with the 128-byte swizzle: HD / 64 parts of [64 rows][128 bytes], each 8 KB; within a
+// part, the 16-byte chunk c of row r lies at chunk c ^ (r % 8).  `chunk` counts 16-byte chunks of the whole row.
+constexpr bool HAS_TMA = HD % 64 == 0;
+constexpr uint32_t SW_TILE_BYTES = 64 * HD * 2;
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * 8192 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
 // Copy one page tile (64 rows of HD bf16, contiguous in global memory) into a padded smem tile.
@@ -112,6 +123,44 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[
         for (int dt = 0; dt < HD / 8; dt += 2) {
             uint32_t b[4];
             ldsm_x4_t(b, smem_u32(v_tile + key * LDS + dt * 8 + (lane >> 4) * 8));
+            mma_bf16(o[dt], a, b[0], b[1]);
+            mma_bf16(o[dt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// The same two products on a swizzled tile (shared-memory address `k_base` / `v_base`).
+template <int NKT>
+__device__ __forceinline__ void qk_tile_sw(float (&s)[NKT][4], const bf16* q_rows, uint32_t k_base, int key0, int lane,
+                                           int arow) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t a[4];
+        ldsm_x4(a, smem_u32(q_rows + arow * LDS + ks * 16 + (lane >> 4) * 8));
+#pragma unroll
+        for (int j = 0; j < NKT; j += 2) {
+            uint32_t b[4];
+            const int key = key0 + j * 8 + (lane & 7) + (lane >> 4) * 8;
+            ldsm_x4(b, k_base + sw_off(key, ks * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s[j], a, b[0], b[1]);
+            mma_bf16(s[j + 1], a, b[2], b[3]);
+        }
+    }
+}
+template <int NKT>
+__device__ __forceinline__ void pv_tile_sw(float (&o)[HD / 8][4], const float (&p)[NKT][4], uint32_t v_base, int key0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NKT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+        a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+        a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+        a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+        const int key = key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; dt += 2) {
+            uint32_t b[4];
+            ldsm_x4_t(b, v_base + sw_off(key, dt + (lane >> 4)));
             mma_bf16(o[dt], a, b[0], b[1]);
             mma_bf16(o[dt + 1], a, b[2], b[3]);
         }
@@ -289,6 +338,11 @@ constexpr size_t DC_RESULT_BYTES = (size_t)16 * (HD + 2) * sizeof(float);       
 constexpr size_t DC_AFTER_BYTES = DC_MERGE_BYTES + DC_RESULT_BYTES;
 constexpr size_t dc_smem(int q_rows) { return dc_q_bytes(q_rows) + (DC_TILES_BYTES > DC_AFTER_BYTES ? DC_TILES_BYTES : DC_AFTER_BYTES); }
 constexpr size_t DC_SMEM = dc_smem(16);
+// the TMA form: query rows, then (1024-byte aligned) the ring of unpadded tiles or what follows the loop, then the barriers
+constexpr size_t dc_smem_tma(int q_rows) {
+    return dc_q_bytes(q_rows) + 1024 +
+           ((size_t)2 * DC_STAGES * SW_TILE_BYTES > DC_AFTER_BYTES ? (size_t)2 * DC_STAGES * SW_TILE_BYTES : DC_AFTER_BYTES) + 64;
+}
 constexpr int DC_MAX_CLUSTER = 8;                                                   // portable cluster size
 
 // grid = (splits, G * row_groups, tokens).  With one split the output is written directly.  With
@@ -328,20 +382,34 @@ __device__ __forceinline__ void rotate16(uint4& lo, uint4& hi, const float* __re
     }
 }
 
-template <bool CLUSTER, bool ROPE>
+struct PageMaps {               // the TMA form: the caches as [pages * G * 64 rows, HD], boxes of 64 x 64
+    CUtensorMap k, v;
+};
+
+template <bool CLUSTER, bool ROPE, bool TMA>
 __global__ void __launch_bounds__(NT)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                    int max_pages, int H, int G, float scale_log2, int window, int row_groups, const Rotary rot,
-                   int q_rows) {
+                   int q_rows, const __grid_constant__ PageMaps maps, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const size_t q_bytes = (size_t)q_rows * LDS * sizeof(bf16);          // q_rows: 16, or 9 (8 heads and a row of zeros)
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
-    bf16* k_s = reinterpret_cast<bf16*>(smem_raw + q_bytes);
+    // after the query rows: the ring of tiles (padded for cp.async; 1024-byte aligned and unpadded for TMA)
+    const uint32_t ring = TMA ? ((smem_u32(smem_raw) + (uint32_t)q_bytes + 1023u) & ~1023u) : smem_u32(smem_raw) + (uint32_t)q_bytes;
+    uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    bf16* k_s = reinterpret_cast<bf16*>(ring_ptr);
     bf16* v_s = k_s + DC_STAGES * TILE_ELEMS;
-    float* merge = reinterpret_cast<float*>(smem_raw + q_bytes);         // reused after the last tile
-    float* result = reinterpret_cast<float*>(smem_raw + q_bytes + DC_MERGE_BYTES);
+    float* merge = reinterpret_cast<float*>(ring_ptr);                   // reused after the last tile
+    float* result = reinterpret_cast<float*>(ring_ptr + DC_MERGE_BYTES);
+    constexpr size_t RING_BYTES = (size_t)2 * DC_STAGES * SW_TILE_BYTES > DC_AFTER_BYTES ? (size_t)2 * DC_STAGES * SW_TILE_BYTES : DC_AFTER_BYTES;
+    const uint32_t full0 = ring + (uint32_t)RING_BYTES;                   // TMA: one barrier a stage
+    if (TMA && threadIdx.x == 0) {
+        for (int s = 0; s < DC_STAGES; ++s) plm_tc::mbar_init(full0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (TMA) __syncthreads();
     pdl_launch_dependents();
     // What describes the step (positions, page tables) was written before the step began, and pages
     // before a sequence's last one hold keys of earlier steps: all of that may be read before the
@@ -364,10 +432,24 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int* pages = block_table + (size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages;
 
     auto issue = [&](int i) {
-        const size_t base = ((size_t)PLM_PAGE_NO(pages[p_begin + i]) * G + g) * PLM_PAGE * HD;
-        const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
-        load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
-        load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
+        if constexpr (TMA) {
+            if (threadIdx.x == 0) {                     // a page's keys and values: HD / 64 boxes each, one barrier
+                const int st = i % DC_STAGES;
+                const int row0 = (PLM_PAGE_NO(pages[p_begin + i]) * G + g) * PLM_PAGE;
+                const uint32_t kd = ring + (uint32_t)(2 * st) * SW_TILE_BYTES, vd = kd + SW_TILE_BYTES;
+                plm_tc::mbar_expect_tx(full0 + 8 * st, 2 * SW_TILE_BYTES);
+#pragma unroll
+                for (int sub = 0; sub < HD / 64; ++sub) {
+                    plm_tc::tma_load_2d(kd + sub * 8192, &maps.k, full0 + 8 * st, sub * 64, row0);
+                    plm_tc::tma_load_2d(vd + sub * 8192, &maps.v, full0 + 8 * st, sub * 64, row0);
+                }
+            }
+        } else {
+            const size_t base = ((size_t)PLM_PAGE_NO(pages[p_begin + i]) * G + g) * PLM_PAGE * HD;
+            const int valid = pos + 1 - (p_begin + i) * PLM_PAGE;
+            load_tile(k_s + (i % DC_STAGES) * TILE_ELEMS, kc + base, valid);
+            load_tile(v_s + (i % DC_STAGES) * TILE_ELEMS, vc + base, valid);
+        }
     };
     const int n_first = min(n_pages, DC_STAGES - 1);                    // pages asked for before the loop
     const bool early = ROPE || n_first <= 0 || p_begin + n_first - 1 < page_last;  // none of them is written in this step
@@ -375,7 +457,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
 #pragma unroll
     for (int i = 0; i < DC_STAGES - 1; ++i) {
         if (i < n_pages) issue(i);
-        cp_commit();
+        if (!TMA) cp_commit();
     }
     if (early) pdl_wait();
     if (!CLUSTER && n_pages <= 0) {                     // an empty split: weight zero in the merge
@@ -416,9 +498,27 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
 
     for (int i = 0; i < n_pages; ++i) {
         if (i + DC_STAGES - 1 < n_pages) issue(i + DC_STAGES - 1);
-        cp_commit();
-        cp_wait<DC_STAGES - 1>();
-        __syncthreads();
+        const uint32_t kt_sw = ring + (uint32_t)(2 * (i % DC_STAGES)) * SW_TILE_BYTES, vt_sw = kt_sw + SW_TILE_BYTES;
+        if constexpr (TMA) {
+            // (the stage that was just asked for again was released by the barrier that ended the iteration before)
+            plm_tc::mbar_wait(full0 + 8 * (i % DC_STAGES), (uint32_t)((i / DC_STAGES) & 1), status, 5);
+            if (i == 0) __syncthreads();                // the query rows, written with plain stores above
+            if (p_begin + i == page_last) {
+                // Places of the page that hold no key yet may hold whatever an earlier owner of the page left:
+                // zeros instead, so that nothing of it reaches a sum (a masked score times a stale value).
+                const int first_free = pos + (ROPE ? 0 : 1) - page_last * PLM_PAGE;     // ROPE: this step's row is written below
+                for (int c = threadIdx.x; c < (PLM_PAGE - first_free) * (HD / 8); c += NT) {
+                    const int r = first_free + c / (HD / 8), ch = c % (HD / 8);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(kt_sw + sw_off(r, ch)), "r"(0u) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vt_sw + sw_off(r, ch)), "r"(0u) : "memory");
+                }
+                __syncthreads();
+            }
+        } else {
+            cp_commit();
+            cp_wait<DC_STAGES - 1>();
+            __syncthreads();
+        }
         const bf16* kt = k_s + (i % DC_STAGES) * TILE_ELEMS;
         const bf16* vt = v_s + (i % DC_STAGES) * TILE_ELEMS;
         if (ROPE && p_begin + i == page_last) {
@@ -436,8 +536,15 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
                 uint4 lo = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + g) * HD + j);
                 uint4 hi = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + g) * HD + HD / 2 + j);
                 rotate16(lo, hi, rot.cos, rot.sin, pos, j);
-                *reinterpret_cast<uint4*>(k_row + j) = lo;
-                *reinterpret_cast<uint4*>(k_row + HD / 2 + j) = hi;
+                if constexpr (TMA) {
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(kt_sw + sw_off(in_page, j / 8)),
+                                 "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(kt_sw + sw_off(in_page, (HD / 2 + j) / 8)),
+                                 "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                } else {
+                    *reinterpret_cast<uint4*>(k_row + j) = lo;
+                    *reinterpret_cast<uint4*>(k_row + HD / 2 + j) = hi;
+                }
                 if (to_cache) {
                     *reinterpret_cast<uint4*>(rot.kc_w + cache_row + j) = lo;
                     *reinterpret_cast<uint4*>(rot.kc_w + cache_row + HD / 2 + j) = hi;
@@ -445,7 +552,11 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
             } else if (threadIdx.x >= 32 && threadIdx.x < 32 + HD / 8) {
                 const int j = (threadIdx.x - 32) * 8;
                 const uint4 v = *reinterpret_cast<const uint4*>(qkv_row + (size_t)(H + G + g) * HD + j);
-                *reinterpret_cast<uint4*>(v_row + j) = v;
+                if constexpr (TMA)
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(vt_sw + sw_off(in_page, j / 8)),
+                                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                else
+                    *reinterpret_cast<uint4*>(v_row + j) = v;
                 if (to_cache) *reinterpret_cast<uint4*>(rot.vc_w + cache_row + j) = v;
             }
             __syncthreads();
@@ -455,13 +566,19 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
             float s[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-            qk_tile<2>(s, q_s, kt, warp * 16, lane, min(lane & 15, q_rows - 1));
-            softmax_block<2>(s, o, m, l, scale_log2, key_base, pos, pos, lo, lo, lane);
-            pv_tile<2>(o, s, vt, warp * 16, lane);
+            if constexpr (TMA) {
+                qk_tile_sw<2>(s, q_s, kt_sw, warp * 16, lane, min(lane & 15, q_rows - 1));
+                softmax_block<2>(s, o, m, l, scale_log2, key_base, pos, pos, lo, lo, lane);
+                pv_tile_sw<2>(o, s, vt_sw, warp * 16, lane);
+            } else {
+                qk_tile<2>(s, q_s, kt, warp * 16, lane, min(lane & 15, q_rows - 1));
+                softmax_block<2>(s, o, m, l, scale_log2, key_base, pos, pos, lo, lo, lane);
+                pv_tile<2>(o, s, vt, warp * 16, lane);
+            }
         }
         __syncthreads();
     }
-    cp_wait<0>();
+    if (!TMA) cp_wait<0>();
     __syncthreads();
 
     // merge the four warps' partial results: merge[w][row][0..HD) = acc, [HD] = m, [HD+1] = l
@@ -577,6 +694,14 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
 // three, which leave room for the CTAs of the kernel behind it to ask for their weights meanwhile.
 int decode_q_rows(int heads_per_kv_head, long ctas) { return heads_per_kv_head <= 8 && ctas > 3 * PLM_SM_COUNT ? 9 : 16; }
 
+// The caches as TMA sees them: [n_pages * G * 64 rows, HD] bf16, boxes of 64 rows x 64 columns, 128-byte swizzle.
+int page_maps(PageMaps* maps, const void* kc, const void* vc, int n_pages, int G) {
+    const long rows = (long)n_pages * G * PLM_PAGE;
+    int rc = plm_tc::make_map(&maps->k, kc, rows, HD, HD, 64);
+    if (rc == PLM_OK) rc = plm_tc::make_map(&maps->v, vc, rows, HD, HD, 64);
+    return rc;
+}
+
 template <typename K>
 int set_smem(K kern, size_t bytes) {
     if (bytes <= 48 * 1024) return PLM_OK;
@@ -617,35 +742,45 @@ extern "C" long plm_attn_decode_workspace(int n_tokens, int H, int n_splits) {
 // Decode: one query token per row of q [T, H, HD], at position tok_pos[t] of sequence tok_seq[t].
 // With a workspace the ranges' partial results pass through it and a second kernel merges them;
 // without one (at most 8 ranges) the ranges are the CTAs of a cluster and merge in shared memory.
+// `n_pages`: pages of the cache (kc and vc are [n_pages, G, 64, HD]); `status`: the device word that a wait
+// which runs out writes to (head sizes that are multiples of 64 ask for pages by TMA and wait on barriers).
 extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, void* out, float* workspace,
                                const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
-                               int n_tokens, int H, int G, float scale, int window, int n_splits, cudaStream_t stream) {
+                               int n_tokens, int H, int G, float scale, int window, int n_splits, int n_pages,
+                               int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535) return PLM_ERR_SHAPE;
+    constexpr bool TMA = HAS_TMA;
     static bool configured = false;
     if (!configured) {
-        int rc = set_smem(attn_decode_kernel<false, false>, DC_SMEM);
-        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, false>, DC_SMEM);
+        int rc = set_smem(attn_decode_kernel<false, false, TMA>, TMA ? dc_smem_tma(16) : DC_SMEM);
+        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, false, TMA>, TMA ? dc_smem_tma(16) : DC_SMEM);
         if (rc != PLM_OK) return rc;
         configured = true;
+    }
+    PageMaps maps = {};
+    if (TMA) {
+        if (n_pages <= 0 || !status) return PLM_ERR_SHAPE;
+        int rc = page_maps(&maps, kc, vc, n_pages, G);
+        if (rc != PLM_OK) return rc;
     }
     const int R = H / G, row_groups = (R + 15) / 16;
     if (G * row_groups > 65535) return PLM_ERR_SHAPE;
     const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
-    const size_t smem = dc_smem(q_rows);
+    const size_t smem = TMA ? dc_smem_tma(q_rows) : dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
     if (n_splits > 1 && !workspace) {                       // the splits merge inside their cluster
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
-        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false>, grid, dim3(NT), smem, stream, (const bf16*)q,
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false, TMA>, grid, dim3(NT), smem, stream, (const bf16*)q,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
@@ -657,34 +792,41 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
 extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* out, float* workspace,
                                     const float* cos_t, const float* sin_t, const int* tok_pos, const int* tok_seq,
                                     const int* block_table, int max_pages, int n_tokens, int H, int G, float scale,
-                                    int window, int n_splits, cudaStream_t stream) {
+                                    int window, int n_splits, int n_pages, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535 || !cos_t || !sin_t) return PLM_ERR_SHAPE;
+    constexpr bool TMA = HAS_TMA;
     static bool configured = false;
     if (!configured) {
-        int rc = set_smem(attn_decode_kernel<false, true>, DC_SMEM);
-        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, true>, DC_SMEM);
+        int rc = set_smem(attn_decode_kernel<false, true, TMA>, TMA ? dc_smem_tma(16) : DC_SMEM);
+        if (rc == PLM_OK) rc = set_smem(attn_decode_kernel<true, true, TMA>, TMA ? dc_smem_tma(16) : DC_SMEM);
         if (rc != PLM_OK) return rc;
         configured = true;
+    }
+    PageMaps maps = {};
+    if (TMA) {
+        if (n_pages <= 0 || !status) return PLM_ERR_SHAPE;
+        int rc = page_maps(&maps, kc, vc, n_pages, G);
+        if (rc != PLM_OK) return rc;
     }
     const int R = H / G, row_groups = (R + 15) / 16;
     if (G * row_groups > 65535) return PLM_ERR_SHAPE;
     const Rotary rot = {cos_t, sin_t, (bf16*)kc, (bf16*)vc};
     const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
-    const size_t smem = dc_smem(q_rows);
+    const size_t smem = TMA ? dc_smem_tma(q_rows) : dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
     if (n_splits > 1 && !workspace) {
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
-        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
+        return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)qkv, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
-    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true>, grid, dim3(NT), smem, stream, (const bf16*)qkv,
+    int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true, TMA>, grid, dim3(NT), smem, stream, (const bf16*)qkv,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));

@@ -109,7 +109,11 @@ def decode_ctas_per_sm(head_dim: int, heads_per_kv_head: int) -> int:
     """How many CTAs of the decode kernel share an SM: its shared memory (three stages of a key and a value
     tile of 64 padded rows, and 9 or 16 query rows; csrc/attention_mma.cu) against the SM's 227 KB."""
     row = (head_dim + 8) * 2
-    smem = (9 if heads_per_kv_head <= 8 else 16) * row + 6 * 64 * row
+    q_rows = (9 if heads_per_kv_head <= 8 else 16) * row
+    if head_dim % 64 == 0:                                       # pages by TMA: unpadded tiles, 1024-byte aligned
+        smem = q_rows + 1024 + 6 * 64 * head_dim * 2 + 64
+    else:
+        smem = q_rows + 6 * 64 * row
     return max(1, min(6, (227 * 1024) // (smem + 1024)))         # (registers allow six)
 
 
@@ -160,7 +164,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _cache_bounds(lib, flags, k_cache, block_table)
     _check(_fn(lib, "plm_attn_decode", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
-        block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), _stream()),
+        block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), k_cache.shape[0],
+        _p(status_word(q.device)), _stream()),
         f"attention_decode T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1)
     return out
 
@@ -209,7 +214,7 @@ def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_he
     _check(_fn(lib, "plm_attn_decode_rope", flags)(
         _p(qkv), _p(kv.k), _p(kv.v), _p(out), _p(ws), _p(rotation.cos), _p(rotation.sin), _p(step.tok_pos),
         _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, float(scale), int(kv.window or 0),
-        int(n_splits), _stream()), f"attention_decode_rope T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1,
+        int(n_splits), kv.k.shape[0], _p(status_word(qkv.device)), _stream()), f"attention_decode_rope T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1,
         nbytes=T * (step.max_position + 1) * 2 * G * hd * 2)
     return out
 
