@@ -73,6 +73,7 @@ class DecodeGraph:
         self.step = StepBatch(
             n_seqs=B, n_tokens=B, n_want=B, slots=None, new_lens=None, start_pos=None,
             max_position=max_len - 1,                     # the graph's length class (see length_class)
+            max_new=1,
             is_decode=True, tok_ids=self.d[0], tok_seq=self.d[1], tok_pos=self.d[2], seq_slot=self.d[3],
             seq_start=self.d[4], seq_kv_len=self.d[5], want_rows=self.d[6],
             block_tables=[self.d[7 + g].view(B, P) for g in range(n_groups)],

@@ -54,6 +54,11 @@ class Engine:
             # table needs every launch between two events
             self.use_graphs = False
         self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
+        self._prompt_graphs: Dict[Tuple[int, int], "PromptGraph"] = {}
+        # steps with prompts replay a graph too where every sequence wants its last token's logits (generation);
+        # float32 runs launch them kernel by kernel (their kernels take longer than the launches)
+        self.prompt_graphs = (self.runtime.dtype == torch.bfloat16 and
+                              all(getattr(part, "graph_safe_prompts", False) for b in model.blocks for _, part in b.parts()))
         # one id per live sequence, and never fewer than the largest captured batch size (its padding rows read it)
         from .decode_graph import BUCKETS
         self._tokens = torch.zeros(max(BUCKETS[-1], self.cache.max_seqs), dtype=torch.int32,
@@ -202,6 +207,8 @@ class Engine:
         graphed = False
         if self.use_graphs and self.model.layer_hook is None and all(len(toks) == 1 for _, toks in entries):
             logits, graphed = self._decode_with_graph(entries, wants, device_tokens)
+        elif self.use_graphs and self.prompt_graphs and self.model.layer_hook is None and device_tokens is None:
+            logits, graphed = self._prompts_with_graph(entries, wants)
         if not graphed:
             batch = build_step_batch(entries, wants, self.cache, self.runtime.device)
             self.counters["h2d_bytes"] += batch.h2d_bytes
@@ -215,6 +222,28 @@ class Engine:
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))
         return logits
+
+    def _prompts_with_graph(self, entries, wants) -> Tuple[Optional[torch.Tensor], bool]:
+        """A step with prompts through the captured graph of its size class.  Returns the logits (None if none are
+        wanted) and whether a graph ran: it does not if the step is too large or logits are wanted at other
+        places than every sequence's last token."""
+        from .prompt_graph import PromptGraph, seq_class, token_class
+        n = len(entries)
+        n_tokens = sum(len(toks) for _, toks in entries)
+        key = (token_class(n_tokens), seq_class(n))
+        if key[0] is None or key[1] is None:
+            return None, False
+        n_want = sum(len(w) for w in wants)
+        if n_want not in (0, n) or (n_want and any(list(w) != [len(toks) - 1] for w, (_, toks) in zip(wants, entries))):
+            return None, False
+        g = self._prompt_graphs.get(key)
+        if g is None:
+            g = PromptGraph(self, key[0], key[1])
+            g.capture()
+            self._prompt_graphs[key] = g
+        logits = g.run(entries)
+        self.counters["h2d_bytes"] += g.step.h2d_bytes
+        return (logits if n_want else None), True
 
     def _decode_with_graph(self, entries, wants, device_tokens=None) -> Tuple[Optional[torch.Tensor], bool]:
         """One token for each sequence through the captured graph of the batch's size class.  Returns the

@@ -23,6 +23,7 @@ class StepBatch:
     new_lens: Optional[List[int]]         # host: tokens each sequence brings
     start_pos: Optional[List[int]]        # host: position of each sequence's first new token
     max_position: int                     # host: largest position written by this step
+    max_new: int                          # host: the most tokens a sequence brings (an upper bound in a captured step)
     is_decode: bool                       # every sequence brings exactly one token
     tok_ids: torch.Tensor                 # int32 [T]
     tok_seq: torch.Tensor                 # int32 [T]  index of the token's sequence within the step
@@ -97,7 +98,7 @@ def build_step_batch(entries: Sequence[tuple], wants: Sequence[Sequence[int]], c
         o += n
     return StepBatch(
         n_seqs=B, n_tokens=T, n_want=W, slots=slots, new_lens=new_lens, start_pos=start,
-        max_position=max(s + n for s, n in zip(start, new_lens)) - 1,
+        max_position=max(s + n for s, n in zip(start, new_lens)) - 1, max_new=max(new_lens),
         is_decode=all(n == 1 for n in new_lens),
         tok_ids=dviews[0], tok_seq=dviews[1], tok_pos=dviews[2], seq_slot=dviews[3], seq_start=dviews[4],
         seq_kv_len=dviews[5], want_rows=dviews[6],

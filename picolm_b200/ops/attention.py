@@ -228,7 +228,7 @@ def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> tor
             return attention_decode(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                                     splits, window=kv.window)
         prefill = attention_prefill_tc if attention_tc_supported(q) else attention_prefill
-        return prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table, max(step.new_lens),
+        return prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table, step.max_new,
                        num_kv_heads, scale, window=kv.window)
     return attention_rows(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
                           window=kv.window)

@@ -54,6 +54,10 @@ class Part:
     # through this part may be captured in a CUDA graph.  The engine uses graphs only if every part of
     # every block says so.
     graph_safe: bool = False
+    # The same promise for steps with prompts (several tokens a sequence): nothing of the step is read on the
+    # host, not even `step.slots` or `step.new_lens` (they are None in a captured step), and rows that belong to no
+    # sequence (padding) may hold anything.  Steps with prompts replay graphs only if every part says so.
+    graph_safe_prompts: bool = False
 
     def __init__(self, params: Mapping[str, Any], runtime: Optional[Runtime]):
         self.params = dict(params)

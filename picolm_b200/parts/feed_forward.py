@@ -52,6 +52,7 @@ class GatedMLP(Part):
 
     takes_scaled_rows = True          # h goes into a product and nowhere else
     graph_safe = True
+    graph_safe_prompts = True
 
     def forward(self, h, step):
         if self.fused:

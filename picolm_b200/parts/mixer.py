@@ -42,6 +42,10 @@ class Attention(Part):
         from sizes fixed per batch size); the position encoding has to say the same of itself."""
         return bool(getattr(self.position, "graph_safe", False))
 
+    @property
+    def graph_safe_prompts(self) -> bool:
+        return bool(getattr(self.position, "graph_safe_prompts", False))
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         p = self.params

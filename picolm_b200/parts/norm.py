@@ -28,6 +28,7 @@ class RMSNorm(Part):
 
     can_defer_scale = True
     graph_safe = True
+    graph_safe_prompts = True
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, defer_scale: bool = False):
         """Normalise `x + pending`.  Without `rows` the sum is written back to the

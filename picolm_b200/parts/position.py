@@ -57,6 +57,7 @@ class RotaryEncoding(Part):
     ("half" or "adjacent"), max_positions."""
 
     graph_safe = True
+    graph_safe_prompts = True
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -99,6 +100,7 @@ class NoPositionEncoding(Part):
     """Queries and keys go through unrotated."""
 
     graph_safe = True
+    graph_safe_prompts = True
 
     def prepare(self, n_positions: int) -> None:
         pass

@@ -207,3 +207,47 @@ def test_sampling_with_steps_in_flight_in_bfloat16(model_dirs):
     assert every == flight
     assert len(every[0]) <= 6 and len(every[3]) <= 18 and any(len(o) == 40 for o in every)
     eng.cache.check()
+
+
+def test_prompt_steps_from_graphs_give_the_logits_of_single_launches(tmp_path):
+    """Steps with prompts whose sequences want their last token's logits replay a captured graph of their size
+    class (tokens padded to the class, sequences padded with empty ones): the same logits as the step launched
+    kernel by kernel, for single prompts, unequal batches, a prompt fed in pieces, and size classes met twice
+    (the second time the padding differs), at the 1B widths and a tiny size."""
+    from picolm_b200.engine import Engine
+    d = make_model_dir(str(tmp_path / "wide"), WIDE, 24, sharpen=4.0)
+    cfg, w = P.load_model(d)
+    eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
+    plain = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
+    plain.prompt_graphs = False
+    assert eng.prompt_graphs
+    V = WIDE["vocab_size"]
+
+    def last_logits(e, prompts, pieces=None):
+        slots = [e.new_sequence() for _ in prompts]
+        try:
+            if pieces:                                     # the first prompt in pieces, nothing wanted but at the end
+                o = 0
+                for n in pieces[:-1]:
+                    assert e.step([(slots[0], prompts[0][o:o + n])], [[]]) is None
+                    o += n
+                return e.step([(slots[0], prompts[0][o:])]).float().cpu()
+            return e.step(list(zip(slots, prompts))).float().cpu()
+        finally:
+            for s in slots:
+                e.end_sequence(s)
+
+    cases = [[random_tokens(300, V, 1)], [random_tokens(n, V, 10 + n) for n in (150, 9, 64, 65)],
+             [random_tokens(257, V, 2)], [random_tokens(n, V, 20 + n) for n in (1, 40)], [random_tokens(64, V, 3)]]
+    for prompts in cases:
+        got, want = last_logits(eng, prompts), last_logits(plain, prompts)
+        assert_close(got, want, "bfloat16", f"prompts of {[len(p) for p in prompts]} from a graph")
+        ref = torch.stack([P.forward(cfg, w, p, act_dtype=torch.bfloat16)[-1] for p in prompts])
+        assert_close(got, ref, "bfloat16", "against the plain implementation")
+    long = random_tokens(500, V, 4)
+    got = last_logits(eng, [long], pieces=[200, 130, 170])
+    assert_close(got, P.forward(cfg, w, long, act_dtype=torch.bfloat16)[-1:], "bfloat16", "a prompt in pieces from graphs")
+    assert len(eng._prompt_graphs) >= 5 and not plain._prompt_graphs
+    eng.cache.check()
+    from picolm_b200 import ops
+    ops.check_status()
