@@ -286,7 +286,10 @@ def main():
     pf_ms = statistics.median(times)
     flops = prefill_flops(cfg_dict, prefill_tokens)
     prefill = {"value": round(prefill_tokens / pf_ms * 1e3, 1), "tokens": prefill_tokens, "ms": round(pf_ms, 3),
-               "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "ms_min_max": [round(min(times), 3), round(max(times), 3)], "from_graph": bool(engine._prompt_graphs)}
+    if "bf16_tflops_sustained" in pk:       # the same against what a long cuBLAS loop sustains under the power cap
+        prefill["frac_of_sustained"] = round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # ----------------------------------------------------------------- decode
     w_bytes = engine.model.weight_bytes_per_step()
@@ -392,7 +395,8 @@ def main():
     gen_new = max(args.warmup + 2 * args.steps, int(1000.0 / ms))
     gen_new = max(8, min(gen_new, per_seq - prompt_len - 2))
     ps = prompts(B)
-    generate(engine, ps, max_tokens=4, temperature=0.0, stop_ids=[], max_batch=B)            # warm-up
+    # warm-up over the same lengths: decode steps are captured per length class, and a service has its classes captured
+    generate(engine, ps, max_tokens=gen_new, temperature=0.0, stop_ids=[], max_batch=B)
     engine.reset_counters()
     outs, stats = generate(engine, ps, max_tokens=gen_new, temperature=0.0, stop_ids=[], max_batch=B,
                            return_stats=True)

@@ -57,7 +57,8 @@ class Engine:
         self._prompt_graphs: Dict[Tuple[int, int], "PromptGraph"] = {}
         # steps with prompts replay a graph too where every sequence wants its last token's logits (generation);
         # float32 runs launch them kernel by kernel (their kernels take longer than the launches)
-        self.prompt_graphs = (self.runtime.dtype == torch.bfloat16 and
+        import os
+        self.prompt_graphs = (os.environ.get("PICOLM_B200_PROMPT_GRAPHS", "1") != "0" and self.runtime.dtype == torch.bfloat16 and
                               all(getattr(part, "graph_safe_prompts", False) for b in model.blocks for _, part in b.parts()))
         # one id per live sequence, and never fewer than the largest captured batch size (its padding rows read it)
         from .decode_graph import BUCKETS
