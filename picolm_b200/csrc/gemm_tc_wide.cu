@@ -12,6 +12,11 @@
 //   EPI_STORE   out = product (fp32 or bf16)
 //   EPI_SWIGLU  W's rows come in tiles of 64 gate rows followed by their 64 up rows;
 //               out[t, f] = silu(gate) * up, [T, F/2] in bf16
+//   EPI_RESIDUAL out += product, out being the fp32 residual stream (x = x + delta,
+//               picolm/model_core.c:3120 and 3201).  A thread of the epilogue holds one token's row of
+//               the accumulator, and rows of the stream lie far apart: each warp turns its 32 x 32 piece
+//               over in shared memory, so that a quarter of a warp reads, adds to and writes 128
+//               consecutive bytes of one row.
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
 // epilogue.  Waits on mbarriers are bounded; a wait that runs out records where in `status`
 // and the CTA drains and leaves.
@@ -36,11 +41,13 @@ using namespace plm_tc;
 
 namespace {
 
-constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
+constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2;
+constexpr int TURN_LD = 36;                                  // floats per row of a warp's 32 x 32 piece: 16-byte rows, no bank conflicts
+constexpr size_t TURN_BYTES = 4 * 32 * TURN_LD * 4;          // for the four epilogue warps
 
 __host__ __device__ constexpr int stages_of(int bn) { return bn >= 256 ? 4 : 6; }
-__host__ __device__ constexpr size_t wide_smem(int bn) {
-    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256;
+__host__ __device__ constexpr size_t wide_smem(int bn, int epi = EPI_STORE) {
+    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + (epi == EPI_RESIDUAL ? TURN_BYTES : 0);
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -71,7 +78,9 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_pair(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 __host__ __device__ constexpr int pair_stages() { return 6; }
-__host__ __device__ constexpr size_t pair_smem() { return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256; }
+__host__ __device__ constexpr size_t pair_smem(int epi = EPI_STORE) {
+    return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + (epi == EPI_RESIDUAL ? TURN_BYTES : 0);
+}
 
 template <int BN, int EPI, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -91,6 +100,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_full0 = bars + 16 * STAGES,
                    acc_empty0 = acc_full0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (acc_empty0 + 16 - raw));
+    float* turn_base = reinterpret_cast<float*>(smem_raw + (bars + 256 - raw));    // EPI_RESIDUAL only
     __shared__ int s_abort;
 
     pdl_launch_dependents();
@@ -233,6 +243,48 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         }
                     }
                 }
+            } else if (EPI == EPI_RESIDUAL) {
+                float* turn = turn_base + quarter * 32 * TURN_LD;
+                const int row0 = m0 + quarter * 32;                      // this warp's 32 token rows
+                const int sub = lane >> 3, col = (lane & 7) * 4;         // pass p: row 4 p + sub, four columns from col
+                float* outf = reinterpret_cast<float*>(out);
+                const bool aligned = (ldo % 4 == 0) && ((uintptr_t)outf % 16 == 0);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (f0 + c >= F) break;
+                    const bool vec = aligned && (f0 + c + 32 <= F);
+                    float4 old[8];
+                    if (vec) {
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) {
+                            const int row = row0 + 4 * p + sub;
+                            old[p] = row < T ? *reinterpret_cast<const float4*>(outf + (size_t)row * ldo + f0 + c + col)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                    uint32_t r[32];
+                    tc_ld32(tacc + c, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<uint4*>(turn + lane * TURN_LD + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) {
+                        const int row = row0 + 4 * p + sub;
+                        const float4 d = *reinterpret_cast<const float4*>(turn + (4 * p + sub) * TURN_LD + col);
+                        if (row >= T) continue;
+                        float* dst = outf + (size_t)row * ldo + f0 + c + col;
+                        if (vec) {
+                            *reinterpret_cast<float4*>(dst) = make_float4(old[p].x + d.x, old[p].y + d.y, old[p].z + d.z, old[p].w + d.w);
+                        } else {
+                            const float dd[4] = {d.x, d.y, d.z, d.w};
+                            for (int i = 0; i < 4; ++i)
+                                if (f0 + c + col + i < F) dst[i] += dd[i];
+                        }
+                    }
+                    __syncwarp();                                        // the piece is read before the next one overwrites it
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
@@ -285,7 +337,7 @@ template <int EPI, typename OutT>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
                 cudaStream_t stream) {
     static bool configured = false;
-    constexpr size_t smem = pair_smem();
+    constexpr size_t smem = pair_smem(EPI);
     auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -303,7 +355,7 @@ template <int BN, int EPI, typename OutT>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
            cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0) {
     static bool configured = false;
-    constexpr size_t smem = wide_smem(BN);
+    constexpr size_t smem = wide_smem(BN, EPI);
     auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -446,4 +498,25 @@ extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out
     if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
     if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     return PLM_ERR_DTYPE;
+}
+
+// resid[T, F] += x[T, K] * w[F, K]^T in place, resid in float32 (the residual stream), T > 64; operands as for
+// plm_gemm_tc_wide.  `pair` != 0: by pairs of CTAs (for at least 256 tokens and 256 features).  K is not cut.
+extern "C" int plm_gemm_tc_wide_residual(const void* x, const void* w, float* resid, int T, int F, int K, long ldx,
+                                         long ldw, long ldr, int pair, int* status, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if ((uintptr_t)resid % 4) return PLM_ERR_ALIGN;
+    CUtensorMap mx, mw;
+    int rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
+    if (pair) {
+        if ((rc = make_map(&mw, w, F, K, ldw, 128)) != PLM_OK) return rc;
+        return launch_pair<EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
+    }
+    int bn, k_splits, kb_per;
+    wide_plan(T, F, K, &bn, &k_splits, &kb_per);
+    if ((rc = make_map(&mw, w, F, K, ldw, bn)) != PLM_OK) return rc;
+    if (bn == 256) return launch<256, EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
+    return launch<128, EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
 }
