@@ -46,8 +46,8 @@ constexpr int TURN_LD = 36;                                  // floats per row o
 constexpr size_t TURN_BYTES = 4 * 32 * TURN_LD * 4;          // for the four epilogue warps
 
 __host__ __device__ constexpr int stages_of(int bn) { return bn >= 256 ? 4 : 6; }
-__host__ __device__ constexpr size_t wide_smem(int bn, int epi = EPI_STORE) {
-    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + (epi == EPI_RESIDUAL ? TURN_BYTES : 0);
+__host__ __device__ constexpr size_t wide_smem(int bn) {
+    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + TURN_BYTES;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -78,15 +78,145 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_pair(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 __host__ __device__ constexpr int pair_stages() { return 6; }
-__host__ __device__ constexpr size_t pair_smem(int epi = EPI_STORE) {
-    return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + (epi == EPI_RESIDUAL ? TURN_BYTES : 0);
+__host__ __device__ constexpr size_t pair_smem() {
+    return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + TURN_BYTES;
+}
+
+// ---------------------------------------------------------------- the work of a CTA
+// A CTA walks over pieces of work, each a range of K blocks of one output tile.  Two ways to hand them out:
+//   units   (tile, part of K) number first, first + step, ...; every part of K is a piece of its own whose
+//           result goes to its slice of the output (k_splits == 1: whole tiles)
+//   stream  all K blocks of all tiles in a row, cut into one equal range per CTA.  A range starts and ends
+//           anywhere, so all SMs work to the end whatever the number of tiles.  The CTA whose range holds a
+//           tile's first K block owns the tile; a CTA that starts inside a tile leaves its part (fp32) in its
+//           own slot of a workspace and raises its flag; the owner adds the parts of the CTAs after it, in
+//           their order, and writes the tile.  A part is the FIRST piece of its CTA and an owner's tile its
+//           LAST, and a part waits for nothing: no cycle of waits.
+constexpr int PIECE_WHOLE = 0, PIECE_PART = 1, PIECE_OWNER = 2;
+
+// A build with -DPLM_WIDE_TRACE records when (globaltimer, ns) each CTA of the single-CTA form passed the points
+// marked WIDE_TRACE below; plm_gemm_tc_wide_trace_read copies the table out.
+#ifdef PLM_WIDE_TRACE
+__device__ unsigned long long plm_wide_trace[PLM_SM_COUNT][16];
+#define WIDE_TRACE(point)                                                                              \
+    do {                                                                                               \
+        unsigned long long t_;                                                                         \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                         \
+        if (!PAIR && blockIdx.x < PLM_SM_COUNT && (point) < 16) plm_wide_trace[blockIdx.x][point] = t_; \
+    } while (0)
+#else
+#define WIDE_TRACE(point) do { } while (0)
+#endif
+struct Piece { int tile, ks, kb_begin, kb_end, kind; long tile_end; };
+struct Walk {
+    bool stream;
+    int n_kb, n_tiles_mn, kb_per_split;
+    int unit, unit_end, unit_step;                                       // units
+    long pos, hi;                                                        // stream
+    __host__ __device__ bool next(Piece& w) {
+        if (stream) {
+            if (pos >= hi) return false;
+            w.tile = (int)(pos / n_kb);
+            w.ks = 0;
+            w.kb_begin = (int)(pos - (long)w.tile * n_kb);
+            w.tile_end = (long)(w.tile + 1) * n_kb;
+            const long e = hi < w.tile_end ? hi : w.tile_end;
+            w.kb_end = w.kb_begin + (int)(e - pos);
+            w.kind = w.kb_begin > 0 ? PIECE_PART : (e < w.tile_end ? PIECE_OWNER : PIECE_WHOLE);
+            pos = e;
+            return true;
+        }
+        if (unit >= unit_end) return false;
+        w.tile = unit % n_tiles_mn;
+        w.ks = unit / n_tiles_mn;
+        w.kb_begin = w.ks * kb_per_split;
+        w.kb_end = n_kb < w.kb_begin + kb_per_split ? n_kb : w.kb_begin + kb_per_split;
+        w.kind = PIECE_WHOLE;
+        unit += unit_step;
+        return true;
+    }
+};
+// where CTA `cta` of `ctas` starts in the row of `total` K blocks
+__host__ __device__ inline long stream_begin(long total, int ctas, int cta) { return total * cta / ctas; }
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the four epilogue warps
+
+// A part in the workspace: [column / 4][row 0..127][4], so that the 32 rows of a warp lie side by side.
+__device__ __forceinline__ size_t part_offset(int row, int col) { return ((size_t)(col >> 2) * BM + row) * 4; }
+
+// --- a warp's 32 rows x 32 (fp32) or 64 (bf16) columns, turned over in shared memory: a thread holds a row,
+// --- but a quarter of a warp writes 128 consecutive bytes of one row
+__device__ __forceinline__ void turn_put_f32(float* turn, int lane, const uint32_t* r) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<uint4*>(turn + lane * TURN_LD + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+}
+// 32 floats as bf16 into the first or second half of the thread's row
+__device__ __forceinline__ void turn_put_bf16(float* turn, int lane, int half, const uint32_t* r) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<uint4*>(turn + lane * TURN_LD + half * 16 + i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+}
+// rows row0.. of out[., col0 .. col0 + 63] (below col_end) from the turned piece
+__device__ __forceinline__ void turn_write_bf16(const float* turn, int lane, bf16* out, long ldo, int row0, int T,
+                                                int col0, int col_end, bool aligned) {
+    const int sub = lane >> 3, col = col0 + (lane & 7) * 8;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const int row = row0 + 4 * p + sub;
+        const uint4 v = *reinterpret_cast<const uint4*>(turn + (4 * p + sub) * TURN_LD + (lane & 7) * 4);
+        if (row >= T || col >= col_end) continue;
+        bf16* dst = out + (size_t)row * ldo + col;
+        if (aligned && col + 8 <= col_end) {
+            *reinterpret_cast<uint4*>(dst) = v;
+        } else {
+            const bf16* e = reinterpret_cast<const bf16*>(&v);
+            for (int i = 0; i < 8; ++i)
+                if (col + i < col_end) dst[i] = e[i];
+        }
+    }
+}
+// the same for 32 fp32 columns; ADD: out += piece, `old` holding out's values where `vec` (read before)
+template <bool ADD>
+__device__ __forceinline__ void turn_write_f32(const float* turn, int lane, float* out, long ldo, int row0, int T,
+                                               int col0, int col_end, bool vec, const float4* old) {
+    const int sub = lane >> 3, col = col0 + (lane & 7) * 4;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const int row = row0 + 4 * p + sub;
+        const float4 d = *reinterpret_cast<const float4*>(turn + (4 * p + sub) * TURN_LD + (lane & 7) * 4);
+        if (row >= T) continue;
+        float* dst = out + (size_t)row * ldo + col;
+        if (vec) {
+            *reinterpret_cast<float4*>(dst) = ADD ? make_float4(old[p].x + d.x, old[p].y + d.y, old[p].z + d.z, old[p].w + d.w) : d;
+        } else {
+            const float dd[4] = {d.x, d.y, d.z, d.w};
+            for (int i = 0; i < 4; ++i)
+                if (col + i < col_end) dst[i] = ADD ? dst[i] + dd[i] : dd[i];
+        }
+    }
 }
 
 template <int BN, int EPI, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
-                    int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride) {
+                    int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride,
+                    float* parts, int* flags) {
     static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
     constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
@@ -100,20 +230,31 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_full0 = bars + 16 * STAGES,
                    acc_empty0 = acc_full0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (acc_empty0 + 16 - raw));
-    float* turn_base = reinterpret_cast<float*>(smem_raw + (bars + 256 - raw));    // EPI_RESIDUAL only
-    __shared__ int s_abort;
+    float* turn_base = reinterpret_cast<float*>(smem_raw + (bars + 256 - raw));
+    __shared__ int s_abort, s_parts_missing;
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (K + BK - 1) / BK;
-    const int n_tiles_mn = m_tiles * n_tiles;                            // PAIR: tiles of 256 tokens
-    const int n_tiles_total = n_tiles_mn * k_splits;                     // units of work: (tile, part of K)
     const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
-    const int first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x, tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
     constexpr int TILE_M = PAIR ? 2 * BM : BM;
+    const bool stream = !PAIR && parts != nullptr;
+    Walk walk0;
+    walk0.stream = stream;
+    walk0.n_kb = n_kb;
+    walk0.n_tiles_mn = m_tiles * n_tiles;                                // PAIR: tiles of 256 tokens
+    walk0.kb_per_split = kb_per_split;
+    walk0.unit = PAIR ? blockIdx.x / 2 : blockIdx.x;
+    walk0.unit_step = PAIR ? gridDim.x / 2 : gridDim.x;
+    walk0.unit_end = walk0.n_tiles_mn * k_splits;
+    const long total_kb = (long)walk0.n_tiles_mn * n_kb;
+    walk0.pos = stream ? stream_begin(total_kb, gridDim.x, blockIdx.x) : 0;
+    walk0.hi = stream ? stream_begin(total_kb, gridDim.x, blockIdx.x + 1) : 0;
 
     if (threadIdx.x == 0) {
+        WIDE_TRACE(0);
         s_abort = 0;
+        s_parts_missing = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, PAIR ? 256 : 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -139,13 +280,33 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool waited = false;
-            int it = 0;                                                  // K blocks issued so far, over all tiles
+            int it = 0;                                                  // K blocks issued so far, over all pieces
             bool ok = true;
-            for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step) {
-                const int tile = unit % n_tiles_mn, ks = unit / n_tiles_mn;
-                const int kb_begin = ks * kb_per_split, kb_end = min(n_kb, kb_begin + kb_per_split);
-                const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN + (int)rank * W_ROWS;
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+            Walk walk = walk0;
+            Piece w;
+            while (ok && walk.next(w)) {
+                const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (w.tile / m_tiles) * BN + (int)rank * W_ROWS;
+                // The stream walk takes a tile's K blocks in a turned order (a sum in any order), chosen so that
+                // all CTAs are at the same few places of K at the same time, as CTAs that walk whole tiles are:
+                // what one SM asks the L2 for, others ask for too.  A tile cut between CTAs starts where its
+                // first cut is (the CTA that starts there is at its own first step); a whole tile starts at the
+                // step that its CTA is at.
+                int turn_k = 0;
+                if (stream) {
+                    if (w.kind == PIECE_WHOLE) {
+                        turn_k = it % n_kb;
+                    } else {
+                        long cut = walk0.hi;                             // an owner's tile is cut where its range ends
+                        if (w.kind == PIECE_PART) {
+                            int c = blockIdx.x;
+                            while (c > 0 && stream_begin(total_kb, gridDim.x, c - 1) > w.tile_end - n_kb) --c;
+                            cut = stream_begin(total_kb, gridDim.x, c);
+                        }
+                        turn_k = (int)((w.tile_end - cut) % n_kb);       // n_kb - (cut - the tile's first block)
+                    }
+                }
+                for (int kb0 = w.kb_begin; kb0 < w.kb_end; ++kb0, ++it) {
+                    const int kb = kb0 + turn_k < n_kb ? kb0 + turn_k : kb0 + turn_k - n_kb;
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
                     if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; ok = false; break; }
@@ -160,11 +321,12 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         mbar_expect_tx(full0 + 8 * s, X_BYTES + W_BYTES);
                         // weights are written by no kernel of the step: they may be requested at once
                         tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, kb * BK, f0);
-                        if (!waited) { pdl_wait(); waited = true; }     // activations come from the kernel before
+                        if (!waited) { pdl_wait(); waited = true; WIDE_TRACE(1); }   // activations come from the kernel before
                         tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, kb * BK, m0);
                     }
                 }
             }
+            WIDE_TRACE(2);
             if (*(volatile int*)&s_abort && (!PAIR || rank == 0))
                 for (int i = max(0, it - STAGES); i < it; ++i)
                     mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
@@ -175,14 +337,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             constexpr uint32_t idesc = PAIR ? instr_desc_bf16_pair(BN) : instr_desc_bf16(BN);
             int it = 0, j = 0;
             bool ok = true;
-            for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step, ++j) {
+            Walk walk = walk0;
+            Piece w;
+            for (; ok && walk.next(w); ++j) {
                 const int acc = j & 1;
-                const int ks = unit / n_tiles_mn;
-                const int kb_begin = ks * kb_per_split, kb_end = min(n_kb, kb_begin + kb_per_split);
-                // the epilogue must have read this accumulator's previous tile out
+                // the epilogue must have read this accumulator's previous piece out
                 if (!mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, status, 2)) { s_abort = 1; ok = false; break; }
                 tc_fence_after();
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
                     if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 2)) { s_abort = 1; ok = false; break; }
@@ -193,32 +355,122 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         if (PAIR)
                             tc_mma_bf16_pair(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
                         else
                             tc_mma_bf16(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
                     }
                     if (PAIR) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
                 if (PAIR) tc_commit_pair(acc_full0 + 8 * acc); else tc_commit(acc_full0 + 8 * acc);
             }
+            WIDE_TRACE(3);
         }
     } else {
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        float* turn = turn_base + quarter * 32 * TURN_LD;
+        const int my_row = quarter * 32 + lane;                          // the row of the tile that this thread holds
         pdl_wait();                                                      // the output may still be in use by an earlier kernel
         int j = 0;
         bool ok = true;
-        for (int unit = first_tile; unit < n_tiles_total && ok; unit += tile_step, ++j) {
+        Walk walk = walk0;
+        Piece w;
+        for (; ok && walk.next(w); ++j) {
             const int acc = j & 1;
-            const int tile = unit % n_tiles_mn, ks = unit / n_tiles_mn;
-            const int m0 = (tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (tile / m_tiles) * BN;
-            if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, status, 3)) { s_abort = 1; ok = false; break; }
-            tc_fence_after();
-            const int t = m0 + quarter * 32 + lane;                      // the token row held by this thread
+            const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (w.tile / m_tiles) * BN;
+            const int row0 = m0 + quarter * 32;                          // this warp's 32 token rows
             const uint32_t tacc = tmem_base + lane_bits + acc * BN;
-            if (EPI == EPI_SWIGLU) {
+            // an owner's tile: the parts that the CTAs after this one left, once their flags are up (they are
+            // long before this CTA gets here: a part is the first thing its CTA does)
+            int n_parts = 0;
+            if (w.kind == PIECE_OWNER) {
+                while ((int)blockIdx.x + 1 + n_parts < (int)gridDim.x &&
+                       stream_begin(total_kb, gridDim.x, blockIdx.x + 1 + n_parts) < w.tile_end) ++n_parts;
+                for (int p = 0; p < n_parts; ++p) {
+                    bool up = false;
+                    for (uint32_t i = 0; i < WAIT_LIMIT / 8 && !up; ++i) up = ld_acquire(flags + blockIdx.x + 1 + p) != 0;
+                    if (!up) { if (status) atomicCAS(status, 0, 4); s_parts_missing = 1; }
+                }
+                epilogue_sync();                                         // all four warps take the same way from here
+                if (s_parts_missing) { s_abort = 1; ok = false; n_parts = 0; }
+            }
+            const float* theirs = parts + (size_t)(blockIdx.x + 1) * BM * BN;   // the first of the parts
+            // What the piece's first columns need from memory is asked for before the accumulator is waited
+            // for, and every further 32 columns' while the 32 before them are written: one trip to the L2 per
+            // 32 columns would otherwise stand between the last MMA and the end of the kernel.
+            constexpr bool F32_OUT = EPI != EPI_SWIGLU && sizeof(OutT) == 4;
+            float* outf = reinterpret_cast<float*>(out) + (size_t)w.ks * split_stride;
+            const bool aligned4 = (ldo % 4 == 0) && ((uintptr_t)outf % 16 == 0);
+            const int sub = lane >> 3, col4 = (lane & 7) * 4;            // pass p: row 4 p + sub, four columns from col4
+            float4 old_n[8], part_n[8];
+            auto get_old = [&](int c) {
+                if (EPI == EPI_RESIDUAL && aligned4 && f0 + c + 32 <= F) {
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) {
+                        const int row = row0 + 4 * p + sub;
+                        old_n[p] = row < T ? *reinterpret_cast<const float4*>(outf + (size_t)row * ldo + f0 + c + col4)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            };
+            auto get_part = [&](int c) {
+                if (n_parts > 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        part_n[i] = __ldcg(reinterpret_cast<const float4*>(theirs + part_offset(my_row, c + 4 * i)));
+                }
+            };
+            // r += the parts' columns c .. c + 31: the first part from `first` (asked for earlier), the others now
+            auto add_parts = [&](uint32_t* r, int c, const float4* first) {
+                if (n_parts > 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + first[i].x);
+                        r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + first[i].y);
+                        r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + first[i].z);
+                        r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + first[i].w);
+                    }
+                }
+                for (int p = 1; p < n_parts; ++p) {
+                    const float* more = theirs + (size_t)p * BM * BN;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 a = __ldcg(reinterpret_cast<const float4*>(more + part_offset(my_row, c + 4 * i)));
+                        r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + a.x);
+                        r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + a.y);
+                        r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + a.z);
+                        r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + a.w);
+                    }
+                }
+            };
+            if (w.kind != PIECE_PART && EPI != EPI_SWIGLU) {
+                if (F32_OUT) get_old(0);
+                get_part(0);
+            }
+            if (threadIdx.x == 64) WIDE_TRACE(4 + 3 * j);
+            const bool ready = mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, status, 3);
+            tc_fence_after();
+            if (threadIdx.x == 64) WIDE_TRACE(5 + 3 * j);
+            if (!ready) {
+                s_abort = 1;
+                ok = false;
+            } else if (w.kind == PIECE_PART) {
+                float* mine = parts + (size_t)blockIdx.x * BM * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tc_ld32(tacc + c, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<uint4*>(mine + part_offset(my_row, c + i)) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+                }
+                __threadfence();
+            } else if (EPI == EPI_SWIGLU) {
+                bf16* outb = reinterpret_cast<bf16*>(out);
+                const bool aligned = (ldo % 8 == 0) && ((uintptr_t)outb % 16 == 0);
 #pragma unroll 1
                 for (int gq = 0; gq < BN; gq += 128) {
                     if (f0 + gq >= F) break;
@@ -228,83 +480,85 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         tc_ld32(tacc + gq + cc, gt);
                         tc_ld32(tacc + gq + 64 + cc, up);
                         tc_wait_ld();
-                        if (t < T) {
-                            const int fo = (f0 + gq) / 2 + cc;
+                        for (int p = 0; p < n_parts; ++p) {
+                            const float* more = theirs + (size_t)p * BM * BN;
 #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                gt[i] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[i]), __uint_as_float(up[i])));
-                            OutT* rowp = out + (size_t)t * ldo + fo;
-                            if ((((size_t)t * ldo + fo) * sizeof(OutT)) % 16 == 0) {
-#pragma unroll
-                                for (int i = 0; i < 32; i += 8) store_vec8<OutT>(rowp + i, gt + i);
-                            } else {
-                                for (int i = 0; i < 32; ++i) rowp[i] = from_f32<OutT>(__uint_as_float(gt[i]));
+                            for (int i = 0; i < 32; i += 4) {
+                                const float4 a = __ldcg(reinterpret_cast<const float4*>(more + part_offset(my_row, gq + cc + i)));
+                                const float4 b = __ldcg(reinterpret_cast<const float4*>(more + part_offset(my_row, gq + 64 + cc + i)));
+                                gt[i] = __float_as_uint(__uint_as_float(gt[i]) + a.x); gt[i + 1] = __float_as_uint(__uint_as_float(gt[i + 1]) + a.y);
+                                gt[i + 2] = __float_as_uint(__uint_as_float(gt[i + 2]) + a.z); gt[i + 3] = __float_as_uint(__uint_as_float(gt[i + 3]) + a.w);
+                                up[i] = __float_as_uint(__uint_as_float(up[i]) + b.x); up[i + 1] = __float_as_uint(__uint_as_float(up[i + 1]) + b.y);
+                                up[i + 2] = __float_as_uint(__uint_as_float(up[i + 2]) + b.z); up[i + 3] = __float_as_uint(__uint_as_float(up[i + 3]) + b.w);
                             }
                         }
-                    }
-                }
-            } else if (EPI == EPI_RESIDUAL) {
-                float* turn = turn_base + quarter * 32 * TURN_LD;
-                const int row0 = m0 + quarter * 32;                      // this warp's 32 token rows
-                const int sub = lane >> 3, col = (lane & 7) * 4;         // pass p: row 4 p + sub, four columns from col
-                float* outf = reinterpret_cast<float*>(out);
-                const bool aligned = (ldo % 4 == 0) && ((uintptr_t)outf % 16 == 0);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    if (f0 + c >= F) break;
-                    const bool vec = aligned && (f0 + c + 32 <= F);
-                    float4 old[8];
-                    if (vec) {
 #pragma unroll
-                        for (int p = 0; p < 8; ++p) {
-                            const int row = row0 + 4 * p + sub;
-                            old[p] = row < T ? *reinterpret_cast<const float4*>(outf + (size_t)row * ldo + f0 + c + col)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            gt[i] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[i]), __uint_as_float(up[i])));
+                        turn_put_bf16(turn, lane, cc >> 5, gt);
                     }
-                    uint32_t r[32];
-                    tc_ld32(tacc + c, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<uint4*>(turn + lane * TURN_LD + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
                     __syncwarp();
-#pragma unroll
-                    for (int p = 0; p < 8; ++p) {
-                        const int row = row0 + 4 * p + sub;
-                        const float4 d = *reinterpret_cast<const float4*>(turn + (4 * p + sub) * TURN_LD + col);
-                        if (row >= T) continue;
-                        float* dst = outf + (size_t)row * ldo + f0 + c + col;
-                        if (vec) {
-                            *reinterpret_cast<float4*>(dst) = make_float4(old[p].x + d.x, old[p].y + d.y, old[p].z + d.z, old[p].w + d.w);
-                        } else {
-                            const float dd[4] = {d.x, d.y, d.z, d.w};
-                            for (int i = 0; i < 4; ++i)
-                                if (f0 + c + col + i < F) dst[i] += dd[i];
-                        }
-                    }
+                    turn_write_bf16(turn, lane, outb, ldo, row0, T, (f0 + gq) / 2, F / 2, aligned);
                     __syncwarp();                                        // the piece is read before the next one overwrites it
                 }
             } else {
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    if (f0 + c >= F) break;
-                    uint32_t r[32];
-                    tc_ld32(tacc + c, r);
-                    tc_wait_ld();
-                    if (t < T) {
-                        OutT* rowp = out + (size_t)ks * split_stride + (size_t)t * ldo + f0 + c;
-                        const bool vec = (f0 + c + 32 <= F) && ((((size_t)ks * split_stride + (size_t)t * ldo + f0 + c) * sizeof(OutT)) % 16 == 0);
-                        if (vec) {
+                // 32 columns at a time, two register sets in turn: the next 32 columns are on their way out of
+                // the tensor memory while these are converted, turned and written
+                bf16* outb = reinterpret_cast<bf16*>(out);
+                const bool aligned8 = (ldo % 8 == 0) && ((uintptr_t)outb % 16 == 0);
+                const int c_end = min(BN, (F - f0 + 63) & ~63);
+                auto piece32 = [&](uint32_t* r, int c) {
+                    float4 old[8], part[8];
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) store_vec8<OutT>(rowp + i, r + i);
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                if (f0 + c + i < F) rowp[i] = from_f32<OutT>(__uint_as_float(r[i]));
+                    for (int i = 0; i < 8; ++i) { old[i] = old_n[i]; part[i] = part_n[i]; }
+                    if (c + 32 < c_end) {
+                        if (F32_OUT) get_old(c + 32);
+                        get_part(c + 32);
+                    }
+                    add_parts(r, c, part);
+                    if (F32_OUT) {
+                        if (f0 + c < F) {
+                            turn_put_f32(turn, lane, r);
+                            __syncwarp();
+                            turn_write_f32<EPI == EPI_RESIDUAL>(turn, lane, outf, ldo, row0, T, f0 + c, F,
+                                                                aligned4 && (f0 + c + 32 <= F), old);
+                            __syncwarp();                                // the piece is read before the next one overwrites it
+                        }
+                    } else {
+                        turn_put_bf16(turn, lane, (c >> 5) & 1, r);      // two rounds fill a turned piece of 64 columns
+                        if (c & 32) {
+                            __syncwarp();
+                            turn_write_bf16(turn, lane, outb, ldo, row0, T, f0 + (c & ~63), F, aligned8);
+                            __syncwarp();
                         }
                     }
+                };
+                uint32_t ra[32], rb[32];
+                tc_ld32(tacc, ra);
+#pragma unroll 1
+                for (int c = 0; c < c_end; c += 64) {
+                    tc_wait_ld_into(ra);
+                    if (threadIdx.x == 64 && j == 0 && c == 0) WIDE_TRACE(13);
+                    tc_ld32(tacc + c + 32, rb);
+                    piece32(ra, c);
+                    if (threadIdx.x == 64 && j == 0 && c == 0) WIDE_TRACE(14);
+                    tc_wait_ld_into(rb);
+                    if (c + 64 < c_end) tc_ld32(tacc + c + 64, ra);
+                    piece32(rb, c + 32);
+                    if (threadIdx.x == 64 && j == 0 && c == 0) WIDE_TRACE(15);
                 }
             }
+            if (w.kind == PIECE_PART) {                                  // all of the part is written: the flag goes up
+                epilogue_sync();
+                if (threadIdx.x == 64 && ready) st_release(flags + blockIdx.x, 1);
+            }
+            if (n_parts > 0) {                                           // the flags go down for the next launch
+                epilogue_sync();
+                if (threadIdx.x == 64)
+                    for (int p = 0; p < n_parts; ++p) flags[blockIdx.x + 1 + p] = 0;
+            }
+            if (!ready) break;
+            if (threadIdx.x == 64) WIDE_TRACE(6 + 3 * j);
             tc_fence_before();
             // this accumulator may be overwritten (a pair: says so to rank 0, which issues the MMAs)
             if (PAIR) mbar_arrive_cluster(cluster_map_addr(acc_empty0 + 8 * acc, 0)); else mbar_arrive(acc_empty0 + 8 * acc);
@@ -337,7 +591,7 @@ template <int EPI, typename OutT>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
                 cudaStream_t stream) {
     static bool configured = false;
-    constexpr size_t smem = pair_smem(EPI);
+    constexpr size_t smem = pair_smem();
     auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -348,14 +602,38 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
-                                            out, T, F, K, ldo, m_tiles, n_tiles, status, 1, (K + BK - 1) / BK, (size_t)0));
+                                            out, T, F, K, ldo, m_tiles, n_tiles, status, 1, (K + BK - 1) / BK, (size_t)0,
+                                            (float*)nullptr, (int*)nullptr));
+}
+
+// The parts and flags of the stream walk (see Walk): `slots` slots of BM * 256 floats and as many flags, which
+// are zero between launches.  nullptr: whole tiles only.
+struct StreamSpace { float* parts; int* flags; int slots; };
+
+// How many CTAs walk the K blocks of all tiles as one stream; 0: the tiles are handed out whole (they fill
+// the SMs' rounds well enough, or there is no workspace).
+int stream_ctas(int tiles, int n_kb, const StreamSpace& space) {
+    if (!space.parts || !space.flags) return 0;
+    int ctas = sm_count() < space.slots ? sm_count() : space.slots;
+    const long total = (long)tiles * n_kb;
+    if (total / 8 < ctas) ctas = (int)(total / 8);                       // at least 8 K blocks each
+    if (ctas > 2 * tiles) ctas = 2 * tiles;                              // a tile is cut among three CTAs at most: its owner adds the parts up alone
+    if (ctas < 2) return 0;
+    // In K blocks of time: whole tiles take rounds x K blocks; the stream takes total / ctas and what its parts
+    // cost.  With at least a tile per CTA a part is written long before its owner wants it (4 blocks for the
+    // writing and the reading).  With less, some CTA's only piece is a part that is ready when everything else
+    // is, and its owner's epilogue comes after that part's: measured at about 30 blocks' time.
+    const long rounds = (tiles + sm_count() - 1) / sm_count();
+    const long whole = rounds * n_kb, streamed = (total + ctas - 1) / ctas + (tiles >= ctas ? 4 : 32);
+    return streamed < whole ? ctas : 0;
 }
 
 template <int BN, int EPI, typename OutT>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
-           cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0) {
+           cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0,
+           StreamSpace space = StreamSpace{nullptr, nullptr, 0}, int streamed = 0) {
     static bool configured = false;
-    constexpr size_t smem = wide_smem(BN, EPI);
+    constexpr size_t smem = wide_smem(BN);
     auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -364,10 +642,13 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
     }
     const int m_tiles = (T + BM - 1) / BM, n_tiles = (F + BN - 1) / BN;
     const int units = m_tiles * n_tiles * k_splits;
-    const int ctas = units < sm_count() ? units : sm_count();
+    int ctas = units < sm_count() ? units : sm_count();
     if (kb_per_split <= 0) kb_per_split = (K + BK - 1) / BK;
+    if (k_splits > 1) streamed = 0;
+    if (streamed) ctas = streamed;
     return plm_status_of(launch_pdl(kern, dim3(ctas), dim3(NUM_THREADS), smem, stream, mx, mw, out, T, F, K, ldo, m_tiles,
-                                    n_tiles, status, k_splits, kb_per_split, split_stride));
+                                    n_tiles, status, k_splits, kb_per_split, split_stride,
+                                    streamed ? space.parts : (float*)nullptr, streamed ? space.flags : (int*)nullptr));
 }
 
 // out[i] = sum over the K splits of scratch[s * stride + i], in order; four at a time.
@@ -394,28 +675,44 @@ __global__ void reduce_splits_kernel(const float* __restrict__ scratch, OutT* __
     }
 }
 
-// Tile width and K splits of the single-CTA form for (T, F, K); see plm_gemm_tc_wide.
-void wide_plan(int T, int F, int K, int* bn_out, int* k_splits_out, int* kb_per_out) {
-    int bn = 128;
+// How the single-CTA form runs (T, F, K): the tile width, the parts of K that pass through scratch memory
+// (store epilogue only), and the CTAs of the stream walk (0: whole tiles).
+struct Plan { int bn, k_splits, kb_per, streamed; };
+Plan wide_plan(int T, int F, int K, int epilogue, const StreamSpace& space) {
+    Plan p{128, 1, 0, 0};
     const long m_tiles = (T + BM - 1) / BM, sms = sm_count();
-    if (F >= 2048 && T >= 256) {
-        const long wide = (m_tiles * ((F + 255) / 256) + sms - 1) / sms, narrow = (m_tiles * ((F + 127) / 128) + sms - 1) / sms;
-        bn = 0.8 * (double)narrow < (double)wide ? 128 : 256;
-    }
-    // K splits where the tiles leave at least half of the SMs without work and K is long enough to cut
-    const long tiles = m_tiles * ((F + bn - 1) / bn);
     const int n_kb = (K + BK - 1) / BK;
-    int splits = 1;
-    if (tiles * 2 <= sms && F % 4 == 0) {
-        splits = (int)(sms / tiles);
+    p.kb_per = n_kb;
+    const bool may_be_wide = F >= 2048 && T >= 256;
+    if (may_be_wide) {
+        // 256 columns feed the tensor cores best (a 128-column tile takes 0.8 of a 256-column tile's time for
+        // half the work), but CTAs that walk whole tiles finish earlier with narrow tiles where those need no
+        // more rounds over the SMs than the wide ones (prompts of a few hundred tokens).
+        const long wide = (m_tiles * ((F + 255) / 256) + sms - 1) / sms, narrow = (m_tiles * ((F + 127) / 128) + sms - 1) / sms;
+        p.bn = 0.8 * (double)narrow < (double)wide ? 128 : 256;
+    }
+    const long tiles = m_tiles * ((F + p.bn - 1) / p.bn);
+    // K splits where the tiles leave at least half of the SMs without work and K is long enough to cut
+    if (epilogue == EPI_STORE && tiles * 2 <= sms && F % 4 == 0) {
+        int splits = (int)(sms / tiles);
         if (splits > 8) splits = 8;
         if (splits > n_kb / 4) splits = n_kb / 4;
         if (splits < 1) splits = 1;
+        p.kb_per = (n_kb + splits - 1) / splits;
+        p.k_splits = (n_kb + p.kb_per - 1) / p.kb_per;                     // no part of K is empty
     }
-    const int per = (n_kb + splits - 1) / splits;
-    *bn_out = bn;
-    *kb_per_out = per;
-    *k_splits_out = (n_kb + per - 1) / per;                                // no part of K is empty
+    if (p.k_splits > 1) return p;
+    // The stream walk fills the SMs whatever the number of tiles: with wide tiles where it pays at all.
+    if (may_be_wide && p.bn != 256) {
+        const int streamed = stream_ctas((int)(m_tiles * ((F + 255) / 256)), n_kb, space);
+        if (streamed) { p.bn = 256; p.streamed = streamed; return p; }
+    }
+    p.streamed = stream_ctas((int)tiles, n_kb, space);
+    return p;
+}
+
+bool operands_ok(const void* x, const void* w, int K, long ldx, long ldw) {
+    return K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((((uintptr_t)x | (uintptr_t)w) & 15) == 0);
 }
 
 }  // namespace
@@ -423,37 +720,44 @@ void wide_plan(int T, int F, int K, int* bn_out, int* k_splits_out, int* kb_per_
 // Into how many parts plm_gemm_tc_wide cuts K for (T, F, K) with the store epilogue: it needs that many
 // slices of T * F floats of scratch memory if the answer is more than 1.
 extern "C" int plm_gemm_tc_wide_splits(int T, int F, int K) {
-    int bn, splits, per;
-    wide_plan(T, F, K, &bn, &splits, &per);
-    return splits;
+    return wide_plan(T, F, K, EPI_STORE, StreamSpace{nullptr, nullptr, 0}).k_splits;
 }
+
+// Floats of a slot of the stream walk's workspace (`parts` of plm_gemm_tc_wide_space holds `slots` of them).
+extern "C" int plm_gemm_tc_wide_slot_floats() { return BM * 256; }
 
 // out[T, F'] = epilogue(x[T, K] * w[F, K]^T), T > 64, bf16 operands that TMA can address (K and the
 // leading dimensions multiples of 8, pointers 16-byte aligned).  epilogue 0: F' = F, out float32
 // (out_dtype 0) or bfloat16 (1).  epilogue 1 (SwiGLU): w holds tiles of 64 gate rows followed by their
-// 64 up rows (F a multiple of 128), F' = F / 2, out bfloat16.  `scratch`: plm_gemm_tc_wide_splits(T, F, K) slices
-// of T * F floats where that is more than 1 (else unused; without it K is not cut).
-extern "C" int plm_gemm_tc_wide_scratch(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
-                                        int K, long ldx, long ldw, long ldo, float* scratch, int* status,
-                                        cudaStream_t stream) {
+// 64 up rows (F a multiple of 128), F' = F / 2, out bfloat16.  epilogue 2: out += product, out float32.
+// `scratch`: plm_gemm_tc_wide_splits(T, F, K) slices of T * F floats where that is more than 1 (else unused;
+// without it K is not cut; epilogue 0 only).  `parts`, `flags`, `slots`: the workspace of the stream walk,
+// `slots` * plm_gemm_tc_wide_slot_floats() floats and `slots` ints that are zero before the first launch and
+// that launches of one stream at a time use (they leave them zero); nullptr: tiles are handed out whole.
+extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                      int K, long ldx, long ldw, long ldo, float* scratch, float* parts, int* flags,
+                                      int slots, int* status, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return PLM_OK;
-    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (!operands_ok(x, w, K, ldx, ldw)) return PLM_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
-    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
-    // Tile width: 256 columns feed the tensor cores best (a 128-column tile takes 0.8 of a 256-column tile's
-    // time for half the work), but the CTAs walk whole tiles: where the narrow tiles need no more rounds over
-    // the SMs than the wide ones (prompts of a few hundred tokens), they finish earlier.
-    int bn, k_splits, kb_per;
-    wide_plan(T, F, K, &bn, &k_splits, &kb_per);
+    if (epilogue == EPI_RESIDUAL && out_dtype != PLM_F32) return PLM_ERR_DTYPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_RESIDUAL) return PLM_ERR_UNSUPPORTED;
+    if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    const StreamSpace space{parts, flags, (parts && flags) ? slots : 0};
+    const Plan plan = wide_plan(T, F, K, epilogue, space);
+    const int bn = plan.bn, k_splits = plan.k_splits, kb_per = plan.kb_per, st = plan.streamed;
     CUtensorMap mx, mw;
     int rc;
     if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
     if ((rc = make_map(&mw, w, F, K, ldw, bn)) != PLM_OK) return rc;
     if (epilogue == EPI_SWIGLU) {
-        if (bn == 256) return launch<256, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
-        return launch<128, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+        if (bn == 256) return launch<256, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+        return launch<128, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
     }
-    if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    if (epilogue == EPI_RESIDUAL) {
+        if (bn == 256) return launch<256, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+        return launch<128, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+    }
     if (k_splits > 1 && scratch && ldo == F && (((uintptr_t)scratch | (uintptr_t)out) & 15) == 0) {
         // the parts of K as units of work of their own, each into its slice of the scratch; then the sum
         const size_t stride = (size_t)T * F;
@@ -469,17 +773,18 @@ extern "C" int plm_gemm_tc_wide_scratch(const void* x, const void* w, void* out,
                                         (const float*)scratch, (bf16*)out, k_splits, n4, stride));
     }
     if (out_dtype == PLM_F32) {
-        if (bn == 256) return launch<256, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
-        return launch<128, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
+        if (bn == 256) return launch<256, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+        return launch<128, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
     }
-    if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
-    return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+    if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+    return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
 }
 
-// The same without scratch memory (K is never cut).
+// The same without any workspace: K is never cut and tiles are handed out whole.
 extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
                                 int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
-    return plm_gemm_tc_wide_scratch(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, status, stream);
+    return plm_gemm_tc_wide_space(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, nullptr, nullptr, 0,
+                                  status, stream);
 }
 
 // The same product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 tokens x 256 features; see
@@ -487,36 +792,57 @@ extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out
 extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
                                 int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return PLM_OK;
-    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
+    if (!operands_ok(x, w, K, ldx, ldw)) return PLM_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
-    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
+    if (epilogue == EPI_RESIDUAL && out_dtype != PLM_F32) return PLM_ERR_DTYPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_RESIDUAL) return PLM_ERR_UNSUPPORTED;
     CUtensorMap mx, mw;
     int rc;
     if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
     if ((rc = make_map(&mw, w, F, K, ldw, 128)) != PLM_OK) return rc;
     if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+    if (epilogue == EPI_RESIDUAL) return launch_pair<EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
     if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
     if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     return PLM_ERR_DTYPE;
 }
 
-// resid[T, F] += x[T, K] * w[F, K]^T in place, resid in float32 (the residual stream), T > 64; operands as for
-// plm_gemm_tc_wide.  `pair` != 0: by pairs of CTAs (for at least 256 tokens and 256 features).  K is not cut.
-extern "C" int plm_gemm_tc_wide_residual(const void* x, const void* w, float* resid, int T, int F, int K, long ldx,
-                                         long ldw, long ldr, int pair, int* status, cudaStream_t stream) {
-    if (T <= 0 || F <= 0) return PLM_OK;
-    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return PLM_ERR_ALIGN;
-    if ((uintptr_t)resid % 4) return PLM_ERR_ALIGN;
-    CUtensorMap mx, mw;
-    int rc;
-    if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
-    if (pair) {
-        if ((rc = make_map(&mw, w, F, K, ldw, 128)) != PLM_OK) return rc;
-        return launch_pair<EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
+// For tests of the stream walk on the host: the pieces of CTA `cta` of `ctas` over `tiles` tiles of `n_kb` K
+// blocks, four ints each (tile, first K block, end, kind: 0 whole, 1 part, 2 owner) into `out`, at most
+// `max_pieces`; returns their number.
+extern "C" int plm_gemm_tc_wide_pieces(int tiles, int n_kb, int ctas, int cta, int* out, int max_pieces) {
+    Walk walk;
+    walk.stream = true;
+    walk.n_kb = n_kb;
+    walk.n_tiles_mn = tiles;
+    walk.kb_per_split = n_kb;
+    walk.unit = walk.unit_end = walk.unit_step = 0;
+    walk.pos = stream_begin((long)tiles * n_kb, ctas, cta);
+    walk.hi = stream_begin((long)tiles * n_kb, ctas, cta + 1);
+    Piece w;
+    int n = 0;
+    while (walk.next(w)) {
+        if (n < max_pieces) { out[4 * n] = w.tile; out[4 * n + 1] = w.kb_begin; out[4 * n + 2] = w.kb_end; out[4 * n + 3] = w.kind; }
+        ++n;
     }
-    int bn, k_splits, kb_per;
-    wide_plan(T, F, K, &bn, &k_splits, &kb_per);
-    if ((rc = make_map(&mw, w, F, K, ldw, bn)) != PLM_OK) return rc;
-    if (bn == 256) return launch<256, EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
-    return launch<128, EPI_RESIDUAL, float>(mx, mw, resid, T, F, K, ldr, status, stream);
+    return n;
 }
+
+// How the single-CTA form runs (T, F, K) with `slots` slots of stream workspace (0: none): out[0] the tile
+// width, out[1] the parts of K with scratch memory, out[2] the CTAs of the stream walk (0: whole tiles).
+extern "C" int plm_gemm_tc_wide_how(int T, int F, int K, int epilogue, int slots, int* out) {
+    float dummy_parts;
+    int dummy_flags;
+    const StreamSpace space{slots > 0 ? &dummy_parts : nullptr, slots > 0 ? &dummy_flags : nullptr, slots};
+    const Plan p = wide_plan(T, F, K, epilogue, space);
+    out[0] = p.bn;
+    out[1] = p.k_splits;
+    out[2] = p.k_splits == 1 ? p.streamed : 0;
+    return PLM_OK;
+}
+
+#ifdef PLM_WIDE_TRACE
+extern "C" int plm_gemm_tc_wide_trace_read(unsigned long long* host) {
+    return plm_status_of(cudaMemcpyFromSymbol(host, plm_wide_trace, sizeof(unsigned long long) * 16 * PLM_SM_COUNT));
+}
+#endif

@@ -95,6 +95,14 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
 // silu(g) * u for the fused bf16 epilogues: g and u are rounded to bf16 first (as a separate
 // activation kernel would read them), then g / (1 + 2^(-g log2 e)) * u with the special-function
 // unit's 2^x and reciprocal, whose error is far below the bf16 rounding of the result.
+// Wait for the tensor-memory loads in flight, of which `r` (32 registers) is a destination: the registers count as
+// written here, so that nothing the compiler makes of them moves above the wait.
+__device__ __forceinline__ void tc_wait_ld_into(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]));
+}
+
 __device__ __forceinline__ float swiglu_bf16(float g, float u) {
     g = __bfloat162float(__float2bfloat16_rn(g));
     u = __bfloat162float(__float2bfloat16_rn(u));

@@ -27,7 +27,10 @@ _SIGNATURES = {
     "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _i, _f, _vp, _vp],
     "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
-    "plm_gemm_tc_wide_scratch": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp],
+    "plm_gemm_tc_wide_space": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp, _i, _vp, _vp],
+    "plm_gemm_tc_wide_slot_floats": [],
+    "plm_gemm_tc_wide_pieces": [_i, _i, _i, _i, _vp, _i],
+    "plm_gemm_tc_wide_how": [_i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_wide_splits": [_i, _i, _i],
     "plm_gemm_tc_pair": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
@@ -244,6 +247,32 @@ def status_word(device) -> torch.Tensor:
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=key)
         _status[key] = t
+    return t
+
+
+_stream_space = {}
+STREAM_WALK = os.environ.get("PICOLM_B200_STREAM_WALK", "1") != "0"   # 0: the prompt-shaped product hands out whole tiles only
+
+
+def stream_space_enabled() -> bool:
+    return STREAM_WALK
+
+
+def stream_space(device):
+    """(parts, flags, slots): the workspace with which the prompt-shaped product hands the K blocks of all
+    tiles out as one stream, a slot and a flag per CTA.  One per device, for launches of one stream at a
+    time; the kernels leave the flags zero."""
+    if not STREAM_WALK:
+        return None, None, 0
+    key = torch.device(device)
+    t = _stream_space.get(key)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the product's workspace must exist before a graph is captured: run the step once first")
+        slot = _fn("gemm_tc_wide", "plm_gemm_tc_wide_slot_floats")()
+        t = (torch.empty(SM_COUNT * slot, dtype=torch.float32, device=key),
+             torch.zeros(SM_COUNT, dtype=torch.int32, device=key), SM_COUNT)
+        _stream_space[key] = t
     return t
 
 

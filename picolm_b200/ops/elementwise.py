@@ -34,7 +34,11 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     if weight.shape != (d,):
         raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
     if hasattr(delta, "compute"):                          # a product that has not run yet (gemm.PendingLinear)
-        delta = delta.compute()
+        if rows is None and delta.adds_in_place(x):        # many rows: the add in the product's epilogue
+            delta.add_into(x)
+            delta = None
+        else:
+            delta = delta.compute()
     if delta is not None:
         _dev(delta, "delta")
         if delta.dtype != torch.float32 or delta.shape != x.shape:

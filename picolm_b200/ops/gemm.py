@@ -7,7 +7,8 @@ from typing import Optional
 import torch
 
 from . import chain as _chain
-from ._lib import SM_COUNT, KernelError, _check, _dev, _dt, _fn, _p, _stream, status_word
+from ._lib import (SM_COUNT, KernelError, _check, _dev, _dt, _fn, _p, _stream, status_word, stream_space,
+                   stream_space_enabled)
 from .chain import LazyRows
 
 
@@ -106,6 +107,23 @@ class PendingLinear:
             return out
         return linear(self.a, self.w, torch.float32)
 
+    def adds_in_place(self, x: torch.Tensor) -> bool:
+        """Whether `add_into(x)` runs as one kernel: a product of more than 64 rows for the tensor cores
+        with enough tiles for the SMs, and an fp32 stream of its shape."""
+        if (isinstance(self.a, LazyRows) or self.a.shape[0] <= 64 or x.dtype != torch.float32
+                or not x.is_contiguous() or tuple(x.shape) != tuple(self.shape) or x.data_ptr() % 16):
+            return False
+        # where the tiles are few the plain product cuts K into parts, which this epilogue cannot
+        return _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(self.a.shape[0], self.w.shape[0], self.a.shape[1]) == 1
+
+    def add_into(self, x: torch.Tensor) -> None:
+        """x += a @ w^T in place, the add in the product's epilogue: the delta never goes through memory."""
+        if not self.adds_in_place(x):
+            x.add_(self.compute())
+            return
+        gemm_tc_wide(self.a, self.w, torch.float32, out=x, add=True,
+                     pair=pair_pays(self.a.shape[0], self.w.shape[0], self.a.shape[1], 2))
+
 
 class ScaledRows:
     """An RMSNorm whose scale is still due: `x` [T, size] in bfloat16 holds row * norm weight, and
@@ -184,12 +202,14 @@ def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: t
 
 
 def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
-                 out: Optional[torch.Tensor] = None, pair: bool = False) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, pair: bool = False, add: bool = False) -> torch.Tensor:
     """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
     (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
-    tile's main loop).  With `swiglu`, w comes from `interleave_gate_up` and the result is
-    silu(gate) * up, [M, N/2] in bfloat16.  `pair`: the same by pairs of CTAs on tiles of 256 x 256
-    (`tcgen05.mma.cta_group::2`: each CTA of a pair loads half of the weight tile)."""
+    tile's main loop; where whole tiles would leave SMs idle in the last round, the K blocks of all tiles
+    are handed out as one stream, cut into equal ranges).  With `swiglu`, w comes from `interleave_gate_up`
+    and the result is silu(gate) * up, [M, N/2] in bfloat16.  With `add`, `out` (float32) += the product.
+    `pair`: the same by pairs of CTAs on tiles of 256 x 256 (`tcgen05.mma.cta_group::2`: each CTA of a pair
+    loads half of the weight tile)."""
     _dev(a, "a"), _dev(w, "w")
     M, K = a.shape
     N = w.shape[0]
@@ -200,22 +220,32 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
             raise KernelError("gemm_tc_wide: the interleaved gate/up matrix must have a multiple of 128 rows")
         out_dtype = torch.bfloat16
     n_out = N // 2 if swiglu else N
+    if add:
+        if swiglu or out is None or out.dtype != torch.float32 or tuple(out.shape) != (M, N) or not out.is_contiguous():
+            raise KernelError("gemm_tc_wide: `add` needs a contiguous float32 `out` of the product's shape")
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
-    if not pair and not swiglu:
+    epilogue = 2 if add else 1 if swiglu else 0
+    name = f"{'_swiglu' if swiglu else '_residual' if add else ''} {M}x{N}x{K}"
+    work = _work(a, w, out, extra=out.numel() * 4 if add else 0)
+    if pair:
+        _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair")(
+            _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out,
+            _p(status_word(a.device)), _stream()), "gemm_tc_pair" + name, **work)
+        return out
+    scratch, kernels = None, 1
+    if epilogue == 0:
         # few tiles (a prompt of a few hundred tokens): K is cut into parts that pass through scratch memory
         k_splits = _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(M, N, K)
         if k_splits > 1:
             scratch = torch.empty((k_splits, M, N), dtype=torch.float32, device=a.device)
-            _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_scratch")(
-                _p(a), _p(w), _p(out), _dt(out, "out"), 0, M, N, K, K, K, n_out, _p(scratch),
-                _p(status_word(a.device)), _stream()), f"gemm_tc_wide(K in {k_splits} parts) {M}x{N}x{K}", kernels=2,
-                **_work(a, w, out, extra=2 * scratch.numel() * 4))
-            return out
-    _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair" if pair else "plm_gemm_tc_wide")(
-        _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
-        _p(status_word(a.device)), _stream()),
-        f"{'gemm_tc_pair' if pair else 'gemm_tc_wide'}{'_swiglu' if swiglu else ''} {M}x{N}x{K}", **_work(a, w, out))
+            name = f"(K in {k_splits} parts)" + name
+            work = _work(a, w, out, extra=2 * scratch.numel() * 4)
+            kernels = 2
+    parts, flags, slots = stream_space(a.device)
+    _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_space")(
+        _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(scratch), _p(parts), _p(flags), slots,
+        _p(status_word(a.device)), _stream()), "gemm_tc_wide" + name, kernels=kernels, **work)
     return out
 
 
@@ -229,11 +259,34 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(F // 64, 64, K), up.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous()
 
 
-def pair_pays(m: int, n: int) -> bool:
-    """Whether the prompt-shaped product runs as pairs of CTAs on tiles of 256 x 256: measured 3..5 % faster
-    than single CTAs on tiles of 128 x 256 where there are at least two rounds of tiles for the 74 pairs,
-    and no faster or slower (a ragged last round of larger tiles) below that."""
-    return m >= 256 and n >= 256 and ((m + 255) // 256) * ((n + 255) // 256) >= SM_COUNT
+_how_cache = {}
+
+
+def wide_how(m: int, n: int, k: int, epilogue: int = 0):
+    """(tile width, parts of K through scratch memory, CTAs of the stream walk or 0) of the single-CTA form of the
+    prompt-shaped product for this shape; epilogue 0 store, 1 SwiGLU, 2 add."""
+    key = (m, n, k, epilogue)
+    how = _how_cache.get(key)
+    if how is None:
+        import ctypes
+        out = (ctypes.c_int * 3)()
+        slots = SM_COUNT if stream_space_enabled() else 0
+        _fn("gemm_tc_wide", "plm_gemm_tc_wide_how")(m, n, k, epilogue, slots, ctypes.cast(out, ctypes.c_void_p))
+        how = _how_cache[key] = tuple(out)
+    return how
+
+
+def pair_pays(m: int, n: int, k: int = 0, epilogue: int = 0) -> bool:
+    """Whether the prompt-shaped product runs as pairs of CTAs on tiles of 256 x 256.  Measured: 3..5 % faster
+    than single CTAs on tiles of 128 x 256 where the pairs have at least one tile each, a little faster or
+    the same down to half as many tiles, and slower than single CTAs that walk the K blocks as one stream
+    where the tiles are few (with `k` given, that case is left to them)."""
+    if m < 256 or n < 256:
+        return False
+    tiles = ((m + 255) // 256) * ((n + 255) // 256)
+    if k and wide_how(m, n, k, epilogue)[2] > 0 and tiles < SM_COUNT // 2:
+        return False
+    return tiles >= SM_COUNT // 4
 
 
 def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):
@@ -259,7 +312,7 @@ def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):
         raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
     if M <= 64:
         return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
-    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N))
+    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N, K, 1))
 
 
 def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):
@@ -283,10 +336,10 @@ def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):
         if defer and out_dtype == torch.float32 and gemm_tc_supported(a, w):
             return PendingLinear(a, w)
         a = a.materialize()
-    if defer and out_dtype == torch.float32 and a.shape[0] <= 64 and gemm_tc_supported(a, w):
+    if defer and out_dtype == torch.float32 and gemm_tc_supported(a, w):
         return PendingLinear(a, w)
     if gemm_tc_supported(a, w):
         if a.shape[0] <= 64:
             return gemm_tc_skinny(a, w, out_dtype)
-        return gemm_tc_wide(a, w, out_dtype, pair=pair_pays(a.shape[0], w.shape[0]))
+        return gemm_tc_wide(a, w, out_dtype, pair=pair_pays(a.shape[0], w.shape[0], a.shape[1], 0))
     return gemm_simt(a, w, out_dtype)

@@ -357,6 +357,36 @@ def test_gemm_tc_wide_with_k_in_parts(out_dtype, M, N, K):
     assert torch.equal(got, ops.linear(a.to(DEV), w.to(DEV), DT[out_dtype]))
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 512), (2304, 2562, 264), (1100, 2100, 328), (4100, 2400, 72),
+                                   (3000, 3340, 136), (2900, 3333, 64), (20000, 130, 64)])
+def test_product_added_to_the_stream_in_its_epilogue(M, N, K):
+    """x += a @ w^T with the add in the product's epilogue (single CTAs and pairs, as the shape decides):
+    against float64, ragged tiles in both directions, widths that are no multiple of 4 or 32 (the
+    element-wise tail), and every element outside the product's rows untouched."""
+    from picolm_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    x0 = torch.randn(M + 1, N) * 3
+    x = x0.to(DEV)
+    pending = ops.PendingLinear(a.to(DEV), w.to(DEV))
+    assert pending.adds_in_place(x[:M])
+    pending.add_into(x[:M])
+    ops.check_status(DEV)
+    ref = x0[:M].double() + a.double() @ w.double().t()
+    assert torch.allclose(x[:M].double().cpu(), ref, atol=2e-3, rtol=1e-4)
+    assert torch.equal(x[M].cpu(), x0[M])
+    # the norm takes the same road: the sum lands in the stream, the rows are normalised
+    x2 = x0[:M].to(DEV).contiguous()
+    wn = (1 + 0.1 * torch.randn(N)).to(torch.bfloat16)
+    h = ops.rmsnorm(x2, wn.to(DEV), 1e-5, torch.bfloat16, delta=ops.PendingLinear(a.to(DEV), w.to(DEV)))
+    assert torch.equal(x2, x[:M])
+    want = ref.float() * torch.rsqrt(ref.float().pow(2).mean(-1, keepdim=True) + 1e-5) * wn.float()
+    assert torch.allclose(h.float().cpu(), want, atol=3e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("window", [None, 90])
 @pytest.mark.parametrize("scratch", [False, True])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (40, 2, 16), (6, 3, 128), (4, 4, 48)])
@@ -662,6 +692,55 @@ def test_attention_prefill_tcgen05_with_one_slow_warp():
         out = ops.attention_prefill_tc(*args)
         ops.check_status(DEV)
         assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("epilogue", ["float32", "bfloat16", "swiglu", "add"])
+@pytest.mark.parametrize("M,N,K", [(2048, 3072, 520), (130, 512, 8192), (2300, 3000, 1032), (1024, 2304, 6144),
+                                   (128, 256, 8192)])
+def test_gemm_tc_wide_stream_walk(epilogue, M, N, K):
+    """The K blocks of all tiles handed out as one stream: tiles cut between two CTAs and among many (few
+    tiles with a long K), with every epilogue, against float64; three launches in a row (the flags go down
+    again) with the same bits; ragged edges."""
+    import ctypes
+    from picolm_b200 import ops
+    from picolm_b200.ops._lib import _fn
+    how = (ctypes.c_int * 3)()
+    code = {"float32": 0, "bfloat16": 0, "swiglu": 1, "add": 2}[epilogue]
+    if epilogue == "swiglu":
+        N = N // 128 * 128
+    _fn("gemm_tc_wide", "plm_gemm_tc_wide_how")(M, N, K, code, 148, ctypes.cast(how, ctypes.c_void_p))
+    if how[1] > 1:
+        pytest.skip("this shape cuts K through scratch memory with the store epilogue")
+    assert how[2] > 0, "the shape was chosen to take the stream walk"
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    a[M // 2, :] *= -2.0
+    y = a.double() @ w.double().t()
+    ad, wd = a.to(DEV), w.to(DEV)
+    outs = []
+    for _ in range(3):
+        if epilogue == "swiglu":
+            wi = ops.interleave_gate_up(wd[: N // 2].contiguous(), wd[N // 2:].contiguous())
+            got = ops.gemm_tc_wide(ad, wi, torch.bfloat16, swiglu=True)
+            g, u = y[:, : N // 2].bfloat16().double(), y[:, N // 2:].bfloat16().double()
+            ref, tol_ = g / (1 + torch.exp(-g)) * u, dict(atol=3e-2, rtol=2e-2)
+        elif epilogue == "add":
+            x0 = torch.randn(M, N) * 3
+            got = ops.gemm_tc_wide(ad, wd, torch.float32, out=x0.to(DEV), add=True)
+            ref, tol_ = x0.double() + y, dict(atol=2e-3, rtol=1e-4)
+        else:
+            got = ops.gemm_tc_wide(ad, wd, DT[epilogue])
+            ref, tol_ = y, dict(atol=2e-3, rtol=1e-4) if epilogue == "float32" else dict(atol=3e-2, rtol=2e-2)
+        ops.check_status(DEV)
+        assert torch.allclose(got.double().cpu(), ref, **tol_)
+        outs.append(got)
+    if epilogue != "add":
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    from picolm_b200.ops._lib import stream_space
+    assert int(stream_space(DEV)[1].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
