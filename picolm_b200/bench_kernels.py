@@ -6,6 +6,7 @@ against the bytes it has to move or the flops it has to do.
     python -m picolm_b200.bench_kernels attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
     python -m picolm_b200.bench_kernels sample --batch 8 --vocab 128256 --temperature 0.8 --top-k 40 --top-p 0.9
     python -m picolm_b200.bench_kernels gemm --m 8 --n 2048 --k 8192 --residual      (the product with the norm's half)
+    python -m picolm_b200.bench_kernels gemm --m 2048 --n 2048 --k 8192 --residual   (the product added to the stream)
 
 Operands rotate through copies that together exceed the L2 cache, so every
 timed launch reads its weights or its cache from HBM.  `--iters` launches are
@@ -74,6 +75,8 @@ def bench_gemm(args):
             if args.swiglu:                                  # rows in this kernel's order: tiles of 64 gate, 64 up rows
                 y = y.view(M, N // 128, 2, 64)
                 torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]
+        elif args.residual and M > 64:                      # the add to the stream in the prompt-shaped product's epilogue
+            ops.PendingLinear(a, ws[i]).add_into(x)
         elif args.residual:
             ops.linear_residual_norm(ops.PendingLinear(a, ws[i]), x, nw, 1e-5)
         elif args.pair:
@@ -85,11 +88,47 @@ def bench_gemm(args):
 
     sec = _time(run, len(ws), 1 if args.once else args.iters, 0 if args.once else args.warmup)
     ops.check_status()
+    if args.stations:
+        _print_stations()
     bytes_moved = w_bytes + M * K * 2 + M * N * (4 if out_dtype == torch.float32 else 2)
     flops = 2.0 * M * N * K
     return {"kernel": "torch.matmul (library)" if args.library else "linear (tensor cores)", "m": M, "n": N, "k": K,
             "us": round(sec * 1e6, 2),
             "GB/s": round(bytes_moved / sec / 1e9, 1), "TFLOP/s": round(flops / sec / 1e12, 2), "weight_copies": len(ws)}
+
+
+def _print_stations():
+    """The last launch of the prompt-shaped product's trace build (`-DPLM_WIDE_TRACE`): when its CTAs passed
+    their stations (microseconds after the first CTA's entry) and, for CTAs with one piece of work, how many
+    cycles the loading thread waited for a free stage and the MMA thread for loads to land."""
+    import ctypes
+
+    import numpy as np
+
+    from .csrc.build import load_library
+    from .ops import _lib
+    name, flags = _lib.VARIANT_OF["gemm_tc_wide"]
+    lib = load_library(name, flags)
+    buf = (ctypes.c_ulonglong * (16 * _lib.SM_COUNT))()
+    lib.plm_gemm_tc_wide_trace_read.argtypes = [ctypes.c_void_p]
+    if lib.plm_gemm_tc_wide_trace_read(buf):
+        raise RuntimeError("the trace could not be read")
+    t = np.frombuffer(buf, dtype=np.uint64).reshape(_lib.SM_COUNT, 16).astype(np.int64)
+    used = t[:, 0] > 0
+    t0 = t[used, 0].min()
+    for i, what in ((0, "entry"), (1, "activations may be read"), (2, "all loads issued"), (3, "all MMAs issued"),
+                    (5, "first piece: accumulator ready"), (13, "first piece: 32 columns in registers"),
+                    (14, "first piece: 32 columns written"), (6, "first piece: written")):
+        ok = used & (t[:, i] >= t0)
+        if ok.any():
+            c = (t[ok, i] - t0) / 1e3
+            print(f"{what:40s} CTAs {int(ok.sum()):3d}  min {c.min():7.2f}  median {np.median(c):7.2f}  max {c.max():7.2f} us",
+                  file=sys.stderr)
+    ok = used & (t[:, 10] > 0)
+    if ok.any():
+        print(f"loading thread: {np.median(t[ok, 7]):.0f} of {np.median(t[ok, 8]):.0f} cycles waiting for a free stage; "
+              f"MMA thread: {np.median(t[ok, 9]):.0f} of {np.median(t[ok, 10]):.0f} cycles waiting for loads "
+              f"(medians over {int(ok.sum())} CTAs)", file=sys.stderr)
 
 
 def _paged_cache(batch, ctx, G, hd, n_copies):
@@ -187,7 +226,8 @@ def main(argv=None):
     ap.add_argument("--swiglu", action="store_true", help="gemm: the product with the SwiGLU epilogue (n counts gate and up rows)")
     ap.add_argument("--pair", action="store_true", help="gemm (m > 64): the kernel of CTA pairs (tcgen05.mma.cta_group::2)")
     ap.add_argument("--residual", action="store_true",
-                    help="gemm (m <= 64): the product in front of an RMSNorm (adds to the stream, norm weight, sums of squares)")
+                    help="gemm: the product in front of an RMSNorm; m <= 64: adds to the stream, norm weight, sums of squares; "
+                         "m > 64: adds to the stream")
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--temperature", type=float, default=0.8, help="sample: 0 times the argmax kernel")
     ap.add_argument("--top-k", type=int, default=40)
@@ -203,7 +243,13 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--once", action="store_true", help="one launch, no warm-up (for a profiler)")
     ap.add_argument("--graph", action="store_true", help="time the launches as one CUDA graph (for short kernels)")
+    ap.add_argument("--stations", action="store_true",
+                    help="gemm (m > 64): run the trace build of the prompt-shaped product and print when its CTAs passed "
+                         "their stations in the last launch (stderr)")
     args = ap.parse_args(argv)
+    if args.stations:
+        from .ops import _lib
+        _lib.VARIANT_OF["gemm_tc_wide"] = ("gemm_tc_wide@trace", ("-DPLM_WIDE_TRACE",))
     global USE_GRAPH
     USE_GRAPH = args.graph and not args.once
     fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,

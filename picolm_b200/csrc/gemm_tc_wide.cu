@@ -102,10 +102,14 @@ __device__ unsigned long long plm_wide_trace[PLM_SM_COUNT][16];
     do {                                                                                               \
         unsigned long long t_;                                                                         \
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                         \
-        if (!PAIR && blockIdx.x < PLM_SM_COUNT && (point) < 16) plm_wide_trace[blockIdx.x][point] = t_; \
+        if (blockIdx.x < PLM_SM_COUNT && (point) < 16) plm_wide_trace[blockIdx.x][point] = t_; \
     } while (0)
+#define WIDE_TRACE_VALUE(point, v) do { if (blockIdx.x < PLM_SM_COUNT) plm_wide_trace[blockIdx.x][point] = (v); } while (0)
+#define WIDE_TRACE_CLOCK(var) long long var = clock64()
 #else
 #define WIDE_TRACE(point) do { } while (0)
+#define WIDE_TRACE_VALUE(point, v) do { } while (0)
+#define WIDE_TRACE_CLOCK(var) do { } while (0)
 #endif
 struct Piece { int tile, ks, kb_begin, kb_end, kind; long tile_end; };
 struct Walk {
@@ -280,6 +284,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool waited = false;
+#ifdef PLM_WIDE_TRACE
+            long long waited_empty = 0, p_begin = clock64();
+#endif
             int it = 0;                                                  // K blocks issued so far, over all pieces
             bool ok = true;
             Walk walk = walk0;
@@ -309,7 +316,11 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     const int kb = kb0 + turn_k < n_kb ? kb0 + turn_k : kb0 + turn_k - n_kb;
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
+                    WIDE_TRACE_CLOCK(e0);
                     if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; ok = false; break; }
+#ifdef PLM_WIDE_TRACE
+                    waited_empty += clock64() - e0;                      // cycles this thread waited for a free stage
+#endif
                     if (PAIR) {
                         // both CTAs' tiles count at the "full" barrier of rank 0, which expects them all
                         const uint32_t full = cluster_map_addr(full0 + 8 * s, 0);
@@ -327,6 +338,10 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
             WIDE_TRACE(2);
+#ifdef PLM_WIDE_TRACE
+            WIDE_TRACE_VALUE(7, (unsigned long long)waited_empty);       // of a CTA with one piece: points 7..10 are cycle counts
+            WIDE_TRACE_VALUE(8, (unsigned long long)(clock64() - p_begin));
+#endif
             if (*(volatile int*)&s_abort && (!PAIR || rank == 0))
                 for (int i = max(0, it - STAGES); i < it; ++i)
                     mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
@@ -339,6 +354,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             bool ok = true;
             Walk walk = walk0;
             Piece w;
+#ifdef PLM_WIDE_TRACE
+            long long waited_full = 0, m_begin = clock64();
+#endif
             for (; ok && walk.next(w); ++j) {
                 const int acc = j & 1;
                 // the epilogue must have read this accumulator's previous piece out
@@ -347,7 +365,11 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (*(volatile int*)&s_abort) { ok = false; break; }
+                    WIDE_TRACE_CLOCK(f0_);
                     if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 2)) { s_abort = 1; ok = false; break; }
+#ifdef PLM_WIDE_TRACE
+                    waited_full += clock64() - f0_;                      // cycles this thread waited for loads to land
+#endif
                     tc_fence_after();
                     const uint64_t xd = smem_desc_sw128(x_smem + s * X_BYTES);
                     const uint64_t wd = smem_desc_sw128(w_smem + s * W_BYTES);
@@ -365,6 +387,10 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (PAIR) tc_commit_pair(acc_full0 + 8 * acc); else tc_commit(acc_full0 + 8 * acc);
             }
             WIDE_TRACE(3);
+#ifdef PLM_WIDE_TRACE
+            WIDE_TRACE_VALUE(9, (unsigned long long)waited_full);
+            WIDE_TRACE_VALUE(10, (unsigned long long)(clock64() - m_begin));
+#endif
         }
     } else {
         // ---------------------------------------------------------------- epilogue

@@ -64,7 +64,15 @@ _CODES = {-1: "unsupported element type", -2: "bad shape", -3: "bad alignment", 
           -5: "the device wait ran out (see the status word)"}
 
 
+# library -> (variant name, compile flags): a measuring build that stands in for a library in this process
+# (`bench_kernels --stations` puts the prompt-shaped product's trace build here)
+VARIANT_OF = {}
+
+
 def _fn(library: str, name: str, extra_flags=()):
+    if library in VARIANT_OF:
+        library, more = VARIANT_OF[library]
+        extra_flags = tuple(extra_flags) + tuple(more)
     if CHECKED and library.split("@")[0] in CHECKED_LIBRARIES:
         library = library + ("_check" if "@" in library else "@check")
         extra_flags = tuple(extra_flags) + ("-DPLM_CHECK",)
