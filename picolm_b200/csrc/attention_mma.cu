@@ -669,23 +669,73 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
 }
 
 // out[row, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp2(m_s - max m): one block per (token, head).
-__global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
-                                  bf16* __restrict__ out, int n_splits) {
+// 256 threads: the ranges' maxima and weights are found by all threads side by side; then MERGE_GROUPS groups of
+// MERGE_LANES threads (one per component) each add up a stretch of the ranges, with the loads of eight ranges in
+// flight, and the stretches' sums are added in their order: always the same order for a number of ranges.
+constexpr int MERGE_THREADS = 256;
+constexpr int MERGE_MAX_SPLITS = 8192;                   // the weights of all ranges lie in shared memory
+constexpr int MERGE_LANES = HD <= 64 ? 64 : HD <= 128 ? 128 : 256;
+constexpr int MERGE_GROUPS = MERGE_THREADS / MERGE_LANES;
+__global__ void __launch_bounds__(MERGE_THREADS)
+attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int n_splits) {
+    extern __shared__ float merge_w[];                  // [n_splits] weights, then [MERGE_GROUPS][MERGE_LANES] sums
+    __shared__ float red[MERGE_THREADS / 32];
+    __shared__ float s_max, s_l;
     pdl_launch_dependents();
     pdl_wait();
     const size_t row = blockIdx.x;
-    float mm = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, ws_ml[(row * n_splits + s) * 2]);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f, ll = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = ws_ml[(row * n_splits + s) * 2];
-            if (ms == -INFINITY) continue;
-            const float wgt = exp2f(ms - mm);
-            acc += wgt * ws_o[(row * n_splits + s) * HD + d];
-            ll += wgt * ws_ml[(row * n_splits + s) * 2 + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* ml = ws_ml + row * n_splits * 2;
+    float m = -INFINITY;
+    for (int s = tid; s < n_splits; s += MERGE_THREADS) m = fmaxf(m, ml[2 * s]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float mm = red[0];
+        for (int w = 1; w < MERGE_THREADS / 32; ++w) mm = fmaxf(mm, red[w]);
+        s_max = mm;
+    }
+    __syncthreads();
+    const float mm = s_max;
+    for (int s = tid; s < n_splits; s += MERGE_THREADS) {
+        const float ms = ml[2 * s];
+        merge_w[s] = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    }
+    __syncthreads();
+    if (warp == 0) {                                    // the sum of the weighted row sums, ranges in order
+        float ll = 0.f;
+        if (lane == 0)
+            for (int s = 0; s < n_splits; ++s)
+                if (merge_w[s] != 0.f) ll += merge_w[s] * ml[2 * s + 1];
+        if (lane == 0) s_l = ll;
+    }
+    float* sums = merge_w + n_splits;
+    const int g = tid / MERGE_LANES, d = tid % MERGE_LANES;
+    const int per = (n_splits + MERGE_GROUPS - 1) / MERGE_GROUPS;
+    const int s_begin = g * per, s_end = min(n_splits, s_begin + per);
+    float acc = 0.f;
+    if (d < HD) {
+        const float* o = ws_o + row * n_splits * HD + d;
+        int s = s_begin;
+        for (; s + 8 <= s_end; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = o[(size_t)(s + i) * HD];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (merge_w[s + i] != 0.f) acc += merge_w[s + i] * v[i];   // an empty range left nothing to read
         }
-        out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        for (; s < s_end; ++s)
+            if (merge_w[s] != 0.f) acc += merge_w[s] * o[(size_t)s * HD];
+    }
+    sums[g * MERGE_LANES + d] = acc;
+    __syncthreads();
+    if (g == 0 && d < HD) {
+        float total = sums[d];
+        for (int k = 1; k < MERGE_GROUPS; ++k) total += sums[k * MERGE_LANES + d];
+        const float ll = s_l;
+        out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? total / ll : 0.f);
     }
 }
 
@@ -769,6 +819,7 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
     const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
     const size_t smem = TMA ? dc_smem_tma(q_rows) : dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
+    if (n_splits > MERGE_MAX_SPLITS) return PLM_ERR_SHAPE;
     if (n_splits > 1 && !workspace) {                       // the splits merge inside their cluster
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
         return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
@@ -782,7 +833,8 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
                                       block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status));
     if (rc != PLM_OK || n_splits == 1) return rc;
-    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
+    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(MERGE_THREADS),
+                                    (size_t)(n_splits + MERGE_THREADS) * sizeof(float), stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
 }
 
@@ -815,6 +867,7 @@ extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* o
     const int q_rows = decode_q_rows(R, (long)n_splits * G * row_groups * n_tokens);
     const size_t smem = TMA ? dc_smem_tma(q_rows) : dc_smem(q_rows);
     dim3 grid(n_splits, G * row_groups, n_tokens);
+    if (n_splits > MERGE_MAX_SPLITS) return PLM_ERR_SHAPE;
     if (n_splits > 1 && !workspace) {
         if (n_splits > DC_MAX_CLUSTER) return PLM_ERR_SHAPE;
         return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
@@ -828,6 +881,7 @@ extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* o
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
                                       block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status));
     if (rc != PLM_OK || n_splits == 1) return rc;
-    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(HD < 64 ? 32 : 64), 0, stream,
+    return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(MERGE_THREADS),
+                                    (size_t)(n_splits + MERGE_THREADS) * sizeof(float), stream,
                                     (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
 }

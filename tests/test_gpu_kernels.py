@@ -565,7 +565,7 @@ def test_attention_prefill_mma(H, G, hd, window):
 
 
 @pytest.mark.parametrize("window", [None, 90])
-@pytest.mark.parametrize("n_splits,scratch", [(1, False), (2, False), (3, False), (3, True), (8, False), (16, True)])
+@pytest.mark.parametrize("n_splits,scratch", [(1, False), (2, False), (3, False), (3, True), (8, False), (16, True), (37, True)])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (6, 2, 48), (5, 5, 16), (40, 1, 128), (3, 1, 32), (4, 2, 256)])
 def test_attention_decode_mma(H, G, hd, n_splits, scratch, window):
     """Decode on the tensor cores with the keys cut into ranges: sequences of very unequal lengths (some
@@ -588,6 +588,29 @@ def test_attention_decode_mma(H, G, hd, n_splits, scratch, window):
         row = out.float().cpu()[0].reshape(H, hd)
         for h in range(H):
             assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
+
+
+@pytest.mark.parametrize("H,G,hd,n_splits", [(8, 2, 64, 47), (4, 1, 128, 33), (6, 3, 48, 94), (2, 2, 256, 19)])
+def test_attention_decode_many_ranges_of_a_long_sequence(H, G, hd, n_splits):
+    """One long sequence cut into many ranges that a second kernel merges (the shape of a single request far
+    into its context): groups of threads add up stretches of the ranges, so counts that leave stretches of
+    unequal length and tails shorter than the unrolled eight; a far key must be found; the same bits twice."""
+    from picolm_b200 import ops
+    lens = [6000, 70]
+    new = [1, 1]
+    ks, vs, qs = _attn_case(H, G, hd, lens, new, H + hd + n_splits)
+    scale = 1.0 / math.sqrt(hd)
+    ref = _attn_ref(ks, vs, qs, lens, new, H, hd, scale, None)
+    kc, vc, table = _paged(ks, vs, lens, 100, torch.bfloat16, 5)
+    args = (torch.cat(qs).to(torch.bfloat16).to(DEV), kc.to(DEV), vc.to(DEV),
+            torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV),
+            torch.arange(len(lens), dtype=torch.int32, device=DEV), table.to(DEV), G, scale, n_splits)
+    out = ops.attention_decode(*args, scratch=True)
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    row = out.float().cpu()[0].reshape(H, hd)
+    for h in range(H):
+        assert torch.allclose(row[h], vs[0][lens[0] // 7][h // (H // G)], atol=5e-2)
+    assert torch.equal(out, ops.attention_decode(*args, scratch=True))
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
