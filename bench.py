@@ -216,6 +216,8 @@ def main():
     ap.add_argument("--unequal", action="store_true",
                     help="also time one step of eight prompts of 128 to 2,048 tokens (always done for a configuration "
                          "that names an unequal batch)")
+    ap.add_argument("--long-context", type=int, default=32768,
+                    help="with the other points: one request's decode rate after a prompt of this many tokens (0: skip)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
     args = ap.parse_args()
@@ -364,6 +366,39 @@ def main():
         pr = decode_run(pb, args.steps, args.warmup)
         points[f"decode_b{pb}"] = round(pb / pr["ms"] * 1e3, 1)
         points_frac[f"decode_b{pb}"] = round(pr["achieved"] / pk["hbm_gbs"], 4)
+
+    # One request far into its context: the decode rate after a long prompt (an engine of its own, one sequence).
+    n_long = args.long_context
+    if n_long and not args.skip_points and n_long + 512 <= cfg.max_position_embeddings:
+        with tempfile.TemporaryDirectory() as tmp:
+            write_random_model(cfg, seed, tmp, norm_std=0.0)
+            room = n_long + 512
+            long_engine = Engine.from_folder(tmp, dtype="bfloat16", max_tokens=room, max_seqs=1, max_seq_tokens=room,
+                                             use_graphs=False if args.no_graphs else None)
+        slot = long_engine.new_sequence()
+        tok = ops.argmax(long_engine.step([(slot, prompts(1, n_long)[0])])).tolist()
+        for _ in range(args.warmup):
+            tok = ops.argmax(long_engine.step([(slot, tok)])).tolist()
+        tok_dev = torch.tensor(tok, dtype=torch.int32, device="cuda:0")
+        pinned = torch.empty((256, 1), dtype=torch.int32).pin_memory()
+        tok_dev = greedy_steps_in_flight(long_engine, [slot], tok_dev, 64, pinned)      # the classes' graphs, the clocks
+        per_block = []
+        for r in range(4):
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            tok_dev = greedy_steps_in_flight(long_engine, [slot], tok_dev, 32, pinned)
+            b.record()
+            torch.cuda.synchronize()
+            per_block.append(a.elapsed_time(b) / 32)
+        lms = statistics.median(per_block)
+        ctx_mean = n_long + args.warmup + 64 + 64
+        long_engine.end_sequence(slot)
+        points[f"decode_b1_ctx{n_long}"] = round(1e3 / lms, 1)
+        points_frac[f"decode_b1_ctx{n_long}"] = round(
+            (w_bytes + long_engine.cache.kv_bytes_per_token() * ctx_mean) / (lms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        del long_engine
+        torch.cuda.empty_cache()
 
     # The unequal batch that the 8B configuration names: prompts of 128 to 2,048 tokens in one step.
     if "Unequal batch" in baseline_text(args.config) or args.unequal:
