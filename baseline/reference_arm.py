@@ -26,7 +26,8 @@ from typing import Dict, Optional, Tuple
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref", "picolm")
-SOURCE = os.environ.get("PICOLM_REFERENCE_SOURCE", "/root/reference/picolm")
+# where the reference's checkout is looked for: beside this repository, unless the variable says otherwise
+SOURCE = os.environ.get("PICOLM_REFERENCE_SOURCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference", "picolm")
 
 GGUF_F32, GGUF_BF16 = 0, 30
 META_U32, META_F32, META_BOOL, META_STR, META_ARRAY = 4, 6, 7, 8, 9
