@@ -56,10 +56,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+// rows from `row`, all 64 columns, slabs of K from `slab` (a map of make_map with slabs > 1)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row, int slab) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(0), "r"(row), "r"(slab) : "memory");
 }
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {           // arrives at `bar` in both CTAs of the pair
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -77,9 +78,10 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_des
 __host__ __device__ constexpr uint32_t instr_desc_bf16_pair(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
-__host__ __device__ constexpr int pair_stages() { return 6; }
+constexpr int PAIR_SLABS = 2;                                // tiles of 64 columns of K per stage and copy
+__host__ __device__ constexpr int pair_stages() { return 3; }
 __host__ __device__ constexpr size_t pair_smem() {
-    return (size_t)pair_stages() * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + TURN_BYTES;
+    return (size_t)pair_stages() * PAIR_SLABS * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + TURN_BYTES;
 }
 
 // ---------------------------------------------------------------- the work of a CTA
@@ -224,7 +226,10 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
     constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
-    constexpr uint32_t X_BYTES = BM * BK * 2, W_BYTES = W_ROWS * BK * 2;
+    // Pairs take two tiles of 64 columns of K per stage, each operand's in one copy (see make_map): with one tile
+    // per copy the copies took longer than the MMAs (0.31 us per stage of 32 KB against 0.27 us).
+    constexpr int SLABS = PAIR ? PAIR_SLABS : 1;
+    constexpr uint32_t X_BYTES = BM * BK * 2 * SLABS, W_BYTES = W_ROWS * BK * 2 * SLABS;
     constexpr uint32_t TMEM_COLS = 2 * BN;                               // two accumulators
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -239,7 +244,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_kb = (K + BK - 1) / BK;
+    const int n_kb = (K + BK * SLABS - 1) / (BK * SLABS);                // stages of K
     const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
     constexpr int TILE_M = PAIR ? 2 * BM : BM;
     const bool stream = !PAIR && parts != nullptr;
@@ -325,9 +330,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         // both CTAs' tiles count at the "full" barrier of rank 0, which expects them all
                         const uint32_t full = cluster_map_addr(full0 + 8 * s, 0);
                         if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * (X_BYTES + W_BYTES));
-                        tma_load_2d_pair(w_smem + s * W_BYTES, &map_w, full, kb * BK, f0);
+                        tma_load_3d_pair(w_smem + s * W_BYTES, &map_w, full, f0, kb * SLABS);
                         if (!waited) { pdl_wait(); waited = true; }
-                        tma_load_2d_pair(x_smem + s * X_BYTES, &map_x, full, kb * BK, m0);
+                        tma_load_3d_pair(x_smem + s * X_BYTES, &map_x, full, m0, kb * SLABS);
                     } else {
                         mbar_expect_tx(full0 + 8 * s, X_BYTES + W_BYTES);
                         // weights are written by no kernel of the step: they may be requested at once
@@ -373,15 +378,18 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     tc_fence_after();
                     const uint64_t xd = smem_desc_sw128(x_smem + s * X_BYTES);
                     const uint64_t wd = smem_desc_sw128(w_smem + s * W_BYTES);
+#ifndef PLM_WIDE_LOADS_ONLY                                              // a measuring build: what the copies alone take
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                    for (int k = 0; k < SLABS * (BK / UMMA_K); ++k) {
+                        // a stage holds SLABS tiles of 64 columns of K one behind the other
+                        const uint64_t x_off = (uint64_t)(((k / (BK / UMMA_K)) * (BM * BK * 2) + (k % (BK / UMMA_K)) * UMMA_K * 2) / 16);
+                        const uint64_t w_off = (uint64_t)(((k / (BK / UMMA_K)) * (W_ROWS * BK * 2) + (k % (BK / UMMA_K)) * UMMA_K * 2) / 16);
                         if (PAIR)
-                            tc_mma_bf16_pair(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                             wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
+                            tc_mma_bf16_pair(tmem_base + acc * BN, xd + x_off, wd + w_off, idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
                         else
-                            tc_mma_bf16(tmem_base + acc * BN, xd + (uint64_t)(k * UMMA_K * 2 / 16),
-                                        wd + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
+                            tc_mma_bf16(tmem_base + acc * BN, xd + x_off, wd + w_off, idesc, (kb > w.kb_begin || k > 0) ? 1u : 0u);
                     }
+#endif
                     if (PAIR) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
                 if (PAIR) tc_commit_pair(acc_full0 + 8 * acc); else tc_commit(acc_full0 + 8 * acc);
@@ -628,7 +636,8 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
-                                            out, T, F, K, ldo, m_tiles, n_tiles, status, 1, (K + BK - 1) / BK, (size_t)0,
+                                            out, T, F, K, ldo, m_tiles, n_tiles, status, 1,
+                                            (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), (size_t)0,
                                             (float*)nullptr, (int*)nullptr));
 }
 
@@ -822,10 +831,12 @@ extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out
     if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
     if (epilogue == EPI_RESIDUAL && out_dtype != PLM_F32) return PLM_ERR_DTYPE;
     if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_RESIDUAL) return PLM_ERR_UNSUPPORTED;
+    if (K % BK)          // the pairs' copies take whole tiles of 64 columns of K: other widths go to the single CTAs
+        return plm_gemm_tc_wide(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, status, stream);
     CUtensorMap mx, mw;
     int rc;
-    if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
-    if ((rc = make_map(&mw, w, F, K, ldw, 128)) != PLM_OK) return rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, BM, PAIR_SLABS)) != PLM_OK) return rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, 128, PAIR_SLABS)) != PLM_OK) return rc;
     if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
     if (epilogue == EPI_RESIDUAL) return launch_pair<EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
     if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);

@@ -144,34 +144,51 @@ static inline EncodeTiledFn encode_fn() {
 }
 
 // A [rows, K] bf16 row-major matrix with leading dimension ld (elements); boxes of box_rows x 64.
+// With `slabs` > 1 (K a multiple of 64) the matrix is described as [K / 64 slabs][rows][64] and a box holds
+// `slabs` consecutive slabs of box_rows x 64: one copy brings in what `slabs` copies of the plain form do, and
+// lands as that many tiles one behind the other.  (A tensor copy occupies an SM's copy engine for some 300
+// cycles whatever its size, so a kernel bound by its copies wants few and large ones.)
 // Descriptors are kept in a small table by what they describe (a descriptor depends on nothing else, and
 // encoding one costs a few microseconds of host time per operand and launch).
-static inline int make_map(CUtensorMap* map, const void* ptr, long rows, long K, long ld, int box_rows) {
-    struct Entry { const void* ptr; long rows, K, ld; int box_rows; bool used; CUtensorMap map; };
+static inline int make_map(CUtensorMap* map, const void* ptr, long rows, long K, long ld, int box_rows, int slabs = 1) {
+    struct Entry { const void* ptr; long rows, K, ld; int box_rows, slabs; bool used; CUtensorMap map; };
     constexpr int SLOTS = 512;
     static Entry table[SLOTS];
     static std::mutex lock;
-    const size_t h = ((size_t)ptr >> 4) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)K * 131 + (size_t)box_rows;
+    if (slabs < 1 || (slabs > 1 && K % BK)) return PLM_ERR_SHAPE;
+    const size_t h = ((size_t)ptr >> 4) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)K * 131 + (size_t)box_rows +
+                     (size_t)slabs * 7919;
     Entry& e = table[(h >> 20) % SLOTS];
     {
         std::lock_guard<std::mutex> g(lock);
-        if (e.used && e.ptr == ptr && e.rows == rows && e.K == K && e.ld == ld && e.box_rows == box_rows) {
+        if (e.used && e.ptr == ptr && e.rows == rows && e.K == K && e.ld == ld && e.box_rows == box_rows && e.slabs == slabs) {
             *map = e.map;
             return PLM_OK;
         }
     }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return PLM_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (slabs == 1) {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+        cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+        cuuint32_t estr[2] = {1, 1};
+        r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(K / BK)};
+        cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)BK * 2};
+        cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, (cuuint32_t)slabs};
+        cuuint32_t estr[3] = {1, 1, 1};
+        r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return PLM_ERR_ALIGN;
     std::lock_guard<std::mutex> g(lock);
-    e.ptr = ptr; e.rows = rows; e.K = K; e.ld = ld; e.box_rows = box_rows; e.map = *map; e.used = true;
+    e.ptr = ptr; e.rows = rows; e.K = K; e.ld = ld; e.box_rows = box_rows; e.slabs = slabs; e.map = *map; e.used = true;
     return PLM_OK;
 }
 
