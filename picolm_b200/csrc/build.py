@@ -52,6 +52,10 @@ VARIANTS: Dict[str, Dict[str, List[str]]] = {
 }
 
 
+# Variants of libraries that also exist plain: (name, flags).  The build check builds them too.
+MORE_BUILDS: List = [("gemm_tc_wide@stream", ["-DPLM_WIDE_STREAM"])]
+
+
 def attention_variant(head_dim: int, family: str = "attention_mma"):
     """(library name, extra flags) of a tensor-core attention library for a head size."""
     return f"{family}@hd{head_dim}", [f"-DPLM_HD={head_dim}"]
@@ -207,11 +211,13 @@ def build_all(names: Optional[Iterable[str]] = None, jobs: int = 4, verbose: boo
         names = [n for n in LIBRARIES if n not in VARIANTS]
         for base, variants in VARIANTS.items():
             names += [f"{base}@{v}" for v in variants]
+        names += [n for n, _ in MORE_BUILDS]
     names = list(names)
+    more = dict(MORE_BUILDS)
 
     def one(n):
         base, _, variant = n.partition("@")
-        flags = VARIANTS[base][variant] if variant else ()
+        flags = more[n] if n in more else VARIANTS[base][variant] if variant else ()
         return compile_library(n, flags, verbose=verbose)
 
     with ThreadPoolExecutor(max_workers=jobs) as pool:

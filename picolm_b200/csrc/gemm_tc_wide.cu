@@ -95,6 +95,13 @@ __host__ __device__ constexpr size_t pair_smem() {
 //           their order, and writes the tile.  A part is the FIRST piece of its CTA and an owner's tile its
 //           LAST, and a part waits for nothing: no cycle of waits.
 constexpr int PIECE_WHOLE = 0, PIECE_PART = 1, PIECE_OWNER = 2;
+// The stream walk's code is in a build of its own (-DPLM_WIDE_STREAM, the library variant "gemm_tc_wide@stream"):
+// with it in, the epilogue of every kernel here was 2 .. 3 us slower (registers), and most shapes never walk.
+#ifdef PLM_WIDE_STREAM
+constexpr bool STREAM_BUILD = true;
+#else
+constexpr bool STREAM_BUILD = false;
+#endif
 
 // A build with -DPLM_WIDE_TRACE records when (globaltimer, ns) each CTA of the single-CTA form passed the points
 // marked WIDE_TRACE below; plm_gemm_tc_wide_trace_read copies the table out.
@@ -247,18 +254,20 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int n_kb = (K + BK * SLABS - 1) / (BK * SLABS);                // stages of K
     const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
     constexpr int TILE_M = PAIR ? 2 * BM : BM;
-    const bool stream = !PAIR && parts != nullptr;
+    constexpr int GROUP = PAIR ? 2 : 1;                                  // CTAs that work on a piece together
+    const int group_no = blockIdx.x / GROUP, n_groups = gridDim.x / GROUP;
+    const bool stream = STREAM_BUILD && parts != nullptr;
     Walk walk0;
     walk0.stream = stream;
     walk0.n_kb = n_kb;
     walk0.n_tiles_mn = m_tiles * n_tiles;                                // PAIR: tiles of 256 tokens
     walk0.kb_per_split = kb_per_split;
-    walk0.unit = PAIR ? blockIdx.x / 2 : blockIdx.x;
-    walk0.unit_step = PAIR ? gridDim.x / 2 : gridDim.x;
+    walk0.unit = group_no;
+    walk0.unit_step = n_groups;
     walk0.unit_end = walk0.n_tiles_mn * k_splits;
     const long total_kb = (long)walk0.n_tiles_mn * n_kb;
-    walk0.pos = stream ? stream_begin(total_kb, gridDim.x, blockIdx.x) : 0;
-    walk0.hi = stream ? stream_begin(total_kb, gridDim.x, blockIdx.x + 1) : 0;
+    walk0.pos = stream ? stream_begin(total_kb, n_groups, group_no) : 0;
+    walk0.hi = stream ? stream_begin(total_kb, n_groups, group_no + 1) : 0;
 
     if (threadIdx.x == 0) {
         WIDE_TRACE(0);
@@ -310,9 +319,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     } else {
                         long cut = walk0.hi;                             // an owner's tile is cut where its range ends
                         if (w.kind == PIECE_PART) {
-                            int c = blockIdx.x;
-                            while (c > 0 && stream_begin(total_kb, gridDim.x, c - 1) > w.tile_end - n_kb) --c;
-                            cut = stream_begin(total_kb, gridDim.x, c);
+                            int c = group_no;
+                            while (c > 0 && stream_begin(total_kb, n_groups, c - 1) > w.tile_end - n_kb) --c;
+                            cut = stream_begin(total_kb, n_groups, c);
                         }
                         turn_k = (int)((w.tile_end - cut) % n_kb);       // n_kb - (cut - the tile's first block)
                     }
@@ -419,18 +428,19 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // an owner's tile: the parts that the CTAs after this one left, once their flags are up (they are
             // long before this CTA gets here: a part is the first thing its CTA does)
             int n_parts = 0;
-            if (w.kind == PIECE_OWNER) {
-                while ((int)blockIdx.x + 1 + n_parts < (int)gridDim.x &&
-                       stream_begin(total_kb, gridDim.x, blockIdx.x + 1 + n_parts) < w.tile_end) ++n_parts;
+            if (STREAM_BUILD && w.kind == PIECE_OWNER) {
+                while (group_no + 1 + n_parts < n_groups &&
+                       stream_begin(total_kb, n_groups, group_no + 1 + n_parts) < w.tile_end) ++n_parts;
                 for (int p = 0; p < n_parts; ++p) {
                     bool up = false;
-                    for (uint32_t i = 0; i < WAIT_LIMIT / 8 && !up; ++i) up = ld_acquire(flags + blockIdx.x + 1 + p) != 0;
+                    for (uint32_t i = 0; i < WAIT_LIMIT / 8 && !up; ++i) up = ld_acquire(flags + blockIdx.x + GROUP * (1 + p)) != 0;
                     if (!up) { if (status) atomicCAS(status, 0, 4); s_parts_missing = 1; }
                 }
                 epilogue_sync();                                         // all four warps take the same way from here
                 if (s_parts_missing) { s_abort = 1; ok = false; n_parts = 0; }
             }
-            const float* theirs = parts + (size_t)(blockIdx.x + 1) * BM * BN;   // the first of the parts
+            // the first of the parts: the slot of the CTA of this rank in the next group (a pair: each CTA its 128 rows)
+            const float* theirs = parts + (size_t)(blockIdx.x + GROUP) * BM * BN;
             // What the piece's first columns need from memory is asked for before the accumulator is waited
             // for, and every further 32 columns' while the 32 before them are written: one trip to the L2 per
             // 32 columns would otherwise stand between the last MMA and the end of the kernel.
@@ -450,7 +460,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             };
             auto get_part = [&](int c) {
-                if (n_parts > 0) {
+                if (STREAM_BUILD && n_parts > 0) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         part_n[i] = __ldcg(reinterpret_cast<const float4*>(theirs + part_offset(my_row, c + 4 * i)));
@@ -458,6 +468,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             };
             // r += the parts' columns c .. c + 31: the first part from `first` (asked for earlier), the others now
             auto add_parts = [&](uint32_t* r, int c, const float4* first) {
+                if (!STREAM_BUILD) return;
                 if (n_parts > 0) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -468,7 +479,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
                 for (int p = 1; p < n_parts; ++p) {
-                    const float* more = theirs + (size_t)p * BM * BN;
+                    const float* more = theirs + (size_t)p * GROUP * BM * BN;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float4 a = __ldcg(reinterpret_cast<const float4*>(more + part_offset(my_row, c + 4 * i)));
@@ -490,7 +501,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (!ready) {
                 s_abort = 1;
                 ok = false;
-            } else if (w.kind == PIECE_PART) {
+            } else if (STREAM_BUILD && w.kind == PIECE_PART) {
                 float* mine = parts + (size_t)blockIdx.x * BM * BN;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
@@ -514,8 +525,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         tc_ld32(tacc + gq + cc, gt);
                         tc_ld32(tacc + gq + 64 + cc, up);
                         tc_wait_ld();
-                        for (int p = 0; p < n_parts; ++p) {
-                            const float* more = theirs + (size_t)p * BM * BN;
+                        for (int p = 0; STREAM_BUILD && p < n_parts; ++p) {
+                            const float* more = theirs + (size_t)p * GROUP * BM * BN;
 #pragma unroll
                             for (int i = 0; i < 32; i += 4) {
                                 const float4 a = __ldcg(reinterpret_cast<const float4*>(more + part_offset(my_row, gq + cc + i)));
@@ -582,14 +593,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     if (threadIdx.x == 64 && j == 0 && c == 0) WIDE_TRACE(15);
                 }
             }
-            if (w.kind == PIECE_PART) {                                  // all of the part is written: the flag goes up
+            if (STREAM_BUILD && w.kind == PIECE_PART) {                  // all of the part is written: the flag goes up
                 epilogue_sync();
                 if (threadIdx.x == 64 && ready) st_release(flags + blockIdx.x, 1);
             }
-            if (n_parts > 0) {                                           // the flags go down for the next launch
+            if (STREAM_BUILD && n_parts > 0) {                           // the flags go down for the next launch
                 epilogue_sync();
                 if (threadIdx.x == 64)
-                    for (int p = 0; p < n_parts; ++p) flags[blockIdx.x + 1 + p] = 0;
+                    for (int p = 0; p < n_parts; ++p) flags[blockIdx.x + GROUP * (1 + p)] = 0;
             }
             if (!ready) break;
             if (threadIdx.x == 64) WIDE_TRACE(6 + 3 * j);
@@ -623,7 +634,7 @@ int sm_count() {
 
 template <int EPI, typename OutT>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, float* parts = nullptr, int* flags = nullptr, int streamed_pairs = 0) {
     static bool configured = false;
     constexpr size_t smem = pair_smem();
     auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
@@ -635,10 +646,11 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     const int m_tiles = (T + 2 * BM - 1) / (2 * BM), n_tiles = (F + 255) / 256;
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
+    if (streamed_pairs) pairs = streamed_pairs;
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
                                             out, T, F, K, ldo, m_tiles, n_tiles, status, 1,
                                             (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), (size_t)0,
-                                            (float*)nullptr, (int*)nullptr));
+                                            streamed_pairs ? parts : (float*)nullptr, streamed_pairs ? flags : (int*)nullptr));
 }
 
 // The parts and flags of the stream walk (see Walk): `slots` slots of BM * 256 floats and as many flags, which
@@ -647,19 +659,25 @@ struct StreamSpace { float* parts; int* flags; int slots; };
 
 // How many CTAs walk the K blocks of all tiles as one stream; 0: the tiles are handed out whole (they fill
 // the SMs' rounds well enough, or there is no workspace).
-int stream_ctas(int tiles, int n_kb, const StreamSpace& space) {
+// `group`: 1 for single CTAs, 2 for pairs (the answer then counts pairs, and `n_kb` their stages of two tiles of K).
+int stream_ctas(int tiles, int n_kb, const StreamSpace& space, int group = 1) {
     if (!space.parts || !space.flags) return 0;
-    int ctas = sm_count() < space.slots ? sm_count() : space.slots;
+    const int sms = sm_count() / group;
+    int ctas = sms < space.slots / group ? sms : space.slots / group;
     const long total = (long)tiles * n_kb;
-    if (total / 8 < ctas) ctas = (int)(total / 8);                       // at least 8 K blocks each
+    const int least = 8 / group;                                         // at least 8 tiles of K each
+    if (total / least < ctas) ctas = (int)(total / least);
     if (ctas > 2 * tiles) ctas = 2 * tiles;                              // a tile is cut among three CTAs at most: its owner adds the parts up alone
     if (ctas < 2) return 0;
-    // In K blocks of time: whole tiles take rounds x K blocks; the stream takes total / ctas and what its parts
-    // cost.  With at least a tile per CTA a part is written long before its owner wants it (4 blocks for the
-    // writing and the reading).  With less, some CTA's only piece is a part that is ready when everything else
-    // is, and its owner's epilogue comes after that part's: measured at about 30 blocks' time.
-    const long rounds = (tiles + sm_count() - 1) / sm_count();
-    const long whole = rounds * n_kb, streamed = (total + ctas - 1) / ctas + (tiles >= ctas ? 4 : 32);
+    // Only where the tiles do not fill one round over the SMs.  With more tiles the stream was measured slower than
+    // whole tiles although it leaves no SM idle (4,096 x 2,048 x 8,192 by pairs: 110 against 105 us; 1,024 x 16,384 x
+    // 2,048 with SwiGLU: 59 against 50 us): under the power cap the SMs that still work in a ragged last round run
+    // at a higher clock, and the parts cost what they cost.
+    if (tiles >= sms) return 0;
+    // In K blocks of time: a round of whole tiles takes a tile's K blocks; the stream takes total / ctas and what
+    // its parts cost: some CTA's only piece is a part that is ready when everything else is, and its owner's
+    // epilogue comes after that part's: measured at about 30 blocks' time.
+    const long whole = n_kb, streamed = (total + ctas - 1) / ctas + 32 / group;
     return streamed < whole ? ctas : 0;
 }
 
@@ -778,6 +796,7 @@ extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, i
     if (epilogue == EPI_RESIDUAL && out_dtype != PLM_F32) return PLM_ERR_DTYPE;
     if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_RESIDUAL) return PLM_ERR_UNSUPPORTED;
     if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    if (!STREAM_BUILD) parts = nullptr;                                  // this build walks whole tiles only
     const StreamSpace space{parts, flags, (parts && flags) ? slots : 0};
     const Plan plan = wide_plan(T, F, K, epilogue, space);
     const int bn = plan.bn, k_splits = plan.k_splits, kb_per = plan.kb_per, st = plan.streamed;
@@ -822,26 +841,47 @@ extern "C" int plm_gemm_tc_wide(const void* x, const void* w, void* out, int out
                                   status, stream);
 }
 
+// How many pairs walk the stages of all 256 x 256 tiles as one stream for (T, F, K) with `slots` slots of workspace;
+// 0: the pairs take whole tiles.
+extern "C" int plm_gemm_tc_pair_streamed(int T, int F, int K, int slots) {
+    float dummy_parts;
+    int dummy_flags;
+    if (slots <= 0 || K % BK) return 0;
+    const StreamSpace space{&dummy_parts, &dummy_flags, slots};
+    const int tiles = ((T + 2 * BM - 1) / (2 * BM)) * ((F + 255) / 256);
+    return stream_ctas(tiles, (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), space, 2);
+}
+
 // The same product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 tokens x 256 features; see
-// PAIR at the top).  For prompts of at least 256 tokens and at least 256 features.
-extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
-                                int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+// PAIR at the top).  For prompts of at least 256 tokens and at least 256 features.  `parts`, `flags`, `slots` as for
+// plm_gemm_tc_wide_space: where the tiles are few, the pairs walk them as one stream.
+extern "C" int plm_gemm_tc_pair_space(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                      int K, long ldx, long ldw, long ldo, float* parts, int* flags, int slots, int* status,
+                                      cudaStream_t stream) {
     if (T <= 0 || F <= 0) return PLM_OK;
     if (!operands_ok(x, w, K, ldx, ldw)) return PLM_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
     if (epilogue == EPI_RESIDUAL && out_dtype != PLM_F32) return PLM_ERR_DTYPE;
     if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_RESIDUAL) return PLM_ERR_UNSUPPORTED;
     if (K % BK)          // the pairs' copies take whole tiles of 64 columns of K: other widths go to the single CTAs
-        return plm_gemm_tc_wide(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, status, stream);
+        return plm_gemm_tc_wide_space(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, parts, flags, slots,
+                                      status, stream);
+    const int st = (STREAM_BUILD && parts && flags) ? plm_gemm_tc_pair_streamed(T, F, K, slots) : 0;
     CUtensorMap mx, mw;
     int rc;
     if ((rc = make_map(&mx, x, T, K, ldx, BM, PAIR_SLABS)) != PLM_OK) return rc;
     if ((rc = make_map(&mw, w, F, K, ldw, 128, PAIR_SLABS)) != PLM_OK) return rc;
-    if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
-    if (epilogue == EPI_RESIDUAL) return launch_pair<EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
-    if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
-    if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+    if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (epilogue == EPI_RESIDUAL) return launch_pair<EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
     return PLM_ERR_DTYPE;
+}
+
+// The same without a workspace: the pairs take whole tiles.
+extern "C" int plm_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                int K, long ldx, long ldw, long ldo, int* status, cudaStream_t stream) {
+    return plm_gemm_tc_pair_space(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, nullptr, 0, status, stream);
 }
 
 // For tests of the stream walk on the host: the pieces of CTA `cta` of `ctas` over `tiles` tiles of `n_kb` K

@@ -28,6 +28,8 @@ _SIGNATURES = {
     "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_wide_space": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp, _i, _vp, _vp],
+    "plm_gemm_tc_pair_space": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _i, _vp, _vp],
+    "plm_gemm_tc_pair_streamed": [_i, _i, _i, _i],
     "plm_gemm_tc_wide_slot_floats": [],
     "plm_gemm_tc_wide_pieces": [_i, _i, _i, _i, _vp, _i],
     "plm_gemm_tc_wide_how": [_i, _i, _i, _i, _i, _vp],

@@ -113,7 +113,7 @@ class PendingLinear:
         if (isinstance(self.a, LazyRows) or self.a.shape[0] <= 64 or x.dtype != torch.float32
                 or not x.is_contiguous() or tuple(x.shape) != tuple(self.shape) or x.data_ptr() % 16):
             return False
-        # where the tiles are few the plain product cuts K into parts, which this epilogue cannot
+        # where the tiles are few the plain product cuts K into parts through scratch memory, which this epilogue cannot
         return _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(self.a.shape[0], self.w.shape[0], self.a.shape[1]) == 1
 
     def add_into(self, x: torch.Tensor) -> None:
@@ -228,24 +228,32 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
     epilogue = 2 if add else 1 if swiglu else 0
     name = f"{'_swiglu' if swiglu else '_residual' if add else ''} {M}x{N}x{K}"
     work = _work(a, w, out, extra=out.numel() * 4 if add else 0)
+    # Shapes whose tiles leave most SMs idle walk K as one stream: that code is in a build variant of the library
+    # (compiled when the first such shape comes), with a workspace; everything else runs the plain build.
+    STREAM_LIB = ("gemm_tc_wide@stream", ("-DPLM_WIDE_STREAM",))
     if pair:
-        _check(_fn("gemm_tc_wide", "plm_gemm_tc_pair")(
-            _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out,
-            _p(status_word(a.device)), _stream()), "gemm_tc_pair" + name, **work)
+        streamed = K % 64 == 0 and stream_space_enabled() and _pair_streamed(M, N, K) > 0
+        parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
+        lib = STREAM_LIB if streamed else ("gemm_tc_wide", ())
+        _check(_fn(lib[0], "plm_gemm_tc_pair_space", lib[1])(
+            _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(parts), _p(flags), slots,
+            _p(status_word(a.device)), _stream()), "gemm_tc_pair" + (" (stream)" if streamed else "") + name, **work)
         return out
     scratch, kernels = None, 1
-    if epilogue == 0:
+    how = wide_how(M, N, K, epilogue)
+    if epilogue == 0 and how[1] > 1:
         # few tiles (a prompt of a few hundred tokens): K is cut into parts that pass through scratch memory
-        k_splits = _fn("gemm_tc_wide", "plm_gemm_tc_wide_splits")(M, N, K)
-        if k_splits > 1:
-            scratch = torch.empty((k_splits, M, N), dtype=torch.float32, device=a.device)
-            name = f"(K in {k_splits} parts)" + name
-            work = _work(a, w, out, extra=2 * scratch.numel() * 4)
-            kernels = 2
-    parts, flags, slots = stream_space(a.device)
-    _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_space")(
+        k_splits = how[1]
+        scratch = torch.empty((k_splits, M, N), dtype=torch.float32, device=a.device)
+        name = f"(K in {k_splits} parts)" + name
+        work = _work(a, w, out, extra=2 * scratch.numel() * 4)
+        kernels = 2
+    streamed = how[2] > 0
+    parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
+    lib = STREAM_LIB if streamed else ("gemm_tc_wide", ())
+    _check(_fn(lib[0], "plm_gemm_tc_wide_space", lib[1])(
         _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(scratch), _p(parts), _p(flags), slots,
-        _p(status_word(a.device)), _stream()), "gemm_tc_wide" + name, kernels=kernels, **work)
+        _p(status_word(a.device)), _stream()), "gemm_tc_wide" + (" (stream)" if streamed else "") + name, kernels=kernels, **work)
     return out
 
 
@@ -260,6 +268,16 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 _how_cache = {}
+_pair_streamed_cache = {}
+
+
+def _pair_streamed(m: int, n: int, k: int) -> int:
+    """How many pairs walk the stages of (m, n, k)'s tiles as one stream (0: whole tiles)."""
+    key = (m, n, k)
+    v = _pair_streamed_cache.get(key)
+    if v is None:
+        v = _pair_streamed_cache[key] = _fn("gemm_tc_wide", "plm_gemm_tc_pair_streamed")(m, n, k, SM_COUNT)
+    return v
 
 
 def wide_how(m: int, n: int, k: int, epilogue: int = 0):
@@ -277,16 +295,20 @@ def wide_how(m: int, n: int, k: int, epilogue: int = 0):
 
 
 def pair_pays(m: int, n: int, k: int = 0, epilogue: int = 0) -> bool:
-    """Whether the prompt-shaped product runs as pairs of CTAs on tiles of 256 x 256.  Measured: 3..5 % faster
-    than single CTAs on tiles of 128 x 256 where the pairs have at least one tile each, a little faster or
-    the same down to half as many tiles, and slower than single CTAs that walk the K blocks as one stream
-    where the tiles are few (with `k` given, that case is left to them)."""
-    if m < 256 or n < 256:
+    """Whether the prompt-shaped product runs as pairs of CTAs on tiles of 256 x 256: from half a round of
+    such tiles for the 74 pairs on (measured faster than single CTAs there: the pairs take two tiles of K per copy,
+    and the copies bound the single CTAs), and below that where the pairs can walk the tiles' stages of K as one
+    stream (with `k` given: K a multiple of 64, enough stages).  `epilogue` 0 store, 1 SwiGLU, 2 add."""
+    if m < 256 or n < 256 or (k and k % 64):
         return False
     tiles = ((m + 255) // 256) * ((n + 255) // 256)
-    if k and wide_how(m, n, k, epilogue)[2] > 0 and tiles < SM_COUNT // 2:
+    if tiles >= SM_COUNT // 4:
+        return True
+    if not k or not stream_space_enabled():
         return False
-    return tiles >= SM_COUNT // 4
+    if epilogue == 0 and wide_how(m, n, k, 0)[1] > 1:
+        return False                            # few tiles, store: the single CTAs cut K through scratch memory
+    return _pair_streamed(m, n, k) > 0
 
 
 def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):

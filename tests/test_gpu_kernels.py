@@ -718,8 +718,7 @@ def test_attention_prefill_tcgen05_with_one_slow_warp():
 
 
 @pytest.mark.parametrize("epilogue", ["float32", "bfloat16", "swiglu", "add"])
-@pytest.mark.parametrize("M,N,K", [(2048, 3072, 520), (130, 512, 8192), (2300, 3000, 1032), (1024, 2304, 6144),
-                                   (128, 256, 8192)])
+@pytest.mark.parametrize("M,N,K", [(1100, 2100, 6144), (130, 512, 8192), (1024, 2304, 6144), (128, 256, 8192)])
 def test_gemm_tc_wide_stream_walk(epilogue, M, N, K):
     """The K blocks of all tiles handed out as one stream: tiles cut between two CTAs and among many (few
     tiles with a long K), with every epilogue, against float64; three launches in a row (the flags go down
@@ -763,6 +762,45 @@ def test_gemm_tc_wide_stream_walk(epilogue, M, N, K):
     if epilogue != "add":
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     from picolm_b200.ops._lib import stream_space
+    assert int(stream_space(DEV)[1].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("epilogue", ["float32", "bfloat16", "swiglu", "add"])
+@pytest.mark.parametrize("M,N,K", [(1024, 2304, 6144), (512, 2048, 8192), (300, 700, 8192)])
+def test_gemm_tc_pair_stream_walk(epilogue, M, N, K):
+    """Pairs of CTAs that walk the stages of few tiles as one stream (each CTA of a pair leaves and adds the part
+    of its own 128 rows): against float64, three launches with the same bits, ragged edges."""
+    from picolm_b200 import ops
+    from picolm_b200.ops._lib import _fn, stream_space
+    if epilogue == "swiglu":
+        N = N // 128 * 128
+    assert _fn("gemm_tc_wide", "plm_gemm_tc_pair_streamed")(M, N, K, 148) > 0, "the shape was chosen to take the stream walk"
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
+    w = (torch.randn(N, K) / K ** 0.25).to(torch.bfloat16)
+    a[:, K // 3] += 2.0
+    w[N // 2, :] *= 3.0
+    a[M // 2, :] *= -2.0
+    y = a.double() @ w.double().t()
+    ad, wd = a.to(DEV), w.to(DEV)
+    x0 = torch.randn(M, N) * 3
+    outs = []
+    for _ in range(3):
+        if epilogue == "swiglu":
+            wi = ops.interleave_gate_up(wd[: N // 2].contiguous(), wd[N // 2:].contiguous())
+            got = ops.gemm_tc_wide(ad, wi, torch.bfloat16, swiglu=True, pair=True)
+            g, u = y[:, : N // 2].bfloat16().double(), y[:, N // 2:].bfloat16().double()
+            ref, tol_ = g / (1 + torch.exp(-g)) * u, dict(atol=3e-2, rtol=2e-2)
+        elif epilogue == "add":
+            got = ops.gemm_tc_wide(ad, wd, torch.float32, out=x0.to(DEV), add=True, pair=True)
+            ref, tol_ = x0.double() + y, dict(atol=2e-3, rtol=1e-4)
+        else:
+            got = ops.gemm_tc_wide(ad, wd, DT[epilogue], pair=True)
+            ref, tol_ = y, dict(atol=2e-3, rtol=1e-4) if epilogue == "float32" else dict(atol=3e-2, rtol=2e-2)
+        ops.check_status(DEV)
+        assert torch.allclose(got.double().cpu(), ref, **tol_)
+        outs.append(got)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert int(stream_space(DEV)[1].abs().sum()) == 0
 
 

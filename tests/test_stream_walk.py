@@ -53,8 +53,9 @@ def test_when_the_stream_walk_is_taken():
         assert how(T, F, K, epilogue, slots, ctypes.cast(out, ctypes.c_void_p)) == 0
         return tuple(out)
 
-    assert ask(4096, 2048, 8192, 0, 148)[2] == 148              # 256 tiles: two rounds of whole tiles, 1.73 as a stream
-    assert ask(4096, 2048, 8192, 0, 0)[2] == 0                  # no workspace: whole tiles
+    assert ask(4096, 2048, 8192, 0, 148)[2] == 0                # 256 tiles, 1.73 rounds: whole tiles (measured faster)
+    assert ask(1536, 2048, 8192, 0, 148)[2] == 148              # 96 tiles: a third of the SMs would idle
+    assert ask(1536, 2048, 8192, 0, 0)[2] == 0                  # no workspace: whole tiles
     assert ask(128 * 148, 256 * 4, 512, 0, 148)[2] == 0         # four full rounds: whole tiles
     assert ask(2048, 2048, 8192, 0, 148)[2] == 0                # 128 tiles for 148 SMs: the parts would cost more
     assert ask(1024, 2048, 8192, 0, 148)[2] == 128              # 64 tiles: less than half of the SMs would work; two CTAs a tile
