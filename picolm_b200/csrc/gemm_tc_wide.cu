@@ -35,6 +35,8 @@
 // its commits arrive at the "empty" and "accumulator full" barriers of both CTAs (commit with
 // multicast), and both CTAs' epilogues arrive at ITS "accumulator empty" barriers.  No TMA load
 // uses multicast.
+#include <cstring>
+
 #include "tc_common.cuh"
 
 using namespace plm_tc;
@@ -46,8 +48,12 @@ constexpr int TURN_LD = 36;                                  // floats per row o
 constexpr size_t TURN_BYTES = 4 * 32 * TURN_LD * 4;          // for the four epilogue warps
 
 __host__ __device__ constexpr int stages_of(int bn) { return bn >= 256 ? 4 : 6; }
-__host__ __device__ constexpr size_t wide_smem(int bn) {
-    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + TURN_BYTES;
+// The add to the stream leaves the tile to the copy engine, 128 rows x 32 columns of floats at a time (16 KB, two
+// of them in turn); the other epilogues turn their pieces over in TURN_BYTES.  Both start where the ring ends.
+constexpr size_t OUT_PIECE = (size_t)BM * 32 * 4, OUT_BYTES = 2 * OUT_PIECE;
+__host__ __device__ constexpr size_t epilogue_smem(int epi) { return epi == 2 ? OUT_BYTES : (TURN_BYTES + 1023) / 1024 * 1024; }
+__host__ __device__ constexpr size_t wide_smem(int bn, int epi) {
+    return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + epilogue_smem(epi);
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -80,8 +86,8 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_pair(int n) {
 }
 constexpr int PAIR_SLABS = 2;                                // tiles of 64 columns of K per stage and copy
 __host__ __device__ constexpr int pair_stages() { return 3; }
-__host__ __device__ constexpr size_t pair_smem() {
-    return (size_t)pair_stages() * PAIR_SLABS * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + TURN_BYTES;
+__host__ __device__ constexpr size_t pair_smem(int epi) {
+    return (size_t)pair_stages() * PAIR_SLABS * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256 + epilogue_smem(epi);
 }
 
 // ---------------------------------------------------------------- the work of a CTA
@@ -162,6 +168,21 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 }
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the four epilogue warps
 
+// out[rows from `row`, columns from `col`] += the 128 x 32 floats at `src` (rows of 128 bytes, 128-byte swizzle), by the
+// copy engine: the add happens where the data lives, and nothing of `out` comes to this SM.  Rows and columns beyond
+// the tensor's edges are left out.  One thread; the copies of a thread form groups that it can wait for.
+__device__ __forceinline__ void copy_add_out(const CUtensorMap* map, uint32_t src, int col, int row) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(col), "r"(row) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// wait until all but the `N` latest groups of this thread's copies have read their shared memory
+template <int N> __device__ __forceinline__ void copies_have_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void copies_done() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_for_copies() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // A part in the workspace: [column / 4][row 0..127][4], so that the 32 rows of a warp lie side by side.
 __device__ __forceinline__ size_t part_offset(int row, int col) { return ((size_t)(col >> 2) * BM + row) * 4; }
 
@@ -229,7 +250,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
                     int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride,
-                    float* parts, int* flags) {
+                    float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies) {
     static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
     constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
@@ -242,11 +263,12 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t x_smem = base, w_smem = base + STAGES * X_BYTES;
-    const uint32_t bars = w_smem + STAGES * W_BYTES;
+    const uint32_t epi_smem = w_smem + STAGES * W_BYTES;                 // 1,024-byte aligned: the ring's sizes are
+    const uint32_t bars = epi_smem + (uint32_t)epilogue_smem(EPI);
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_full0 = bars + 16 * STAGES,
                    acc_empty0 = acc_full0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (acc_empty0 + 16 - raw));
-    float* turn_base = reinterpret_cast<float*>(smem_raw + (bars + 256 - raw));
+    float* turn_base = reinterpret_cast<float*>(smem_raw + (epi_smem - raw));
     __shared__ int s_abort, s_parts_missing;
 
     pdl_launch_dependents();
@@ -491,7 +513,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             };
             if (w.kind != PIECE_PART && EPI != EPI_SWIGLU) {
-                if (F32_OUT) get_old(0);
+                if (F32_OUT && !out_by_copies) get_old(0);
                 get_part(0);
             }
             if (threadIdx.x == 64) WIDE_TRACE(4 + 3 * j);
@@ -557,11 +579,25 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 8; ++i) { old[i] = old_n[i]; part[i] = part_n[i]; }
                     if (c + 32 < c_end) {
-                        if (F32_OUT) get_old(c + 32);
+                        if (F32_OUT && !out_by_copies) get_old(c + 32);
                         get_part(c + 32);
                     }
                     add_parts(r, c, part);
-                    if (F32_OUT) {
+                    if (EPI == EPI_RESIDUAL && out_by_copies) {
+                        // the piece goes to shared memory as the copy engine wants it (a row's eight 16-byte chunks
+                        // at places turned by the row's number), and one thread hands it over; two pieces in turn
+                        const uint32_t piece = epi_smem + (uint32_t)(((c >> 5) & 1) * OUT_PIECE);
+                        if (threadIdx.x == 64) copies_have_read<1>();        // the copy that read this piece's room before
+                        epilogue_sync();
+                        uint8_t* mine = smem_raw + (piece - raw) + my_row * 128;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<uint4*>(mine + ((i ^ (my_row & 7)) << 4)) =
+                                make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                        fence_for_copies();
+                        epilogue_sync();
+                        if (threadIdx.x == 64 && f0 + c < F) copy_add_out(&map_out, piece, f0 + c, m0);
+                    } else if (F32_OUT) {
                         if (f0 + c < F) {
                             turn_put_f32(turn, lane, r);
                             __syncwarp();
@@ -609,6 +645,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (PAIR) mbar_arrive_cluster(cluster_map_addr(acc_empty0 + 8 * acc, 0)); else mbar_arrive(acc_empty0 + 8 * acc);
         }
     }
+    if (EPI == EPI_RESIDUAL && threadIdx.x == 64) copies_done();         // this thread's copies out of shared memory
     tc_fence_before();
     __syncthreads();
     if (PAIR) cluster_sync_all();          // the other CTA's MMAs read this CTA's tiles and write its tensor memory
@@ -632,11 +669,42 @@ int sm_count() {
     return n;
 }
 
+// The fp32 stream out[T, F] (leading dimension ldo floats) as the copy engine adds to it: pieces of 128 rows x 32
+// columns, 128-byte swizzle.  `usable`: whether it can (16-byte aligned rows); else the epilogue adds by itself.
+struct OutMap { CUtensorMap map; int usable; };
+OutMap out_map(const void* out, int out_is_f32, int epilogue, int T, int F, long ldo) {
+    OutMap m;
+    memset(&m, 0, sizeof(m));
+    if (epilogue != EPI_RESIDUAL || !out_is_f32 || ldo % 4 || ((uintptr_t)out & 15)) return m;
+    struct Entry { const void* ptr; int T, F; long ldo; bool used; CUtensorMap map; };
+    static Entry table[64];
+    static std::mutex lock;
+    Entry& e = table[(((size_t)out >> 8) * 0x9E3779B97F4A7C15ull >> 40) % 64];
+    {
+        std::lock_guard<std::mutex> g(lock);
+        if (e.used && e.ptr == out && e.T == T && e.F == F && e.ldo == ldo) { m.map = e.map; m.usable = 1; return m; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return m;
+    cuuint64_t dims[2] = {(cuuint64_t)F, (cuuint64_t)T};
+    cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(&m.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(out), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return m;
+    m.usable = 1;
+    std::lock_guard<std::mutex> g(lock);
+    e.ptr = out; e.T = T; e.F = F; e.ldo = ldo; e.map = m.map; e.used = true;
+    return m;
+}
+
 template <int EPI, typename OutT>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
                 cudaStream_t stream, float* parts = nullptr, int* flags = nullptr, int streamed_pairs = 0) {
     static bool configured = false;
-    constexpr size_t smem = pair_smem();
+    constexpr size_t smem = pair_smem(EPI);
     auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -647,10 +715,12 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     if (streamed_pairs) pairs = streamed_pairs;
+    const OutMap mo = out_map(out, sizeof(OutT) == 4, EPI, T, F, ldo);
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
                                             out, T, F, K, ldo, m_tiles, n_tiles, status, 1,
                                             (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), (size_t)0,
-                                            streamed_pairs ? parts : (float*)nullptr, streamed_pairs ? flags : (int*)nullptr));
+                                            streamed_pairs ? parts : (float*)nullptr, streamed_pairs ? flags : (int*)nullptr,
+                                            mo.map, mo.usable));
 }
 
 // The parts and flags of the stream walk (see Walk): `slots` slots of BM * 256 floats and as many flags, which
@@ -686,7 +756,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
            cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0,
            StreamSpace space = StreamSpace{nullptr, nullptr, 0}, int streamed = 0) {
     static bool configured = false;
-    constexpr size_t smem = wide_smem(BN);
+    constexpr size_t smem = wide_smem(BN, EPI);
     auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -699,9 +769,11 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
     if (kb_per_split <= 0) kb_per_split = (K + BK - 1) / BK;
     if (k_splits > 1) streamed = 0;
     if (streamed) ctas = streamed;
+    const OutMap mo = out_map(out, sizeof(OutT) == 4, EPI, T, F, ldo);
     return plm_status_of(launch_pdl(kern, dim3(ctas), dim3(NUM_THREADS), smem, stream, mx, mw, out, T, F, K, ldo, m_tiles,
                                     n_tiles, status, k_splits, kb_per_split, split_stride,
-                                    streamed ? space.parts : (float*)nullptr, streamed ? space.flags : (int*)nullptr));
+                                    streamed ? space.parts : (float*)nullptr, streamed ? space.flags : (int*)nullptr,
+                                    mo.map, mo.usable));
 }
 
 // out[i] = sum over the K splits of scratch[s * stride + i], in order; four at a time.
