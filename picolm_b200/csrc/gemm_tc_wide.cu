@@ -51,7 +51,7 @@ __host__ __device__ constexpr int stages_of(int bn) { return bn >= 256 ? 4 : 6; 
 // The add to the stream leaves the tile to the copy engine, 128 rows x 32 columns of floats at a time (16 KB, two
 // of them in turn); the other epilogues turn their pieces over in TURN_BYTES.  Both start where the ring ends.
 constexpr size_t OUT_PIECE = (size_t)BM * 32 * 4, OUT_BYTES = 2 * OUT_PIECE;
-__host__ __device__ constexpr size_t epilogue_smem(int epi) { return epi == 2 ? OUT_BYTES : (TURN_BYTES + 1023) / 1024 * 1024; }
+__host__ __device__ constexpr size_t epilogue_smem(int) { return OUT_BYTES > TURN_BYTES ? OUT_BYTES : TURN_BYTES; }
 __host__ __device__ constexpr size_t wide_smem(int bn, int epi) {
     return (size_t)stages_of(bn) * (BM * BK * 2 + bn * BK * 2) + 1024 + 256 + epilogue_smem(epi);
 }
@@ -175,6 +175,25 @@ __device__ __forceinline__ void copy_add_out(const CUtensorMap* map, uint32_t sr
     asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"((uint64_t)map), "r"(src), "r"(col), "r"(row) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// the same as a plain store (16-bit types: 128 x 64 elements)
+__device__ __forceinline__ void copy_store_out(const CUtensorMap* map, uint32_t src, int col, int row) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(col), "r"(row) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// 32 floats as 32 bf16 (64 bytes) into chunks chunk0 .. chunk0 + 3 of row `row` of a piece with 128-byte swizzle
+__device__ __forceinline__ void stage_bf16(uint8_t* piece, int row, int chunk0, const uint32_t* r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * k]), __uint_as_float(r[8 * i + 2 * k + 1]));
+            w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(piece + row * 128 + (((chunk0 + i) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 // wait until all but the `N` latest groups of this thread's copies have read their shared memory
 template <int N> __device__ __forceinline__ void copies_have_read() {
@@ -562,11 +581,27 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             gt[i] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[i]), __uint_as_float(up[i])));
-                        turn_put_bf16(turn, lane, cc >> 5, gt);
+                        if (out_by_copies) {
+                            const uint32_t piece = epi_smem + (uint32_t)(((gq >> 7) & 1) * OUT_PIECE);
+                            if (cc == 0) {
+                                if (threadIdx.x == 64) copies_have_read<1>();    // the copy that read this piece's room before
+                                epilogue_sync();
+                            }
+                            stage_bf16(smem_raw + (piece - raw), my_row, cc >> 3, gt);
+                        } else {
+                            turn_put_bf16(turn, lane, cc >> 5, gt);
+                        }
                     }
-                    __syncwarp();
-                    turn_write_bf16(turn, lane, outb, ldo, row0, T, (f0 + gq) / 2, F / 2, aligned);
-                    __syncwarp();                                        // the piece is read before the next one overwrites it
+                    if (out_by_copies) {
+                        fence_for_copies();
+                        epilogue_sync();
+                        if (threadIdx.x == 64)
+                            copy_store_out(&map_out, epi_smem + (uint32_t)(((gq >> 7) & 1) * OUT_PIECE), (f0 + gq) / 2, m0);
+                    } else {
+                        __syncwarp();
+                        turn_write_bf16(turn, lane, outb, ldo, row0, T, (f0 + gq) / 2, F / 2, aligned);
+                        __syncwarp();                                    // the piece is read before the next one overwrites it
+                    }
                 }
             } else {
                 // 32 columns at a time, two register sets in turn: the next 32 columns are on their way out of
@@ -597,6 +632,30 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         fence_for_copies();
                         epilogue_sync();
                         if (threadIdx.x == 64 && f0 + c < F) copy_add_out(&map_out, piece, f0 + c, m0);
+                    } else if (F32_OUT && out_by_copies) {               // a plain store of floats, the same way
+                        const uint32_t piece = epi_smem + (uint32_t)(((c >> 5) & 1) * OUT_PIECE);
+                        if (threadIdx.x == 64) copies_have_read<1>();
+                        epilogue_sync();
+                        uint8_t* mine = smem_raw + (piece - raw) + my_row * 128;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<uint4*>(mine + ((i ^ (my_row & 7)) << 4)) =
+                                make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                        fence_for_copies();
+                        epilogue_sync();
+                        if (threadIdx.x == 64 && f0 + c < F) copy_store_out(&map_out, piece, f0 + c, m0);
+                    } else if (!F32_OUT && out_by_copies) {              // bf16: two rounds of 32 columns fill a piece of 64
+                        const uint32_t piece = epi_smem + (uint32_t)(((c >> 6) & 1) * OUT_PIECE);
+                        if (!(c & 32)) {
+                            if (threadIdx.x == 64) copies_have_read<1>();
+                            epilogue_sync();
+                        }
+                        stage_bf16(smem_raw + (piece - raw), my_row, (c & 32) >> 3, r);
+                        if (c & 32) {
+                            fence_for_copies();
+                            epilogue_sync();
+                            if (threadIdx.x == 64 && f0 + (c & ~63) < F) copy_store_out(&map_out, piece, f0 + (c & ~63), m0);
+                        }
                     } else if (F32_OUT) {
                         if (f0 + c < F) {
                             turn_put_f32(turn, lane, r);
@@ -645,7 +704,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (PAIR) mbar_arrive_cluster(cluster_map_addr(acc_empty0 + 8 * acc, 0)); else mbar_arrive(acc_empty0 + 8 * acc);
         }
     }
-    if (EPI == EPI_RESIDUAL && threadIdx.x == 64) copies_done();         // this thread's copies out of shared memory
+    if (threadIdx.x == 64) copies_done();                                // this thread's copies out of shared memory
     tc_fence_before();
     __syncthreads();
     if (PAIR) cluster_sync_all();          // the other CTA's MMAs read this CTA's tiles and write its tensor memory
@@ -669,34 +728,40 @@ int sm_count() {
     return n;
 }
 
-// The fp32 stream out[T, F] (leading dimension ldo floats) as the copy engine adds to it: pieces of 128 rows x 32
-// columns, 128-byte swizzle.  `usable`: whether it can (16-byte aligned rows); else the epilogue adds by itself.
+// The result as the copy engine writes it (or adds to it): pieces of 128 rows x 128 bytes, 128-byte swizzle.
+// `usable`: whether it can (16-byte aligned rows); else the epilogue's threads write by themselves.
 struct OutMap { CUtensorMap map; int usable; };
-OutMap out_map(const void* out, int out_is_f32, int epilogue, int T, int F, long ldo) {
+// `out` [T, F_out] with leading dimension ldo elements, of floats (pieces of 128 x 32) or bf16 (128 x 64).
+OutMap out_map(const void* out, int out_is_f32, int T, int F_out, long ldo) {
     OutMap m;
     memset(&m, 0, sizeof(m));
-    if (epilogue != EPI_RESIDUAL || !out_is_f32 || ldo % 4 || ((uintptr_t)out & 15)) return m;
-    struct Entry { const void* ptr; int T, F; long ldo; bool used; CUtensorMap map; };
+    const int esize = out_is_f32 ? 4 : 2;
+    if ((ldo * esize) % 16 || ((uintptr_t)out & 15)) return m;
+    struct Entry { const void* ptr; int T, F, f32; long ldo; bool used; CUtensorMap map; };
     static Entry table[64];
     static std::mutex lock;
     Entry& e = table[(((size_t)out >> 8) * 0x9E3779B97F4A7C15ull >> 40) % 64];
     {
         std::lock_guard<std::mutex> g(lock);
-        if (e.used && e.ptr == out && e.T == T && e.F == F && e.ldo == ldo) { m.map = e.map; m.usable = 1; return m; }
+        if (e.used && e.ptr == out && e.T == T && e.F == F_out && e.ldo == ldo && e.f32 == out_is_f32) {
+            m.map = e.map;
+            m.usable = 1;
+            return m;
+        }
     }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return m;
-    cuuint64_t dims[2] = {(cuuint64_t)F, (cuuint64_t)T};
-    cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
-    cuuint32_t box[2] = {32, (cuuint32_t)BM};
+    cuuint64_t dims[2] = {(cuuint64_t)F_out, (cuuint64_t)T};
+    cuuint64_t strides[1] = {(cuuint64_t)ldo * esize};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)BM};
     cuuint32_t estr[2] = {1, 1};
-    if (fn(&m.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(out), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (fn(&m.map, out_is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(out),
+           dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return m;
     m.usable = 1;
     std::lock_guard<std::mutex> g(lock);
-    e.ptr = out; e.T = T; e.F = F; e.ldo = ldo; e.map = m.map; e.used = true;
+    e.ptr = out; e.T = T; e.F = F_out; e.ldo = ldo; e.f32 = out_is_f32; e.map = m.map; e.used = true;
     return m;
 }
 
@@ -715,7 +780,7 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     if (streamed_pairs) pairs = streamed_pairs;
-    const OutMap mo = out_map(out, sizeof(OutT) == 4, EPI, T, F, ldo);
+    const OutMap mo = out_map(out, sizeof(OutT) == 4, T, EPI == EPI_SWIGLU ? F / 2 : F, ldo);
     return plm_status_of(launch_pdl_cluster(kern, dim3(2 * pairs), dim3(NUM_THREADS), dim3(2, 1, 1), smem, stream, mx, mw,
                                             out, T, F, K, ldo, m_tiles, n_tiles, status, 1,
                                             (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), (size_t)0,
@@ -769,7 +834,9 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
     if (kb_per_split <= 0) kb_per_split = (K + BK - 1) / BK;
     if (k_splits > 1) streamed = 0;
     if (streamed) ctas = streamed;
-    const OutMap mo = out_map(out, sizeof(OutT) == 4, EPI, T, F, ldo);
+    // (the slices of a K split go to scratch memory by the threads' own stores)
+    OutMap mo = out_map(out, sizeof(OutT) == 4, T, EPI == EPI_SWIGLU ? F / 2 : F, ldo);
+    if (k_splits > 1) mo.usable = 0;
     return plm_status_of(launch_pdl(kern, dim3(ctas), dim3(NUM_THREADS), smem, stream, mx, mw, out, T, F, K, ldo, m_tiles,
                                     n_tiles, status, k_splits, kb_per_split, split_stride,
                                     streamed ? space.parts : (float*)nullptr, streamed ? space.flags : (int*)nullptr,
