@@ -13,13 +13,18 @@
 //   EPI_SWIGLU  W's rows come in tiles of 64 gate rows followed by their 64 up rows;
 //               out[t, f] = silu(gate) * up, [T, F/2] in bf16
 //   EPI_RESIDUAL out += product, out being the fp32 residual stream (x = x + delta,
-//               picolm/model_core.c:3120 and 3201).  A thread of the epilogue holds one token's row of
-//               the accumulator, and rows of the stream lie far apart: each warp turns its 32 x 32 piece
-//               over in shared memory, so that a quarter of a warp reads, adds to and writes 128
-//               consecutive bytes of one row.
+//               picolm/model_core.c:3120 and 3201)
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
 // epilogue.  Waits on mbarriers are bounded; a wait that runs out records where in `status`
 // and the CTA drains and leaves.
+//
+// The epilogue.  A thread holds one token's row of the accumulator, 32 columns at a time (the next 32 are
+// on their way out of tensor memory meanwhile).  Where the result's rows are 16-byte aligned it writes them
+// into a piece of 128 rows x 128 bytes in shared memory, laid out as the copy engine wants it (128-byte
+// swizzle), and one thread hands the piece over: a tensor store, or for EPI_RESIDUAL a tensor reduce-add, so
+// that the add happens where the stream lives and its old values never come to the SM.  Otherwise each warp
+// turns its 32 rows over in shared memory so that a quarter of a warp writes (or reads, adds to and writes)
+// 128 consecutive bytes of one row.
 //
 // K splits (single CTAs, store epilogue): where a problem has fewer tiles than SMs (prompts of a few
 // hundred tokens), every tile's K range is cut into `k_splits` parts that are units of work of their own;
@@ -29,8 +34,10 @@
 // PAIR: two CTAs of a cluster (two SMs) work on one tile of 256 tokens x 256 features with
 // tcgen05.mma.cta_group::2.  Each CTA loads its 128 token rows and HALF of the weight tile (128
 // features), the tensor cores of both SMs read both halves, and each CTA's tensor memory receives
-// its own 128 rows of the result.  A 128 x 256 tile is bound by what an SM has to bring in from L2
-// per MMA cycle (48 KB per K block of 64); the pair brings in 32 KB each for the same work.  The
+// its own 128 rows of the result.  What bounds these kernels is the NUMBER of tensor copies: a copy keeps
+// the SM's copy engine busy for about 190 cycles plus 6.6 a KB, and two copies of 16 KB per 64 columns of K
+// took longer than those columns' MMAs (512 cycles).  A pair's stage therefore holds two 64-column tiles of K
+// per operand, each operand's brought in by one copy (a 3-D tensor map, see make_map).  The
 // CTA of rank 0 issues all MMAs: both CTAs' loads signal ITS "full" barriers (expect-tx set there),
 // its commits arrive at the "empty" and "accumulator full" barriers of both CTAs (commit with
 // multicast), and both CTAs' epilogues arrive at ITS "accumulator empty" barriers.  No TMA load
