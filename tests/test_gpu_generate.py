@@ -71,7 +71,9 @@ def test_generation_across_a_new_graph(tmp_path):
     want = [P.greedy(cfg, w, p, 40) for p in prompts]
     eng = model_load(d, dtype="float32", max_batch=2)
     assert generate(eng, prompts, max_tokens=40, temperature=0.0, stop_ids=[]) == want
-    assert len(eng._graphs) >= 2                              # the two length classes each have a graph
+    from picolm_b200.ops import _lib
+    if not (_lib.CHECKED or _lib.TRACED):                     # (those builds launch every kernel by itself)
+        assert len(eng._graphs) >= 2                          # the two length classes each have a graph
     eng16 = model_load(d, dtype="bfloat16", max_batch=2)
     a = generate(eng16, prompts, max_tokens=40, temperature=0.0, stop_ids=[])
     b = generate(eng16, prompts, max_tokens=40, temperature=0.0, stop_ids=[], steps_per_sync=1)

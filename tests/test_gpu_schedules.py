@@ -52,7 +52,9 @@ def test_two_hundred_live_sequences(tmp_path, model_dirs, which, dtype):
     reqs, prompt_lens = _crowd(vocab, 5)
     eng = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 200, max_seqs=200)
     outs = run_batch(eng, reqs, prompt_lens)
-    assert {k[0] for k in eng._graphs} >= {256, 192, 128, 96, 64, 48}
+    from picolm_b200.ops import _lib
+    if not (_lib.CHECKED or _lib.TRACED):                     # (those builds launch every kernel by itself)
+        assert {k[0] for k in eng._graphs} >= {256, 192, 128, 96, 64, 48}
     act = torch.bfloat16 if dtype == "bfloat16" else None
     for i in list(range(0, 200, 7)) + [199]:
         assert_close(outs[i], P.forward(cfg, w, reqs[i], act_dtype=act), dtype, f"{which} {dtype} request {i} of 200")
@@ -220,6 +222,9 @@ def test_prompt_steps_from_graphs_give_the_logits_of_single_launches(tmp_path):
     eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
     plain = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
     plain.prompt_graphs = False
+    from picolm_b200.ops import _lib
+    if _lib.CHECKED or _lib.TRACED:
+        pytest.skip("the checked and the traced build launch every kernel by itself")
     assert eng.prompt_graphs
     V = WIDE["vocab_size"]
 
