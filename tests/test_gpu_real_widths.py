@@ -142,3 +142,43 @@ def test_a_long_sequence(tmp_path_factory, dtype):
     eng.cache.check()
     if dtype == "bfloat16":
         ops.check_status()
+
+
+# Prompts long enough for the forms of the prompt-shaped product that short prompts never reach: pairs of CTAs
+# with two tiles of K per copy (QKV, gate/up with SwiGLU), pairs that walk few tiles' stages as one stream (the down
+# projection of 1,024 tokens), the add to the stream and the stores by the copy engine, and a prompt step replayed
+# from a CUDA graph of its length class.  Layer sizes of Llama-3.2-1B, a small vocabulary.
+CONFIG_PROMPT = dict(CONFIG, vocab_size=2000, tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+
+
+def test_long_prompts_at_real_widths(tmp_path_factory):
+    from picolm_b200 import ops
+    from picolm_b200.engine import Engine
+    from picolm_b200.ops.gemm import _pair_streamed, pair_pays
+    assert pair_pays(1024, 3072, 2048, 0) and pair_pays(1024, 16384, 2048, 1)       # the forms named above are
+    assert pair_pays(1024, 2048, 8192, 2) and _pair_streamed(1024, 2048, 8192) > 0  # what these prompts run
+    d = make_model_dir(str(tmp_path_factory.mktemp("prompt") / "m"), CONFIG_PROMPT, 11, sharpen=4.0)
+    cfg, w = P.load_model(d)
+    toks = {n: random_tokens(n, CONFIG_PROMPT["vocab_size"], 900 + n) for n in (1024, 700)}
+    ref = {n: P.forward(cfg, w, t, act_dtype=torch.bfloat16) for n, t in toks.items()}
+    rows = {1024: [0, 1, 127, 128, 255, 256, 511, 777, 1023], 700: [0, 63, 64, 300, 699]}
+    for graphs in (True, False):
+        eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=2)
+        eng.prompt_graphs = graphs and eng.prompt_graphs
+        for n in (1024, 700, 1024):                           # the second 1,024 replays the graph of the first
+            s = eng.new_sequence()
+            try:
+                got = eng.step([(s, toks[n])], [rows[n]]).float().cpu()
+            finally:
+                eng.end_sequence(s)
+            assert_close(got, ref[n][rows[n]], "bfloat16", f"{n} tokens, graphs {graphs}")
+        both = [eng.new_sequence(), eng.new_sequence()]       # the two prompts in one step: 1,724 rows
+        try:
+            got = eng.step([(both[0], toks[1024]), (both[1], toks[700])], [rows[1024], rows[700]]).float().cpu()
+        finally:
+            for s in both:
+                eng.end_sequence(s)
+        assert_close(got, torch.cat([ref[1024][rows[1024]], ref[700][rows[700]]]), "bfloat16", f"both, graphs {graphs}")
+        eng.cache.check()
+        ops.check_status()
+        del eng
