@@ -391,3 +391,30 @@ extern "C" int plm_rope_store(const void* qkv, void* q_out, void* kc, void* vc, 
                                         tok_seq, block_table, max_pages, H, G, hd, rot_dim, pairing, store));
     return PLM_ERR_DTYPE;
 }
+
+// dst[i, :] = src[rows[i], :] for rows of `row_bytes` bytes (a multiple of 4; 16 bytes at a time where the rows
+// and both pointers allow it).  Rows of a prompt step that are wanted further on, out of all of its rows.
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, const int* __restrict__ rows,
+                                   long row_bytes, long src_ld, int wide) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const uint8_t* s = src + (size_t)PLM_ROW_NO(rows[i]) * src_ld;
+    uint8_t* d = dst + (size_t)i * row_bytes;
+    if (wide) {
+        for (long o = (long)threadIdx.x * 16; o < row_bytes; o += (long)blockDim.x * 16)
+            *reinterpret_cast<uint4*>(d + o) = *reinterpret_cast<const uint4*>(s + o);
+    } else {
+        for (long o = (long)threadIdx.x * 4; o < row_bytes; o += (long)blockDim.x * 4)
+            *reinterpret_cast<uint32_t*>(d + o) = *reinterpret_cast<const uint32_t*>(s + o);
+    }
+}
+
+extern "C" int plm_gather_rows(const void* src, void* dst, const int* rows, int n_rows, long row_bytes, long src_ld_bytes,
+                               cudaStream_t stream) {
+    if (n_rows <= 0 || row_bytes <= 0) return PLM_OK;
+    if (row_bytes % 4 || src_ld_bytes % 4 || (((uintptr_t)src | (uintptr_t)dst) & 3)) return PLM_ERR_ALIGN;
+    const int wide = row_bytes % 16 == 0 && src_ld_bytes % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0);
+    return plm_status_of(launch_pdl(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, (const uint8_t*)src,
+                                    (uint8_t*)dst, rows, row_bytes, src_ld_bytes, wide));
+}

@@ -134,14 +134,23 @@ class Model:
         [wanted rows, vocab] (None if no row is wanted)."""
         stream = ResidualStream(self.embedding.forward(step))
         hook = self.layer_hook
+        last = len(self.spec.schedule) - 1
         for run, i in enumerate(self.spec.schedule):
             if hook is not None:
                 hook(run, i, False)
-            self.blocks[i].forward(stream, step, self.layer_caches(run, cache, step))
+            block = self.blocks[i]
+            # Nothing but the final norm reads what the last layer leaves, and that at the wanted rows only: a layer
+            # that can narrows the stream to them once its mixer is through (a prompt's feed-forward then runs on
+            # its last row alone).  Worth it where few of the step's rows are wanted.
+            if run == last and getattr(block, "narrows_rows", False) and 4 * step.n_want <= step.n_tokens:
+                keep = step.want_rows if step.n_want > 0 else torch.empty(0, dtype=torch.int32, device=stream.x.device)
+                block.forward(stream, step, self.layer_caches(run, cache, step), keep_rows=keep)
+            else:
+                block.forward(stream, step, self.layer_caches(run, cache, step))
             if hook is not None:
                 hook(run, i, True)
         if step.n_want == 0:
             # the last delta need not be added: nothing reads the stream after it
             return None
-        h = self.final_norm.forward(stream, rows=step.want_rows)
+        h = self.final_norm.forward(stream, rows=None if stream.narrowed else step.want_rows)
         return self.head.forward(h)

@@ -9,7 +9,7 @@ from .attention import (DECODE_CLUSTER_SPLITS, Rotation, attention, attention_de
                         attention_decode_rope, attention_decode_rope_supported, attention_mma_supported,
                         attention_prefill, attention_prefill_tc, attention_rows, attention_tc_supported, decode_splits)
 from .chain import Chain, LazyRows  # noqa: F401
-from .elementwise import GATE_ACTIVATIONS, embed, rmsnorm, rope_store, swiglu  # noqa: F401
+from .elementwise import GATE_ACTIVATIONS, embed, gather_rows, rmsnorm, rope_store, swiglu  # noqa: F401
 from .gemm import (PendingLinear, ScaledRows, gemm_simt, gemm_tc_skinny, gemm_tc_supported,  # noqa: F401
                    gemm_tc_wide, interleave_gate_up, linear, linear_residual_norm, linear_swiglu, pair_pays,
                    residual_norm_supported)

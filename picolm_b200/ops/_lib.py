@@ -26,6 +26,7 @@ _SIGNATURES = {
     "plm_gemm_tc_skinny_residual_parts": [_i, _i],
     "plm_gemm_tc_skinny_scaled": [_vp, _vp, _vp, _i, _i, _i, _i, _l, _l, _l, _vp, _i, _i, _i, _f, _vp, _vp],
     "plm_scale_rows": [_vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp],
+    "plm_gather_rows": [_vp, _vp, _vp, _i, _l, _l, _vp],
     "plm_gemm_tc_wide": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_wide_space": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _vp, _i, _vp, _vp],
     "plm_gemm_tc_pair_space": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp, _i, _vp, _vp],

@@ -57,6 +57,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """x[rows] for a 2-D `x` with contiguous rows and int32 `rows` on the device: [len(rows), x.shape[1]]."""
+    _i32(rows, "rows")
+    if not x.is_cuda:
+        raise KernelError(f"x is on {x.device}; picolm_b200 kernels run on a CUDA device only")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("gather_rows takes a matrix with contiguous rows")
+    n, d = rows.numel(), x.shape[1]
+    out = torch.empty((n, d), dtype=x.dtype, device=x.device)
+    set_bounds("elementwise", n_rows=x.shape[0], device=x.device)
+    _check(_fn("elementwise", "plm_gather_rows")(_p(x), _p(out), _p(rows), n, d * x.element_size(),
+                                                x.stride(0) * x.element_size(), _stream()),
+           f"gather_rows {n} of {x.shape[0]}", nbytes=2 * n * d * x.element_size())
+    return out
+
+
 GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 

@@ -6,7 +6,10 @@ and what they are called is its business, not the model's);
 what the layer wants of the cache, one `CacheSpec` per part that keeps something;
 `prepare(max_seq_tokens)` runs once before the first step;
 `forward(stream, step, caches)` runs the layer on the stream in place, `caches`
-holding one entry per entry of `cache_specs()`, in that order.
+holding one entry per entry of `cache_specs()`, in that order.  An arrangement
+with `narrows_rows = True` also takes `keep_rows=`: the rows that anything after the
+layer will read (the model says so to the last layer of a step), so that it may
+narrow the stream to them as soon as its parts no longer need the others.
 
 `pre_norm` is the reference's Llama layer: `x += mixer(norm(x));
 x += feed_forward(norm(x))` (picolm/model_core.c:1797-2210).
@@ -25,6 +28,7 @@ class Arrangement(Part):
     (`forward`)."""
 
     wants: tuple = ()
+    narrows_rows = False
 
     def __init__(self, layer_spec: LayerSpec, runtime):
         super().__init__({}, runtime)
@@ -67,9 +71,19 @@ class Arrangement(Part):
 class PreNormBlock(Arrangement):
     wants = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
 
-    def forward(self, stream, step, caches):
+    narrows_rows = True
+
+    def forward(self, stream, step, caches, keep_rows=None):
+        """`keep_rows` (the model gives it to the last layer of a step when few rows are wanted): once the mixer
+        has seen all tokens, the stream is narrowed to those rows and the feed-forward runs on them alone; with
+        no row to keep, nothing runs after the mixer."""
         h = self._norm(self.mixer_norm, self.mixer, stream)
         stream.pending = self.mixer.forward(h, step, caches[0] if caches else None)
+        if keep_rows is not None:
+            if keep_rows.numel() == 0:
+                stream.pending = None
+                return
+            stream.narrow(keep_rows)
         h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
         stream.pending = self.feed_forward.forward(h, step)
 

@@ -387,6 +387,23 @@ def test_product_added_to_the_stream_in_its_epilogue(M, N, K):
     assert torch.allclose(h.float().cpu(), want, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,d", [(300, 2048), (70, 130), (5, 6)])
+def test_gather_rows(dtype, T, d):
+    """Rows picked out of a matrix, in the order asked for, repeats included; widths that allow 16-byte copies
+    and widths that do not; a source whose rows are wider than what is taken."""
+    from picolm_b200 import ops
+    torch.manual_seed(T + d)
+    x = torch.randn(T, d + 2).to(DT[dtype])
+    if dtype == "bfloat16" and d % 2:
+        pytest.skip("rows are copied four bytes at a time")
+    rows = torch.tensor([T - 1, 0, 3, 3, T // 2], dtype=torch.int32)
+    got = ops.gather_rows(x.to(DEV)[:, :d], rows.to(DEV))
+    assert torch.equal(got.cpu(), x[rows.long(), :d])
+    got = ops.gather_rows(x.to(DEV), rows.to(DEV))
+    assert torch.equal(got.cpu(), x[rows.long()])
+
+
 @pytest.mark.parametrize("window", [None, 90])
 @pytest.mark.parametrize("scratch", [False, True])
 @pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (40, 2, 16), (6, 3, 128), (4, 4, 48)])

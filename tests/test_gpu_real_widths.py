@@ -182,3 +182,35 @@ def test_long_prompts_at_real_widths(tmp_path_factory):
         eng.cache.check()
         ops.check_status()
         del eng
+
+
+def test_the_last_layer_runs_on_the_wanted_rows_alone(real):
+    """A prompt whose last logits alone are wanted runs its last layer's feed-forward on that row only (the
+    stream is narrowed once the attention has seen all tokens): the same logits, up to rounding, as when every
+    row is wanted and nothing is narrowed; and a prompt of which nothing is wanted leaves the cache as the other
+    steps do (the next token's logits agree with the plain implementation)."""
+    from picolm_b200.engine import Engine
+    d, toks, plain = real
+    eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 8, max_seqs=2)
+    n = 200
+    ref = plain(n, "bfloat16")
+    s = eng.new_sequence()
+    try:
+        few = eng.step([(s, toks[n])], [[n - 1]]).float().cpu()
+    finally:
+        eng.end_sequence(s)
+    s = eng.new_sequence()
+    try:
+        every = eng.step([(s, toks[n])], [list(range(n))]).float().cpu()
+    finally:
+        eng.end_sequence(s)
+    assert_close(few, ref[n - 1:], "bfloat16", "the last row alone")
+    assert_close(every, ref, "bfloat16", "every row")
+    s = eng.new_sequence()
+    try:
+        assert eng.step([(s, toks[n][:n - 1])], [[]]) is None       # nothing wanted: the last layer stops after its mixer
+        nxt = eng.step([(s, toks[n][n - 1:])], [[0]]).float().cpu()
+    finally:
+        eng.end_sequence(s)
+    assert_close(nxt, ref[n - 1:], "bfloat16", "after a prompt of which nothing was wanted")
+    eng.cache.check()
