@@ -205,8 +205,8 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
                  out: Optional[torch.Tensor] = None, pair: bool = False, add: bool = False) -> torch.Tensor:
     """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
     (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
-    tile's main loop; where whole tiles would leave SMs idle in the last round, the K blocks of all tiles
-    are handed out as one stream, cut into equal ranges).  With `swiglu`, w comes from `interleave_gate_up`
+    tile's main loop; where the tiles do not fill one round over the SMs and K is long, the K blocks of all
+    tiles are handed out as one stream, cut into equal ranges).  With `swiglu`, w comes from `interleave_gate_up`
     and the result is silu(gate) * up, [M, N/2] in bfloat16.  With `add`, `out` (float32) += the product.
     `pair`: the same by pairs of CTAs on tiles of 256 x 256 (`tcgen05.mma.cta_group::2`: each CTA of a pair
     loads half of the weight tile)."""
