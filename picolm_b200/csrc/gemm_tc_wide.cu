@@ -277,14 +277,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
                     int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride,
                     float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies) {
-    static_assert(!PAIR || BN == 256, "the pair works on tiles of 256 x 256");
+    static_assert(!PAIR || BN == 256 || BN == 192, "a pair works on tiles of 256 tokens x 256 or 192 features");
     constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
     // Pairs take two tiles of 64 columns of K per stage, each operand's in one copy (see make_map): with one tile
     // per copy the copies took longer than the MMAs (0.31 us per stage of 32 KB against 0.27 us).
     constexpr int SLABS = PAIR ? PAIR_SLABS : 1;
     constexpr uint32_t X_BYTES = BM * BK * 2 * SLABS, W_BYTES = W_ROWS * BK * 2 * SLABS;
-    constexpr uint32_t TMEM_COLS = 2 * BN;                               // two accumulators
+    constexpr uint32_t TMEM_COLS = 2 * BN > 256 ? 512 : 2 * BN;          // two accumulators (a power of two of columns)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -772,18 +772,29 @@ OutMap out_map(const void* out, int out_is_f32, int T, int F_out, long ldo) {
     return m;
 }
 
-template <int EPI, typename OutT>
+// The width of a pair's tiles for (T, F): 256 features, or 192 where that needs less time over the 74 pairs (rounds
+// of tiles x the tile's width: 3,072 features at 2,048 tokens are 96 tiles of 256, two rounds the second of which is
+// a third full, or 128 tiles of 192, two rounds of three quarters of the work each).  SwiGLU keeps 256 (its tiles
+// hold gate and up rows in groups of 128).
+int pair_width(int T, int F, int epilogue) {
+    if (epilogue == EPI_SWIGLU) return 256;
+    const long m_tiles = (T + 2 * BM - 1) / (2 * BM), pairs = sm_count() / 2;
+    const long r256 = (m_tiles * ((F + 255) / 256) + pairs - 1) / pairs, r192 = (m_tiles * ((F + 191) / 192) + pairs - 1) / pairs;
+    return r192 * 192 < r256 * 256 ? 192 : 256;
+}
+
+template <int BN, int EPI, typename OutT>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
                 cudaStream_t stream, float* parts = nullptr, int* flags = nullptr, int streamed_pairs = 0) {
     static bool configured = false;
     constexpr size_t smem = pair_smem(EPI);
-    auto kern = gemm_tc_wide_kernel<256, EPI, OutT, true>;
+    auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, true>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int m_tiles = (T + 2 * BM - 1) / (2 * BM), n_tiles = (F + 255) / 256;
+    const int m_tiles = (T + 2 * BM - 1) / (2 * BM), n_tiles = (F + BN - 1) / BN;
     int pairs = sm_count() / 2;
     if (m_tiles * n_tiles < pairs) pairs = m_tiles * n_tiles;
     if (streamed_pairs) pairs = streamed_pairs;
@@ -1013,14 +1024,21 @@ extern "C" int plm_gemm_tc_pair_space(const void* x, const void* w, void* out, i
         return plm_gemm_tc_wide_space(x, w, out, out_dtype, epilogue, T, F, K, ldx, ldw, ldo, nullptr, parts, flags, slots,
                                       status, stream);
     const int st = (STREAM_BUILD && parts && flags) ? plm_gemm_tc_pair_streamed(T, F, K, slots) : 0;
+    const int bn = st ? 256 : pair_width(T, F, epilogue);                // (the stream walk's slots are for tiles of 256)
     CUtensorMap mx, mw;
     int rc;
     if ((rc = make_map(&mx, x, T, K, ldx, BM, PAIR_SLABS)) != PLM_OK) return rc;
-    if ((rc = make_map(&mw, w, F, K, ldw, 128, PAIR_SLABS)) != PLM_OK) return rc;
-    if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
-    if (epilogue == EPI_RESIDUAL) return launch_pair<EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
-    if (out_dtype == PLM_F32) return launch_pair<EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
-    if (out_dtype == PLM_BF16) return launch_pair<EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if ((rc = make_map(&mw, w, F, K, ldw, bn / 2, PAIR_SLABS)) != PLM_OK) return rc;
+    if (epilogue == EPI_SWIGLU) return launch_pair<256, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (bn == 192) {
+        if (epilogue == EPI_RESIDUAL) return launch_pair<192, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
+        if (out_dtype == PLM_F32) return launch_pair<192, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream);
+        if (out_dtype == PLM_BF16) return launch_pair<192, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream);
+        return PLM_ERR_DTYPE;
+    }
+    if (epilogue == EPI_RESIDUAL) return launch_pair<256, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (out_dtype == PLM_F32) return launch_pair<256, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, parts, flags, st);
+    if (out_dtype == PLM_BF16) return launch_pair<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, parts, flags, st);
     return PLM_ERR_DTYPE;
 }
 

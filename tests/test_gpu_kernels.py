@@ -295,9 +295,10 @@ def test_sample_distribution():
 
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (2048, 512, 256), (300, 640, 200), (1000, 1152, 2048), (129, 128, 72)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (2048, 512, 256), (300, 640, 200), (1000, 1152, 2048), (129, 128, 72),
+                                   (2048, 3072, 256), (2100, 2944, 192)])
 def test_gemm_tc_pair(out_dtype, M, N, K, swiglu):
-    """The product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 x 256) against float64: whole
+    """The product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 x 256 or 256 x 192) against float64: whole
     and ragged tiles in both directions (a pair whose second CTA has no rows or no features left), K
     tails, more tiles than pairs, both epilogues."""
     from picolm_b200 import ops
@@ -358,7 +359,8 @@ def test_gemm_tc_wide_with_k_in_parts(out_dtype, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(2048, 2048, 512), (2304, 2562, 264), (1100, 2100, 328), (4100, 2400, 72),
-                                   (3000, 3340, 136), (2900, 3333, 64), (20000, 130, 64)])
+                                   (3000, 3340, 136), (2900, 3333, 64), (20000, 130, 64), (2048, 3072, 128),
+                                   (2100, 3000, 192)])
 def test_product_added_to_the_stream_in_its_epilogue(M, N, K):
     """x += a @ w^T with the add in the product's epilogue (single CTAs and pairs, as the shape decides):
     against float64, ragged tiles in both directions, widths that are no multiple of 4 or 32 (the
