@@ -271,18 +271,22 @@ __device__ __forceinline__ void turn_write_f32(const float* turn, int lane, floa
     }
 }
 
-template <int BN, int EPI, typename OutT, bool PAIR>
+// TWO: a stage holds two 64-column tiles of K per operand, each operand's brought in by one copy (pairs always;
+// single CTAs on 128-column tiles where K is a multiple of 64: three stages of 64 KB instead of six of 32 KB)
+template <int BN, int EPI, typename OutT, bool PAIR, bool TWO = PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
                     int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride,
                     float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies) {
     static_assert(!PAIR || BN == 256 || BN == 192, "a pair works on tiles of 256 tokens x 256 or 192 features");
-    constexpr int STAGES = PAIR ? pair_stages() : stages_of(BN);
+    static_assert(!PAIR || TWO, "pairs take two tiles of K per stage");
+    static_assert(PAIR || !TWO || BN == 128, "single CTAs take two tiles of K per stage on 128-column tiles only");
+    constexpr int STAGES = PAIR ? pair_stages() : TWO ? stages_of(BN) / 2 : stages_of(BN);
     constexpr int W_ROWS = PAIR ? BN / 2 : BN;                           // weight rows that this CTA loads per K block
     // Pairs take two tiles of 64 columns of K per stage, each operand's in one copy (see make_map): with one tile
     // per copy the copies took longer than the MMAs (0.31 us per stage of 32 KB against 0.27 us).
-    constexpr int SLABS = PAIR ? PAIR_SLABS : 1;
+    constexpr int SLABS = TWO ? PAIR_SLABS : 1;
     constexpr uint32_t X_BYTES = BM * BK * 2 * SLABS, W_BYTES = W_ROWS * BK * 2 * SLABS;
     constexpr uint32_t TMEM_COLS = 2 * BN > 256 ? 512 : 2 * BN;          // two accumulators (a power of two of columns)
     extern __shared__ uint8_t smem_raw[];
@@ -393,9 +397,11 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     } else {
                         mbar_expect_tx(full0 + 8 * s, X_BYTES + W_BYTES);
                         // weights are written by no kernel of the step: they may be requested at once
-                        tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, kb * BK, f0);
+                        if (TWO) tma_load_3d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, f0, kb * SLABS);
+                        else tma_load_2d(w_smem + s * W_BYTES, &map_w, full0 + 8 * s, kb * BK, f0);
                         if (!waited) { pdl_wait(); waited = true; WIDE_TRACE(1); }   // activations come from the kernel before
-                        tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, kb * BK, m0);
+                        if (TWO) tma_load_3d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, m0, kb * SLABS);
+                        else tma_load_2d(x_smem + s * X_BYTES, &map_x, full0 + 8 * s, kb * BK, m0);
                     }
                 }
             }
@@ -812,13 +818,13 @@ struct StreamSpace { float* parts; int* flags; int slots; };
 
 // How many CTAs walk the K blocks of all tiles as one stream; 0: the tiles are handed out whole (they fill
 // the SMs' rounds well enough, or there is no workspace).
-// `group`: 1 for single CTAs, 2 for pairs (the answer then counts pairs, and `n_kb` their stages of two tiles of K).
-int stream_ctas(int tiles, int n_kb, const StreamSpace& space, int group = 1) {
+// `group`: 1 for single CTAs, 2 for pairs (the answer then counts pairs); `n_kb` counts stages of `slabs` tiles of K.
+int stream_ctas(int tiles, int n_kb, const StreamSpace& space, int group = 1, int slabs = 1) {
     if (!space.parts || !space.flags) return 0;
     const int sms = sm_count() / group;
     int ctas = sms < space.slots / group ? sms : space.slots / group;
     const long total = (long)tiles * n_kb;
-    const int least = 8 / group;                                         // at least 8 tiles of K each
+    const int least = 8 / slabs;                                         // at least 8 tiles of K each
     if (total / least < ctas) ctas = (int)(total / least);
     if (ctas > 2 * tiles) ctas = 2 * tiles;                              // a tile is cut among three CTAs at most: its owner adds the parts up alone
     if (ctas < 2) return 0;
@@ -830,17 +836,17 @@ int stream_ctas(int tiles, int n_kb, const StreamSpace& space, int group = 1) {
     // In K blocks of time: a round of whole tiles takes a tile's K blocks; the stream takes total / ctas and what
     // its parts cost: some CTA's only piece is a part that is ready when everything else is, and its owner's
     // epilogue comes after that part's: measured at about 30 blocks' time.
-    const long whole = n_kb, streamed = (total + ctas - 1) / ctas + 32 / group;
+    const long whole = n_kb, streamed = (total + ctas - 1) / ctas + 32 / slabs;
     return streamed < whole ? ctas : 0;
 }
 
-template <int BN, int EPI, typename OutT>
+template <int BN, int EPI, typename OutT, bool TWO = false>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
            cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0,
            StreamSpace space = StreamSpace{nullptr, nullptr, 0}, int streamed = 0) {
     static bool configured = false;
     constexpr size_t smem = wide_smem(BN, EPI);
-    auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false>;
+    auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false, TWO>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -849,7 +855,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
     const int m_tiles = (T + BM - 1) / BM, n_tiles = (F + BN - 1) / BN;
     const int units = m_tiles * n_tiles * k_splits;
     int ctas = units < sm_count() ? units : sm_count();
-    if (kb_per_split <= 0) kb_per_split = (K + BK - 1) / BK;
+    if (kb_per_split <= 0) kb_per_split = (K + BK * (TWO ? 2 : 1) - 1) / (BK * (TWO ? 2 : 1));
     if (k_splits > 1) streamed = 0;
     if (streamed) ctas = streamed;
     // (the slices of a K split go to scratch memory by the threads' own stores)
@@ -887,12 +893,10 @@ __global__ void reduce_splits_kernel(const float* __restrict__ scratch, OutT* __
 
 // How the single-CTA form runs (T, F, K): the tile width, the parts of K that pass through scratch memory
 // (store epilogue only), and the CTAs of the stream walk (0: whole tiles).
-struct Plan { int bn, k_splits, kb_per, streamed; };
+struct Plan { int bn, k_splits, kb_per, streamed, slabs; };    // kb_per: stages of `slabs` tiles of K per part
 Plan wide_plan(int T, int F, int K, int epilogue, const StreamSpace& space) {
-    Plan p{128, 1, 0, 0};
+    Plan p{128, 1, 0, 0, 1};
     const long m_tiles = (T + BM - 1) / BM, sms = sm_count();
-    const int n_kb = (K + BK - 1) / BK;
-    p.kb_per = n_kb;
     const bool may_be_wide = F >= 2048 && T >= 256;
     if (may_be_wide) {
         // 256 columns feed the tensor cores best (a 128-column tile takes 0.8 of a 256-column tile's time for
@@ -901,12 +905,16 @@ Plan wide_plan(int T, int F, int K, int epilogue, const StreamSpace& space) {
         const long wide = (m_tiles * ((F + 255) / 256) + sms - 1) / sms, narrow = (m_tiles * ((F + 127) / 128) + sms - 1) / sms;
         p.bn = 0.8 * (double)narrow < (double)wide ? 128 : 256;
     }
+    // 128-column tiles take two tiles of K per stage and copy where K allows it (see the kernel's TWO)
+    p.slabs = (p.bn == 128 && K % BK == 0) ? PAIR_SLABS : 1;
+    int n_kb = (K + BK * p.slabs - 1) / (BK * p.slabs);                  // stages of K
+    p.kb_per = n_kb;
     const long tiles = m_tiles * ((F + p.bn - 1) / p.bn);
     // K splits where the tiles leave at least half of the SMs without work and K is long enough to cut
     if (epilogue == EPI_STORE && tiles * 2 <= sms && F % 4 == 0) {
         int splits = (int)(sms / tiles);
         if (splits > 8) splits = 8;
-        if (splits > n_kb / 4) splits = n_kb / 4;
+        if (splits > n_kb * p.slabs / 4) splits = n_kb * p.slabs / 4;    // at least four tiles of K a part
         if (splits < 1) splits = 1;
         p.kb_per = (n_kb + splits - 1) / splits;
         p.k_splits = (n_kb + p.kb_per - 1) / p.kb_per;                     // no part of K is empty
@@ -914,10 +922,11 @@ Plan wide_plan(int T, int F, int K, int epilogue, const StreamSpace& space) {
     if (p.k_splits > 1) return p;
     // The stream walk fills the SMs whatever the number of tiles: with wide tiles where it pays at all.
     if (may_be_wide && p.bn != 256) {
-        const int streamed = stream_ctas((int)(m_tiles * ((F + 255) / 256)), n_kb, space);
-        if (streamed) { p.bn = 256; p.streamed = streamed; return p; }
+        const int n_kb1 = (K + BK - 1) / BK;
+        const int streamed = stream_ctas((int)(m_tiles * ((F + 255) / 256)), n_kb1, space);
+        if (streamed) { p.bn = 256; p.slabs = 1; p.kb_per = n_kb1; p.streamed = streamed; return p; }
     }
-    p.streamed = stream_ctas((int)tiles, n_kb, space);
+    p.streamed = stream_ctas((int)tiles, n_kb, space, 1, p.slabs);
     return p;
 }
 
@@ -956,24 +965,25 @@ extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, i
     if (!STREAM_BUILD) parts = nullptr;                                  // this build walks whole tiles only
     const StreamSpace space{parts, flags, (parts && flags) ? slots : 0};
     const Plan plan = wide_plan(T, F, K, epilogue, space);
-    const int bn = plan.bn, k_splits = plan.k_splits, kb_per = plan.kb_per, st = plan.streamed;
+    const int bn = plan.bn, st = plan.streamed;
+    const bool two = plan.slabs == 2;
+    const bool cut = plan.k_splits > 1 && scratch && ldo == F && (((uintptr_t)scratch | (uintptr_t)out) & 15) == 0;
+    const int k_splits = cut ? plan.k_splits : 1, kb_per = cut ? plan.kb_per : 0;
     CUtensorMap mx, mw;
     int rc;
-    if ((rc = make_map(&mx, x, T, K, ldx, BM)) != PLM_OK) return rc;
-    if ((rc = make_map(&mw, w, F, K, ldw, bn)) != PLM_OK) return rc;
-    if (epilogue == EPI_SWIGLU) {
-        if (bn == 256) return launch<256, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-        return launch<128, EPI_SWIGLU, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-    }
-    if (epilogue == EPI_RESIDUAL) {
-        if (bn == 256) return launch<256, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-        return launch<128, EPI_RESIDUAL, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-    }
-    if (k_splits > 1 && scratch && ldo == F && (((uintptr_t)scratch | (uintptr_t)out) & 15) == 0) {
+    if ((rc = make_map(&mx, x, T, K, ldx, BM, plan.slabs)) != PLM_OK) return rc;
+    if ((rc = make_map(&mw, w, F, K, ldw, bn, plan.slabs)) != PLM_OK) return rc;
+// the kernel for this plan's tile width and stage, with the epilogue and result type given
+#define PLM_WIDE_LAUNCH(EPI, OutT, outp, ld, splits, per, stride)                                                        \
+    (bn == 256 ? launch<256, EPI, OutT, false>(mx, mw, outp, T, F, K, ld, status, stream, splits, per, stride, space, st)  \
+     : two     ? launch<128, EPI, OutT, true>(mx, mw, outp, T, F, K, ld, status, stream, splits, per, stride, space, st)   \
+               : launch<128, EPI, OutT, false>(mx, mw, outp, T, F, K, ld, status, stream, splits, per, stride, space, st))
+    if (epilogue == EPI_SWIGLU) return PLM_WIDE_LAUNCH(EPI_SWIGLU, bf16, (bf16*)out, ldo, 1, 0, (size_t)0);
+    if (epilogue == EPI_RESIDUAL) return PLM_WIDE_LAUNCH(EPI_RESIDUAL, float, (float*)out, ldo, 1, 0, (size_t)0);
+    if (cut) {
         // the parts of K as units of work of their own, each into its slice of the scratch; then the sum
         const size_t stride = (size_t)T * F;
-        rc = bn == 256 ? launch<256, EPI_STORE, float>(mx, mw, scratch, T, F, K, F, status, stream, k_splits, kb_per, stride)
-                       : launch<128, EPI_STORE, float>(mx, mw, scratch, T, F, K, F, status, stream, k_splits, kb_per, stride);
+        rc = PLM_WIDE_LAUNCH(EPI_STORE, float, scratch, (long)F, k_splits, kb_per, stride);
         if (rc != PLM_OK) return rc;
         const size_t n4 = stride / 4;
         const int blocks = (int)((n4 + 255) / 256 < (size_t)(8 * sm_count()) ? (n4 + 255) / 256 : (size_t)(8 * sm_count()));
@@ -983,12 +993,9 @@ extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, i
         return plm_status_of(launch_pdl(reduce_splits_kernel<bf16>, dim3(blocks), dim3(256), 0, stream,
                                         (const float*)scratch, (bf16*)out, k_splits, n4, stride));
     }
-    if (out_dtype == PLM_F32) {
-        if (bn == 256) return launch<256, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-        return launch<128, EPI_STORE, float>(mx, mw, (float*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-    }
-    if (bn == 256) return launch<256, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
-    return launch<128, EPI_STORE, bf16>(mx, mw, (bf16*)out, T, F, K, ldo, status, stream, 1, 0, 0, space, st);
+    if (out_dtype == PLM_F32) return PLM_WIDE_LAUNCH(EPI_STORE, float, (float*)out, ldo, 1, 0, (size_t)0);
+    return PLM_WIDE_LAUNCH(EPI_STORE, bf16, (bf16*)out, ldo, 1, 0, (size_t)0);
+#undef PLM_WIDE_LAUNCH
 }
 
 // The same without any workspace: K is never cut and tiles are handed out whole.
@@ -1006,7 +1013,7 @@ extern "C" int plm_gemm_tc_pair_streamed(int T, int F, int K, int slots) {
     if (slots <= 0 || K % BK) return 0;
     const StreamSpace space{&dummy_parts, &dummy_flags, slots};
     const int tiles = ((T + 2 * BM - 1) / (2 * BM)) * ((F + 255) / 256);
-    return stream_ctas(tiles, (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), space, 2);
+    return stream_ctas(tiles, (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), space, 2, PAIR_SLABS);
 }
 
 // The same product by pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 tokens x 256 features; see
