@@ -63,3 +63,15 @@ def test_when_the_stream_walk_is_taken():
     assert splits > 1 and streamed == 0                         # few tiles, store: K in parts through scratch memory
     assert ask(128, 2048, 2048, 2, 148)[1] == 1                 # the other epilogues never cut K that way
     assert ask(1024, 2048, 8192, 2, 100)[2] == 100              # no more CTAs than slots
+
+
+def test_which_form_a_shape_takes():
+    """The dispatcher's choice between pairs of CTAs and single CTAs (decided on the host, from the shape alone)."""
+    from picolm_b200.ops.gemm import pair_pays
+    assert pair_pays(2048, 2048, 8192, 2) and pair_pays(2048, 16384, 2048, 1) and pair_pays(2048, 3072, 2048, 0)
+    assert not pair_pays(2048, 2048, 8200, 2)                   # K no multiple of 64: the pairs' copies take whole tiles
+    assert not pair_pays(200, 2048, 2048, 0)                    # fewer than 256 tokens
+    assert not pair_pays(2048, 200, 2048, 0)                    # fewer than 256 features
+    assert pair_pays(1024, 2048, 8192, 2)                       # 32 tiles with a long K: the pairs walk them as a stream
+    assert not pair_pays(1024, 2048, 2048, 2)                   # 32 tiles with a short K: nothing to share out
+    assert not pair_pays(512, 2048, 8192, 0)                    # few tiles, store: single CTAs cut K through scratch memory
