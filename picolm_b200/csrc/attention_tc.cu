@@ -11,12 +11,13 @@
 //                  TMEM across pages; O is rescaled only when a row's maximum has outgrown the
 //                  reference it is kept against by a factor of 256
 // Warp 0 loads (TMA), warp 1 issues the MMAs and owns the tensor memory, warps 2..5 are the
-// 128 softmax threads.  The scores have NSB buffers in TMEM (two with head size 64, one with 128).
-// As soon as all 128 threads have handed over P(i), and with that have read S(i), the issuing
-// thread puts Q K(i + NSB)^T into the freed buffer and only then P(i) V(i), so the scores of the
-// pages ahead are there when the softmax threads get to them.  The softmax warps may drift up to a
-// page apart (never two: page i + 2 needs what follows everybody's arrival for page i), so even and
-// odd pages count their arrivals on barriers of their own.  Keys of a KV head are shared by its
+// 128 softmax threads.  The scores have two buffers in TMEM.  As soon as all 128 threads have handed
+// over P(i), and with that have read S(i), the issuing thread puts Q K(i + 2)^T into the freed buffer
+// and only then P(i) V(i), so the scores of the pages ahead are there when the softmax threads get to
+// them.  (With head size 128 the output takes half of the CTA's tensor memory; P(i) is then written over
+// S(i) and P(i) V(i) goes first.)  The softmax warps may drift up to a page apart (never two: page i + 2
+// needs what follows everybody's arrival for page i), so even and odd pages count their arrivals on
+// barriers of their own.  Keys of a KV head are shared by its
 // query heads through L2 (consecutive CTAs work on the heads of one group).
 //
 // Waits on mbarriers are bounded as in gemm_tc.cu: a wait that runs out records where in
@@ -35,15 +36,24 @@ constexpr int HD = PLM_HD;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention is built for head sizes 64 and 128");
 constexpr int CB = HD / 64;                       // 64-column blocks of a row (one 128-byte swizzle span each)
 constexpr int BQ = 128, BKV = 64;
-constexpr int STAGES = HD == 64 ? 4 : 2;
-constexpr int NSB = HD == 64 ? 2 : 1;             // score buffers in TMEM
+constexpr int KS = HD == 64 ? 4 : 2, VS = KS;    // tiles of keys and of values in shared memory
+// With head size 128 there is room for two tiles of each, and the scores are issued two pages ahead: keys and
+// values then have rings of their own (a key tile is free after Q K^T, a value tile only after P V, two pages
+// later).  With head size 64 a page's keys and values arrive on one barrier and are given back together: the
+// second ring's waits and commits cost the issuing thread more than four tiles of each leave to gain.
+constexpr bool SPLIT_RINGS = HD == 128;
+constexpr int NSB = 2;                            // score buffers in TMEM
+// With head size 128 the output takes half of the CTA's tensor memory (two CTAs an SM, 256 columns each), so
+// the probabilities of a page are written over its own scores: a thread has read its row of S before it
+// writes its row of P, and P takes the first 32 of the buffer's 64 columns.
+constexpr bool P_OVER_S = HD == 128;
 constexpr uint32_t Q_BLOCK = BQ * 128, KV_BLOCK = BKV * 128;       // bytes of one 64-column block
 constexpr uint32_t Q_BYTES = CB * Q_BLOCK, K_BYTES = CB * KV_BLOCK, V_BYTES = K_BYTES;
-constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = TM_P + 2 * 32, TMEM_COLS = 256;      // two P buffers
+constexpr uint32_t TM_S = 0, TM_P = NSB * 64, TM_PV = P_OVER_S ? TM_P : TM_P + 2 * 32, TMEM_COLS = 256;
 static_assert(TM_PV + HD <= TMEM_COLS, "TMEM budget");
-static_assert(STAGES > NSB, "the scores of page i + NSB are issued while page i still holds its stage");
-constexpr size_t SMEM = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+static_assert(SPLIT_RINGS ? (KS >= NSB && VS >= 2) : KS > NSB,
+              "the scores of page i + NSB are issued while page i still holds its values");
+constexpr size_t SMEM = Q_BYTES + KS * K_BYTES + VS * V_BYTES + 1024 + 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Latency-critical waits (a handoff per page between the MMA issuer and the softmax threads): poll
@@ -144,10 +154,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
-    const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
-    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * STAGES,
-                   s_full0 = kv_empty0 + 8 * STAGES, p_ready0 = s_full0 + 8 * NSB, pv_full0 = p_ready0 + 16;   // p_ready[2], pv_full[2]
+    const uint32_t q_smem = base, k_smem0 = base + Q_BYTES, v_smem0 = k_smem0 + KS * K_BYTES;
+    const uint32_t bars = v_smem0 + VS * V_BYTES;
+    const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = k_full0 + 8 * KS,
+                   v_full0 = SPLIT_RINGS ? k_empty0 + 8 * KS : k_full0, v_empty0 = SPLIT_RINGS ? v_full0 + 8 * VS : k_empty0,
+                   s_full0 = k_empty0 + 8 * KS + 16 * VS, p_ready0 = s_full0 + 8 * NSB,
+                   pv_full0 = p_ready0 + 16;                              // p_ready[2], pv_full[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (pv_full0 + 16 - raw));
     __shared__ int s_abort;
 
@@ -176,7 +188,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (threadIdx.x == 0) {
         s_abort = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int s = 0; s < KS; ++s) { mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); }
+        if (SPLIT_RINGS)
+            for (int s = 0; s < VS; ++s) { mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1); }
         for (int s = 0; s < NSB; ++s) mbar_init(s_full0 + 8 * s, 1);
         mbar_init(p_ready0, 128);
         mbar_init(p_ready0 + 8, 128);
@@ -202,25 +216,33 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int cb = 0; cb < CB; ++cb)
                 tma_load_2d(q_smem + cb * Q_BLOCK, &map_q, q_full, h * HD + cb * 64, t0 + tile * BQ);
-            int issued = 0;
+            int issued_k = 0, issued_v = 0;
             for (int i = 0; i < n_pages; ++i) {
-                const int s = i % STAGES;
-                if (*(volatile int*)&s_abort) break;
-                if (!mbar_wait(kv_empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, status, 1)) { s_abort = 1; break; }
-                mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
+                const int ks = i % KS, vs = i % VS;
                 const int row = (PLM_PAGE_NO(pages[page_first + i]) * G + g) * BKV;
-                const uint32_t k_dst = kv_smem + s * STAGE_BYTES, v_dst = k_dst + K_BYTES;
+                if (*(volatile int*)&s_abort) break;
+                if (!mbar_wait(k_empty0 + 8 * ks, ((i / KS) & 1) ^ 1, status, 1)) { s_abort = 1; break; }
+                mbar_expect_tx(k_full0 + 8 * ks, SPLIT_RINGS ? K_BYTES : K_BYTES + V_BYTES);
 #pragma unroll
-                for (int cb = 0; cb < CB; ++cb) {
-                    tma_load_2d(k_dst + cb * KV_BLOCK, &map_k, kv_full0 + 8 * s, cb * 64, row);
-                    tma_load_2d(v_dst + cb * KV_BLOCK, &map_v, kv_full0 + 8 * s, cb * 64, row);
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(k_smem0 + ks * K_BYTES + cb * KV_BLOCK, &map_k, k_full0 + 8 * ks, cb * 64, row);
+                issued_k = i + 1;
+                if (SPLIT_RINGS) {
+                    if (!mbar_wait(v_empty0 + 8 * vs, ((i / VS) & 1) ^ 1, status, 1)) { s_abort = 1; break; }
+                    mbar_expect_tx(v_full0 + 8 * vs, V_BYTES);
                 }
-                issued = i + 1;
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(v_smem0 + vs * V_BYTES + cb * KV_BLOCK, &map_v, v_full0 + 8 * vs, cb * 64, row);
+                issued_v = i + 1;
             }
-            if (*(volatile int*)&s_abort) {
+            if (*(volatile int*)&s_abort) {                              // let what is in flight land
                 mbar_wait(q_full, 0, nullptr, 0);
-                for (int i = max(0, issued - STAGES); i < issued; ++i)
-                    mbar_wait(kv_full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr, 0);
+                for (int i = max(0, issued_k - KS); i < issued_k; ++i)
+                    mbar_wait(k_full0 + 8 * (i % KS), (i / KS) & 1, nullptr, 0);
+                if (SPLIT_RINGS)
+                    for (int i = max(0, issued_v - VS); i < issued_v; ++i)
+                        mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1, nullptr, 0);
             }
         }
     } else if (warp == 1) {
@@ -228,7 +250,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc(BKV, false), idesc_o = instr_desc(HD, true);
             auto qk = [&](int i) {                                       // S[i % NSB] = Q K(i)^T
-                const uint32_t k_smem = kv_smem + (i % STAGES) * STAGE_BYTES;
+                const uint32_t k_smem = k_smem0 + (i % KS) * K_BYTES;
 #pragma unroll
                 for (int cb = 0; cb < CB; ++cb)
 #pragma unroll
@@ -238,10 +260,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                     smem_desc_sw128(k_smem + cb * KV_BLOCK) + (uint64_t)(k * 2), idesc_s,
                                     (cb > 0 || k > 0) ? 1u : 0u);
                 tc_commit(s_full0 + 8 * (i % NSB));
+                if (SPLIT_RINGS) tc_commit(k_empty0 + 8 * (i % KS));
             };
             bool ok = mbar_wait(q_full, 0, status, 2);
             for (int j = 0; j < NSB && j < n_pages && ok; ++j) {         // fill the score buffers
-                ok = mbar_wait(kv_full0 + 8 * (j % STAGES), (j / STAGES) & 1, status, 2);
+                ok = mbar_wait(k_full0 + 8 * (j % KS), (j / KS) & 1, status, 2);
                 if (ok) { tc_fence_after(); qk(j); }
             }
             for (int i = 0; i < n_pages && ok; ++i) {
@@ -250,19 +273,29 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_fence_after();
                 // The softmax threads have read S(i): its buffer takes the scores of page i + NSB at once, before
                 // P(i) V(i) is issued, so that they are there when the softmax of the page in between is done.
-                const int nxt = i + NSB;
-                if (nxt < n_pages) {
-                    if (!mbar_wait(kv_full0 + 8 * (nxt % STAGES), (nxt / STAGES) & 1, status, 2)) { ok = false; break; }
+                // Where P(i) lies in that buffer, P(i) V(i) goes first: the MMAs of one thread run in their order.
+                auto scores_ahead = [&]() {
+                    const int nxt = i + NSB;
+                    if (nxt >= n_pages) return true;
+                    if (!mbar_wait(k_full0 + 8 * (nxt % KS), (nxt / KS) & 1, status, 2)) return false;
                     tc_fence_after();
                     qk(nxt);
+                    return true;
+                };
+                if (!P_OVER_S && !scores_ahead()) { ok = false; break; }
+                if (SPLIT_RINGS) {
+                    if (!mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1, status, 2)) { ok = false; break; }
+                    tc_fence_after();
                 }
-                const uint32_t v_smem = kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES;
+                const uint32_t v_smem = v_smem0 + (i % VS) * V_BYTES;
+                const uint32_t p_tmem = P_OVER_S ? TM_S + (i % NSB) * 64 : TM_P + (i & 1) * 32;
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k)                       // O_page = P V(i), 16 keys a step
-                    tc_mma_bf16_ts(tmem + TM_PV, tmem + TM_P + (i & 1) * 32 + k * 8,
-                                   smem_desc_sw128_mn(v_smem + k * 2048), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_mma_bf16_ts(tmem + TM_PV, tmem + p_tmem + k * 8, smem_desc_sw128_mn(v_smem + k * 2048), idesc_o,
+                                   (i > 0 || k > 0) ? 1u : 0u);
                 tc_commit(pv_full0 + 8 * (i & 1));                     // P buffer i % 2 is free, O holds pages 0..i
-                tc_commit(kv_empty0 + 8 * (i % STAGES));
+                tc_commit(v_empty0 + 8 * (i % VS));
+                if (P_OVER_S && !scores_ahead()) { ok = false; break; }
             }
             if (!ok) s_abort = 1;
         }
@@ -312,8 +345,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // the scale is positive, so the maximum of the scaled scores is the scaled maximum
             const float m_cand = fmaxf(m_ref, mx * scale_log2);
             const bool raise = m_cand > m_ref + RESCALE_LOG2 || (m_ref == -INFINITY && m_cand > -INFINITY);
-            // P has two buffers: page i writes the one that page i - 2 used, whose P V must be done
-            if (i > 1 && !mbar_spin(pv_full0 + 8 * (i & 1), ((i - 2) >> 1) & 1, status, 3)) { ok = false; break; }
+            // P has two buffers: page i writes the one that page i - 2 used, whose P V must be done.  (Written over
+            // the scores it is: S(i) was issued after P(i - 2) V(i - 2) by the same thread.)
+            if (!P_OVER_S && i > 1 && !mbar_spin(pv_full0 + 8 * (i & 1), ((i - 2) >> 1) & 1, status, 3)) { ok = false; break; }
             if (__any_sync(0xffffffffu, raise)) {                        // tcgen05.ld/st are warp-wide
                 const float alpha = raise ? ex2(m_ref - m_cand) : 1.f;   // m_ref = -inf gives 0
                 if (i > 0) {
@@ -353,14 +387,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             unpack2(sum2, sum_lo, sum_hi);
             const float sum = sum_lo + sum_hi;
             l += sum;
-            tc_st32(tmem + lane_bits + TM_P + (i & 1) * 32, p);
+            tc_st32(tmem + lane_bits + (P_OVER_S ? TM_S + (i % NSB) * 64 : TM_P + (i & 1) * 32), p);
             tc_wait_st();
             // places of the sequence's last page that hold no key yet: zero those rows of V, so that
             // whatever an earlier owner of the page left there cannot reach the sum (0 * NaN)
             const int valid = kv_len - key0;
             if (valid < BKV) {
-                ok = mbar_wait(kv_full0 + 8 * (i % STAGES), (i / STAGES) & 1, status, 3);
-                uint8_t* v_ptr = smem_raw + (kv_smem + (i % STAGES) * STAGE_BYTES + K_BYTES - raw);
+                ok = mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1, status, 3);
+                uint8_t* v_ptr = smem_raw + (v_smem0 + (i % VS) * V_BYTES - raw);
                 for (int idx = (int)threadIdx.x - 64; idx < (BKV - valid) * CB * 8; idx += 128) {
                     const int row = valid + idx / (CB * 8), rest = idx % (CB * 8);
                     *reinterpret_cast<uint4*>(v_ptr + (rest / 8) * KV_BLOCK + row * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
