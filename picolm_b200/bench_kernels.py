@@ -131,6 +131,45 @@ def _print_stations():
               f"(medians over {int(ok.sum())} CTAs)", file=sys.stderr)
 
 
+def _print_attention_stations(hd):
+    """The last launch of the prefill attention's trace build (`-DPLM_ATTN_TRACE`): how many cycles the first
+    softmax warp and the issuing thread of the CTA that starts first spent between their stations, page by
+    page (means over pages 8 to 120, where the pipeline is in its steady state)."""
+    import ctypes
+
+    import numpy as np
+
+    from .csrc.build import load_library
+    from .ops import _lib
+    name, flags = _lib.VARIANT_OF[f"attention_tc@hd{hd}"]
+    lib = load_library(name, (f"-DPLM_HD={hd}",) + tuple(flags))
+    buf = (ctypes.c_longlong * (5 * 128 * 8))()
+    lib.plm_attn_tc_trace_read.argtypes = [ctypes.c_void_p]
+    if lib.plm_attn_tc_trace_read(buf):
+        raise RuntimeError("the trace could not be read")
+    t = np.frombuffer(buf, dtype=np.int64).reshape(5, 128, 8)
+    mma = t[4]
+    lo, hi = 8, 120
+    if mma[hi, 2] == 0:
+        print("the first CTA had fewer than 121 pages: no steady state to show", file=sys.stderr)
+        return
+
+    def mean(x):
+        return float(np.mean(x[lo:hi]))
+
+    for w in range(4):
+        sm = t[w]
+        print(f"softmax warp {w}, cycles a page: period {mean(sm[1:, 0] - sm[:-1, 0]):.0f} = "
+              f"scores to registers {mean(sm[:, 1] - sm[:, 0]):.0f} + maximum and P's place {mean(sm[:, 2] - sm[:, 1]):.0f} + "
+              f"exponentials {mean(sm[:, 3] - sm[:, 2]):.0f} + P to tensor memory {mean(sm[:, 4] - sm[:, 3]):.0f} + "
+              f"arrive {mean(sm[:, 5] - sm[:, 4]):.0f} + wait for the next scores {mean(sm[1:, 0] - sm[:-1, 5]):.0f}; "
+              f"its arrival to the issuing thread seeing everybody's {mean(mma[:, 0] - sm[:, 5]):.0f}", file=sys.stderr)
+    print(f"issuing thread, cycles a page: period {mean(mma[1:, 0] - mma[:-1, 0]):.0f} = "
+          f"first group of MMAs {mean(mma[:, 1] - mma[:, 0]):.0f} + second group and commits {mean(mma[:, 2] - mma[:, 1]):.0f} + "
+          f"wait for the next page's arrivals {mean(mma[1:, 0] - mma[:-1, 2]):.0f}; from everybody's arrival to the "
+          f"scores of the page after next seen by warp 0 {mean(t[0][2:, 0] - mma[:-2, 0]):.0f}", file=sys.stderr)
+
+
 def _paged_cache(batch, ctx, G, hd, n_copies):
     pages_per_seq = (ctx + 63) // 64
     n_pages = batch * pages_per_seq + 1
@@ -182,6 +221,8 @@ def bench_attention_prefill(args):
             fn(q, caches[i][0], caches[i][1], start, kvlen, table, T, G, 1.0 / math.sqrt(hd))
 
     sec = _time(run, len(caches), 1 if args.once else args.iters, 0 if args.once else args.warmup)
+    if args.stations and fn is ops.attention_prefill_tc and not args.library:
+        _print_attention_stations(hd)
     flops = 2.0 * 2 * H * hd * T * (T + 1) / 2
     return {"kernel": "scaled_dot_product_attention (library)" if args.library else "attention_prefill", "tokens": T, "heads": H, "kv_heads": G, "head_dim": hd,
             "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 2)}
@@ -244,12 +285,13 @@ def main(argv=None):
     ap.add_argument("--once", action="store_true", help="one launch, no warm-up (for a profiler)")
     ap.add_argument("--graph", action="store_true", help="time the launches as one CUDA graph (for short kernels)")
     ap.add_argument("--stations", action="store_true",
-                    help="gemm (m > 64): run the trace build of the prompt-shaped product and print when its CTAs passed "
-                         "their stations in the last launch (stderr)")
+                    help="gemm (m > 64), attention_prefill: run the kernel's trace build and print when its CTAs "
+                         "(the attention: the threads of its first CTA) passed their stations in the last launch (stderr)")
     args = ap.parse_args(argv)
     if args.stations:
         from .ops import _lib
         _lib.VARIANT_OF["gemm_tc_wide"] = ("gemm_tc_wide@trace", ("-DPLM_WIDE_TRACE",))
+        _lib.VARIANT_OF[f"attention_tc@hd{args.head_dim}"] = (f"attention_tc@hd{args.head_dim}_trace", ("-DPLM_ATTN_TRACE",))
     global USE_GRAPH
     USE_GRAPH = args.graph and not args.once
     fn = {"gemm": bench_gemm, "attention_decode": bench_attention_decode,

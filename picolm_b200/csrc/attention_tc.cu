@@ -144,6 +144,21 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn) {
            ((uint32_t)(BQ >> 4) << 24);
 }
 
+// A build with -DPLM_ATTN_TRACE records the SM's cycle counter at the points marked ATTN_TRACE below, for the
+// first 128 pages of the CTA that starts first: rows 0..3 of the table for the four softmax warps (0 scores
+// seen, 1 scores in registers, 2 maximum known and P's place free, 3 exponentials done, 4 P in tensor memory,
+// 5 arrived), row 4 for the issuing thread (0 everybody's arrival seen, 1 first group of MMAs issued, 2 both
+// issued and committed).  plm_attn_tc_trace_read copies the table out.  A point costs the thread that passes
+// it some tens of cycles, so the traced CTA runs a little slower than the others.
+#ifdef PLM_ATTN_TRACE
+constexpr int TRACE_PAGES = 128;
+__device__ long long plm_attn_trace[5][TRACE_PAGES][8];
+#define ATTN_TRACE(who, page, point)                                                                      \
+    do { if (traced && (page) < TRACE_PAGES) plm_attn_trace[who][page][point] = clock64(); } while (0)
+#else
+#define ATTN_TRACE(who, page, point) do { } while (0)
+#endif
+
 // grid = (query tiles of the longest sequence, heads, sequences)
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -184,6 +199,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_pages = page_last - page_first + 1;
     const int* pages = block_table + (size_t)b * max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef PLM_ATTN_TRACE
+    const bool traced = lin == 0 && b == 0 && lane == 0 && warp >= 1;
+    const int softmax_warp = warp - 2;
+#endif
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -271,6 +290,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (*(volatile int*)&s_abort) { ok = false; break; }
                 if (!mbar_spin(p_ready0 + 8 * (i & 1), (i >> 1) & 1, status, 2)) { ok = false; break; }
                 tc_fence_after();
+                ATTN_TRACE(4, i, 0);
                 // The softmax threads have read S(i): its buffer takes the scores of page i + NSB at once, before
                 // P(i) V(i) is issued, so that they are there when the softmax of the page in between is done.
                 // Where P(i) lies in that buffer, P(i) V(i) goes first: the MMAs of one thread run in their order.
@@ -283,6 +303,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     return true;
                 };
                 if (!P_OVER_S && !scores_ahead()) { ok = false; break; }
+                if (!P_OVER_S) ATTN_TRACE(4, i, 1);
                 if (SPLIT_RINGS) {
                     if (!mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1, status, 2)) { ok = false; break; }
                     tc_fence_after();
@@ -295,7 +316,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                    (i > 0 || k > 0) ? 1u : 0u);
                 tc_commit(pv_full0 + 8 * (i & 1));                     // P buffer i % 2 is free, O holds pages 0..i
                 tc_commit(v_empty0 + 8 * (i % VS));
+                if (P_OVER_S) ATTN_TRACE(4, i, 1);
                 if (P_OVER_S && !scores_ahead()) { ok = false; break; }
+                ATTN_TRACE(4, i, 2);
             }
             if (!ok) s_abort = 1;
         }
@@ -315,6 +338,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < n_pages && ok; ++i) {
             if (!mbar_spin(s_full0 + 8 * (i % NSB), (i / NSB) & 1, status, 3)) { ok = false; break; }
             tc_fence_after();
+            ATTN_TRACE(softmax_warp, i, 0);
             const int key0 = (page_first + i) * BKV;
             const bool need_mask = key0 + BKV - 1 > pos0 || key0 < (window > 0 ? pos_last - window + 1 : 0);
             float mx = -INFINITY;
@@ -322,6 +346,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64, s0);
             tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64 + 32, s1);
             tc_wait_ld();
+            ATTN_TRACE(softmax_warp, i, 1);
             if (need_mask) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -367,6 +392,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (raise) { l *= alpha; m_ref = m_cand; }
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            ATTN_TRACE(softmax_warp, i, 2);
             uint32_t p[32];
             const uint64_t scale2 = pack2(__float_as_uint(scale_log2), __float_as_uint(scale_log2));
             const uint64_t neg_m2 = pack2(__float_as_uint(-m_use), __float_as_uint(-m_use));
@@ -387,8 +413,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             unpack2(sum2, sum_lo, sum_hi);
             const float sum = sum_lo + sum_hi;
             l += sum;
+            ATTN_TRACE(softmax_warp, i, 3);
             tc_st32(tmem + lane_bits + (P_OVER_S ? TM_S + (i % NSB) * 64 : TM_P + (i & 1) * 32), p);
             tc_wait_st();
+            ATTN_TRACE(softmax_warp, i, 4);
             // places of the sequence's last page that hold no key yet: zero those rows of V, so that
             // whatever an earlier owner of the page left there cannot reach the sum (0 * NaN)
             const int valid = kv_len - key0;
@@ -406,6 +434,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // another (never two: page i + 2 needs P V(i), which needs everybody's arrival for page i), and its
             // arrival must not be counted among those of the page before.
             mbar_arrive(p_ready0 + 8 * (i & 1));
+            ATTN_TRACE(softmax_warp, i, 5);
         }
         if (ok && !mbar_spin(pv_full0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, status, 3)) ok = false;
         tc_fence_after();
@@ -446,6 +475,13 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }  // namespace
 
 extern "C" int plm_attn_tc_head_dim() { return HD; }
+
+#ifdef PLM_ATTN_TRACE
+// [5][128][8] cycle counts of the last launch's first CTA (see ATTN_TRACE above)
+extern "C" int plm_attn_tc_trace_read(void* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, plm_attn_trace, sizeof(plm_attn_trace));
+}
+#endif
 
 // q [T, H, HD] bf16, k/v cache [n_pages, G, 64, HD] bf16, out [T, H*HD] bf16.  seq_start [B+1]:
 // offsets of each sequence's new tokens; seq_kv_len [B]: its length after the step; max_new: the most
