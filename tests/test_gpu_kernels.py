@@ -634,11 +634,14 @@ def test_attention_decode_many_ranges_of_a_long_sequence(H, G, hd, n_splits):
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 3072, 2048), (16, 200, 264), (17, 256, 512), (33, 130, 1024),
-                                   (64, 2048, 8192), (5, 16384, 2048), (64, 40000, 128), (3, 2048, 2112)])
+                                   (64, 2048, 8192), (5, 16384, 2048), (64, 40000, 128), (3, 2048, 2112),
+                                   (7, 77001, 200), (20, 38000, 72)])
 def test_gemm_tc_skinny_cluster(out_dtype, M, N, K):
     """The decode-shaped product whose K splits meet in distributed shared memory: every cluster size
     (1, 2, 4, 8), all three token-tile widths, ragged feature edges, K ranges that leave a CTA of the
-    cluster with fewer (or no) K blocks."""
+    cluster with fewer (or no) K blocks; and, with more than 296 tiles of 128 features, the CTAs that stay
+    and walk over the tiles (some take one tile more than others, the last tile is ragged, K ends inside
+    a block)."""
     from picolm_b200 import ops
     torch.manual_seed(M + N + K)
     a = (torch.randn(M, K) / K ** 0.25).to(torch.bfloat16)
