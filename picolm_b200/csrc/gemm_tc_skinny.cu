@@ -391,7 +391,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T
 
 // ---- The walk: products with more tiles than two CTAs an SM hold at once (the LM head: 1,002 tiles of 128 rows
 // at a vocabulary of 128,256), no split of K, plain store.  A CTA that starts, fills its ring, drains it and
-// writes its tile leaves the SM's share of the bandwidth idle at both ends; here 2 x 148 CTAs stay and take the
+// writes its tile leaves the SM's share of the bandwidth idle at both ends; here two CTAs an SM stay and take the
 // tiles blockIdx.x, blockIdx.x + gridDim.x, ... one after another: the ring keeps filling across the tiles'
 // boundaries, the accumulator has two places in tensor memory, and the four epilogue warps write tile i (each
 // thread one feature's results straight from tensor memory, a warp 32 neighbouring features of one token)
