@@ -60,12 +60,14 @@ def test_graph_and_plain_launches_agree(real):
     kernel, up to rounding: the graph sizes the decode attention's key ranges for its length class,
     the plain launch for the true length, so the partial sums are cut differently."""
     from picolm_b200.engine import Engine
+    from picolm_b200.ops import _lib
     d, toks, _ = real
     outs = []
     for graphs in (True, False):
         eng = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 8, max_seqs=4, use_graphs=graphs)
         outs.append(torch.cat(run_batch(eng, [toks[70], toks[33]], [40, 9])))
-        assert bool(eng._graphs) == graphs
+        if not (_lib.CHECKED or _lib.TRACED):                     # (those builds launch every kernel by itself)
+            assert bool(eng._graphs) == graphs
         del eng
     assert_close(outs[0], outs[1], "bfloat16", "graph against plain launches")
 
